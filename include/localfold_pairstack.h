@@ -1,0 +1,292 @@
+/*
+ * localfold_pairstack.h - C ABI of the B200 (sm_100a) pair-stack library.
+ *
+ * Every entry point below replaces one operator of the reference's kernel
+ * library (JavaScript classes over WebGPU); the reference interface each one
+ * stands in for is cited as path:line within the reference project.  The ABI
+ * carries plain pointers, sizes and enums only.  Nothing here throws: every
+ * call returns an lf_status and lf_last_error() holds the message, which
+ * names the tensor and the expected length for shape errors in the same
+ * words as webgpu/kernels/triangle/types.js:7-11.
+ *
+ * Conventions
+ *  - The caller owns every input and output buffer.  `space` says where the
+ *    activation buffers of a call live: LF_SPACE_HOST (float32 host memory;
+ *    the call copies in, runs, copies out and returns when the output is
+ *    ready) or LF_SPACE_DEVICE (device memory of the context's GPU; the call
+ *    only enqueues work on the context's stream - use lf_context_synchronize).
+ *  - Activations in host space are float32.  In device space `act_dtype`
+ *    gives their storage type.
+ *  - Weights are handed over once per operator as float32 host arrays in the
+ *    reference's own layouts and field order; the library keeps its own
+ *    device-resident copy (repacked for its kernels) until lf_weights_destroy.
+ *  - One context per host thread; calls on one context are serialised by the
+ *    caller.  There is no CPU fallback anywhere behind this header.
+ */
+#ifndef LOCALFOLD_PAIRSTACK_H
+#define LOCALFOLD_PAIRSTACK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LF_API __attribute__((visibility("default")))
+#else
+#define LF_API
+#endif
+
+typedef enum lf_status {
+  LF_OK = 0,
+  LF_ERR_SHAPE = 1,       /* a tensor has the wrong number of elements */
+  LF_ERR_ARGUMENT = 2,    /* null pointer, unknown enum, missing dialect bit */
+  LF_ERR_CUDA = 3,        /* a CUDA runtime call failed */
+  LF_ERR_MEMORY = 4,      /* device allocation refused */
+  LF_ERR_UNSUPPORTED = 5, /* shape outside what the kernels cover */
+  LF_ERR_TIMEOUT = 6      /* a bounded device-side wait ran out */
+} lf_status;
+
+typedef enum lf_space { LF_SPACE_HOST = 0, LF_SPACE_DEVICE = 1 } lf_space;
+typedef enum lf_dtype { LF_DTYPE_F32 = 0, LF_DTYPE_BF16 = 1 } lf_dtype;
+
+/* Arithmetic mode.  F32: float32 storage and float32 FMA accumulation
+ * (the reference's `precision: "f32"`).  BF16: bf16 operands on the tensor
+ * cores with float32 accumulation, float32 statistics, softmax and gates
+ * (stands where the reference has `precision: "f16"`). */
+typedef enum lf_precision { LF_PRECISION_F32 = 0, LF_PRECISION_BF16 = 1 } lf_precision;
+
+/* LayerNorm variance: the reference's `variance: "two-pass" | "fast"`
+ * (webgpu/kernels/triangle/shaders.js:43-58). No default: 0 is rejected. */
+typedef enum lf_variance { LF_VARIANCE_TWO_PASS = 1, LF_VARIANCE_FAST = 2 } lf_variance;
+
+typedef struct lf_context lf_context;
+typedef struct lf_weights lf_weights;
+
+/* {elapsedMilliseconds, memory} of every reference operator result
+ * (webgpu/kernels/triangle/webgpu.js:165). elapsed_ms is device time between
+ * CUDA events for host-space calls and 0 for device-space calls. */
+typedef struct lf_result {
+  float elapsed_ms;
+  uint64_t peak_bytes;   /* high-water mark of the context's scratch arena */
+  uint32_t launches;     /* kernels of this library launched by the call */
+} lf_result;
+
+/* ---- context ------------------------------------------------------------ */
+
+/* Replaces createNodeDevice() + per-device runtime (webgpu/node.js:51-81,
+ * webgpu/runtime/execution.js:156).  `stream` may be NULL (the context makes
+ * its own) or a cudaStream_t the caller owns. */
+LF_API lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out);
+LF_API void lf_context_destroy(lf_context* ctx);
+LF_API const char* lf_last_error(const lf_context* ctx);
+LF_API lf_status lf_context_synchronize(lf_context* ctx);
+/* Total kernels launched through this context since creation. */
+LF_API uint64_t lf_context_launch_count(const lf_context* ctx);
+/* Scratch arena: grows on demand; reserve up front to keep allocation out of
+ * timed regions; release returns it to the driver. */
+LF_API lf_status lf_context_reserve(lf_context* ctx, uint64_t bytes);
+LF_API void lf_context_release_scratch(lf_context* ctx);
+LF_API const char* lf_version(void);
+
+/* ---- weights ------------------------------------------------------------ */
+
+typedef enum lf_weight_kind {
+  /* 16 tensors in the order of webgpu/kernels/triangle/weights.js:4-10
+   * (layerNormInWeight ... linearGBias); linear weights are [out][in]. */
+  LF_WEIGHTS_TRIANGLE_AF2 = 1,
+  /* 8 tensors of shared/af3/weights/weights.js:407-416: leftNormInputScale,
+   * leftNormInputOffset, projection (c,2c interleaved), gate (c,2c),
+   * centerNormScale, centerNormOffset, outputProjection, gatingLinear. */
+  LF_WEIGHTS_TRIANGLE_AF3 = 2,
+  /* 9 tensors of webgpu/kernels/attention.js:64-80 (queryNormScale,
+   * queryNormOffset, queryWeight, keyWeight, valueWeight, gatingWeight,
+   * gatingBias, outputWeight, outputBias), then the pair bias tensors:
+   * none; or projectionWeight ("normalized-input"); or layerNormScale,
+   * layerNormOffset, projectionWeight ("separate"). All linears (in,out). */
+  LF_WEIGHTS_ATTENTION_AF2 = 3,
+  /* shared/af3/weights/weights.js:417-442: actNormScale, actNormOffset,
+   * pairBiasProjection (c,H), qProjection (H*d,c), kProjection (H*d,c),
+   * vProjection (c,H*d), gatingQuery (H*d,c), outputProjection (H*d,c),
+   * then optional gatingQueryBias, outputProjectionBias (count 0 = absent). */
+  LF_WEIGHTS_GRID_ATTENTION_AF3 = 4,
+  /* webgpu/kernels/transition.js:477-480: layerNormScale, layerNormOffset,
+   * firstWeight (c,h), firstBias, secondWeight (h,c), secondBias. */
+  LF_WEIGHTS_TRANSITION_AF2 = 5,
+  /* shared/af3/weights/weights.js:447-452: inputLayerNormScale,
+   * inputLayerNormOffset, transition1 (c, 2*f*c gate half first),
+   * transition2 (f*c, c). */
+  LF_WEIGHTS_TRANSITION_AF3 = 6,
+  /* webgpu/kernels/outer-product-mean.js:72-75: layerNormScale,
+   * layerNormOffset, leftWeight (cm,c), leftBias, rightWeight, rightBias,
+   * outputWeight (c*c, cz), outputBias. */
+  LF_WEIGHTS_OPM_AF2 = 7,
+  /* shared/af3/weights/weights.js:699-727 (singleAttention): layerNormScale,
+   * layerNormOffset, qProjection (c,H*d), qBias, kProjection, vProjection,
+   * gatingQuery, outputProjection (H*d,c), then the block's
+   * singlePairLogitsNormScale, singlePairLogitsNormOffset,
+   * singlePairLogitsProjection (cz,H). */
+  LF_WEIGHTS_SINGLE_ATTENTION_AF3 = 8
+} lf_weight_kind;
+
+/* Shape of the operator the weights belong to; unused fields are 0. */
+typedef struct lf_weight_dims {
+  int32_t channels;        /* c_z for pair operators, c_m / c_s otherwise   */
+  int32_t hidden;          /* triangle c_hidden, transition hidden, OPM c   */
+  int32_t heads;           /* attention heads                                */
+  int32_t head_dim;        /* attention head dimension                       */
+  int32_t pair_channels;   /* channels of a separate pair-bias source / c_z  */
+  int32_t out_channels;    /* OPM c_z                                        */
+} lf_weight_dims;
+
+/* Replaces packWeights / packAttentionWeights and the resident-weight upload
+ * (webgpu/kernels/triangle/weights.js:85-171, webgpu/kernels/attention.js:82-97,
+ * webgpu/runtime/resident.js).  `tensors[i]` holds `counts[i]` float32 values
+ * on the host; counts are checked against `dims`. */
+LF_API lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,
+                                   const float* const* tensors, const int64_t* counts,
+                                   int32_t n_tensors, lf_weights** out);
+LF_API void lf_weights_destroy(lf_weights* w);
+
+/* ---- int5 tensor decode ------------------------------------------------- */
+
+/* Replaces readTensorRange for dtype "int5" (shared/weights/dtype.js:330-378)
+ * and the on-device decode of webgpu/weights/quantised-upload.js:100-120:
+ * `elements` values, groups of `block` codes of 5 bits, least significant bit
+ * first, one fp16 scale and one fp16 zero per group; value = code*scale+zero.
+ * `payload` is the tensor's bytes as stored in a shard (host memory);
+ * scale_offset / zero_offset are byte offsets inside it.  Output: float32 on
+ * the host (`out_space` HOST) or on the device. */
+LF_API lf_status lf_int5_decode(lf_context* ctx, const uint8_t* payload, uint64_t payload_bytes,
+                                uint64_t scale_offset, uint64_t zero_offset, int64_t elements,
+                                int32_t block, lf_space out_space, float* out);
+
+/* ---- operators ---------------------------------------------------------- */
+
+/* TriangleMultiplication{Outgoing,Incoming}Gpu.run
+ * (webgpu/kernels/triangle/webgpu.js:25-182) and af3TriangleMultiplication
+ * (webgpu/af3/trunk/triangle.js:148-169).  out = update, or z + update when
+ * `residual` (the in-place form of webgpu/af2/evoformer/block.js:1288-1534;
+ * `out` may alias `z`). */
+typedef struct lf_triangle_desc {
+  int32_t length, c_z, c_hidden;
+  int32_t incoming;            /* 0 outgoing (ikc,jkc->ijc), 1 incoming (kjc,kic->ijc) */
+  int32_t variance;            /* lf_variance */
+  int32_t precision;           /* lf_precision */
+  int32_t residual;
+  int32_t divide_by_length;    /* dialect bit triangleMulDivideByLength */
+  float epsilon;
+  int32_t space;               /* lf_space */
+  int32_t act_dtype;           /* lf_dtype of z/out in device space */
+  const void* z;               /* [length, length, c_z] */
+  const float* mask;           /* [length, length] float32 (same space) */
+  void* out;                   /* [length, length, c_z] */
+  const lf_weights* weights;   /* TRIANGLE_AF2 or TRIANGLE_AF3 */
+} lf_triangle_desc;
+LF_API lf_status lf_triangle_multiplication_run(lf_context* ctx, const lf_triangle_desc* d, lf_result* r);
+
+/* AttentionGpu.run (webgpu/kernels/attention.js:2580-2739): gated multi-head
+ * attention over `batch` rows of `query_length` positions with optional pair
+ * bias and transposed orientation; and Af3GridSelfAttentionGpu.run
+ * (webgpu/af3/trunk/grid-attention.js:1264) when the weights are
+ * GRID_ATTENTION_AF3 (batch = query_length = n; `swap_transposed_bias` is the
+ * dialect bit and must be 0 or 1 explicitly). */
+typedef enum lf_pair_bias { LF_PAIR_BIAS_NONE = 0, LF_PAIR_BIAS_SEPARATE = 1, LF_PAIR_BIAS_NORMALIZED_INPUT = 2 } lf_pair_bias;
+typedef struct lf_attention_desc {
+  int32_t batch, query_length, channels, heads;
+  int32_t transpose;
+  int32_t pair_bias;           /* lf_pair_bias */
+  int32_t pair_channels;       /* channels of pair_activations (SEPARATE) */
+  int32_t swap_transposed_bias;/* AF3 dialect bit; -1 = not applicable (AF2 weights) */
+  int32_t variance, precision, residual;
+  float epsilon;
+  int32_t space, act_dtype;
+  const void* activations;     /* [batch*query_length, channels] in memory order */
+  const float* mask;           /* [batch*query_length] in memory order */
+  const void* pair_activations;/* [Q, Q, pair_channels] when SEPARATE */
+  void* out;
+  const lf_weights* weights;
+} lf_attention_desc;
+LF_API lf_status lf_attention_run(lf_context* ctx, const lf_attention_desc* d, lf_result* r);
+
+/* TransitionGpu.run (webgpu/kernels/transition.js:1009-1105) for
+ * TRANSITION_AF2 weights and Af3TransitionGpu.run
+ * (webgpu/af3/trunk/transition.js:579) for TRANSITION_AF3. */
+typedef struct lf_transition_desc {
+  int64_t rows;
+  int32_t channels, hidden;    /* hidden = hiddenChannels (AF2) or factor*channels (AF3) */
+  int32_t variance, precision, residual;
+  float epsilon;
+  int32_t space, act_dtype;
+  const void* activations;
+  void* out;
+  const lf_weights* weights;
+} lf_transition_desc;
+LF_API lf_status lf_transition_run(lf_context* ctx, const lf_transition_desc* d, lf_result* r);
+
+/* OuterProductMeanGpu.run (webgpu/kernels/outer-product-mean.js:1748).
+ * out[length,length,c_z] = update, or pair + update when `residual`. */
+typedef struct lf_opm_desc {
+  int32_t sequences, length, c_m, c_outer, c_z;
+  int32_t variance, precision, residual;
+  float layer_norm_epsilon;    /* 1e-5 in the reference */
+  float normalization_epsilon; /* 1e-3 in the reference */
+  int32_t space, act_dtype;    /* act_dtype applies to `out` (the pair) */
+  const float* activations;    /* msa [sequences, length, c_m] float32 */
+  const float* mask;           /* [sequences, length] */
+  void* out;                   /* pair */
+  const lf_weights* weights;
+} lf_opm_desc;
+LF_API lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_result* r);
+
+/* Af3SingleAttentionGpu.run (webgpu/af3/trunk/single-attention.js:504) fused
+ * with the pair-logits pass that feeds it
+ * (webgpu/af3/trunk/pairformer-block.js:157-230): single += attention(single,
+ * LN(pair).W). */
+typedef struct lf_single_attention_desc {
+  int32_t tokens, channels, heads, head_dim, pair_channels;
+  int32_t precision, residual;
+  int32_t space, pair_dtype;
+  const float* single;         /* [tokens, channels] float32 */
+  const void* pair;            /* [tokens, tokens, pair_channels] */
+  const float* seq_mask;       /* [tokens] */
+  float* out;                  /* [tokens, channels] */
+  const lf_weights* weights;
+} lf_single_attention_desc;
+LF_API lf_status lf_single_attention_run(lf_context* ctx, const lf_single_attention_desc* d, lf_result* r);
+
+/* One block's worth of pair updates on a caller-owned pair, in the
+ * reference's order with each update added into the running pair:
+ * triangle out, triangle in, attention start, attention end, transition
+ * (webgpu/af2/evoformer/block.js:1575-1612 for AF2 weights;
+ * cpu/af3/trunk/pairformer.js:505-513 and webgpu/af3/trunk/pair-track.js:929
+ * for AF3 weights).  Runs blocks [first_block, first_block + n_blocks) of the
+ * `blocks` table on the same pair, which is what EvoformerStackGpu /
+ * ExtraMsaPairStackGpu / Af3PairformerStackGpu do with a resident pair
+ * (webgpu/af2/evoformer/stack.js:44-163, webgpu/af3/trunk/pairformer-block.js:290-343). */
+typedef struct lf_pair_block_weights {
+  const lf_weights* triangle_outgoing;
+  const lf_weights* triangle_incoming;
+  const lf_weights* attention_starting;
+  const lf_weights* attention_ending;
+  const lf_weights* transition;
+} lf_pair_block_weights;
+typedef struct lf_pair_stack_desc {
+  int32_t length, c_z, c_hidden, heads, transition_hidden;
+  int32_t variance, precision;
+  int32_t swap_transposed_bias;/* AF3 dialect bit; -1 for AF2 weights */
+  float epsilon;
+  int32_t space, act_dtype;
+  void* pair;                  /* updated in place */
+  const float* mask;           /* [length, length] */
+  const lf_pair_block_weights* blocks;
+  int32_t block_count, first_block, n_blocks;
+} lf_pair_stack_desc;
+LF_API lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_result* r);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOCALFOLD_PAIRSTACK_H */

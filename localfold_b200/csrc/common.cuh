@@ -1,0 +1,89 @@
+// Shared host-side plumbing of the pair-stack library: context, scratch arena,
+// resident weights, error reporting.  No torch types anywhere in this library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/localfold_pairstack.h"
+
+typedef __nv_bfloat16 bf16;
+
+struct lf_context {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  std::string error;
+  // Scratch arena: one device allocation, bump-allocated per operator call.
+  char* arena = nullptr;
+  size_t arena_bytes = 0;
+  size_t arena_used = 0;
+  size_t arena_peak = 0;
+  uint64_t launches = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int sm_count = 148;
+};
+
+// Canonical device-resident weights.  Every linear is stored (in,out) row-major
+// float32 in `f[...]`; tensor-core kernels keep extra bf16 repacks in `h[...]`.
+struct lf_weights {
+  lf_context* ctx = nullptr;
+  int kind = 0;
+  lf_weight_dims dims{};
+  std::vector<float*> f;     // named by the per-kind enums in weights.cuh
+  std::vector<void*> h;      // bf16 repacks (tensor-core path)
+  std::vector<void*> owned;  // every device allocation, for destroy
+  bool has_gate_bias = false, has_out_bias = false, has_pair_norm = false, has_pair_proj = false;
+};
+
+static inline lf_status lf_fail(lf_context* ctx, lf_status code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->error = buf;
+  return code;
+}
+
+#define LF_CUDA(ctx, expr)                                                             \
+  do {                                                                                 \
+    cudaError_t e_ = (expr);                                                           \
+    if (e_ != cudaSuccess)                                                             \
+      return lf_fail((ctx), e_ == cudaErrorMemoryAllocation ? LF_ERR_MEMORY : LF_ERR_CUDA, \
+                     "%s failed: %s", #expr, cudaGetErrorString(e_));                  \
+  } while (0)
+
+#define LF_TRY(expr)                  \
+  do {                                \
+    lf_status s_ = (expr);            \
+    if (s_ != LF_OK) return s_;       \
+  } while (0)
+
+// Bump allocation out of the arena.  Sizing happens before any kernel of the
+// call is enqueued (see Arena::plan in api.cu): the arena is never reallocated
+// while work that uses it may still be in flight on the stream.
+static inline size_t lf_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct ArenaCursor {
+  lf_context* ctx;
+  size_t offset;
+  bool dry;       // planning pass: only adds sizes up
+  template <typename T>
+  T* take(size_t count) {
+    size_t bytes = lf_align_up(count * sizeof(T), 256);
+    T* p = dry ? nullptr : reinterpret_cast<T*>(ctx->arena + offset);
+    offset += bytes;
+    return p;
+  }
+};
+
+lf_status lf_arena_ensure(lf_context* ctx, size_t bytes);
+
+static inline int lf_ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,439 @@
+// Float32 SIMT kernels: the precision-"f32" path of every operator and the
+// generic-shape path behind the tensor-core kernels.  All accumulation is
+// float32 FMA; statistics use warp-shuffle reductions.
+#pragma once
+
+#include "common.cuh"
+
+namespace simt {
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// ---------------------------------------------------------------------------
+// LayerNorm over the last axis, one warp per row.  `rows` logical rows; logical
+// row r = b*Q + i reads memory row i*batch + b when `transpose` (batch, Q > 0).
+// variance: 1 two-pass, 2 fast (E[x^2]-E[x]^2, unclamped).
+template <typename TIn>
+__global__ void layer_norm_kernel(const TIn* __restrict__ in, int64_t rows, int ch,
+                                  const float* __restrict__ gamma, const float* __restrict__ beta,
+                                  float eps, int variance, int transpose, int batch, int Q,
+                                  float* __restrict__ out) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  int64_t src = row;
+  if (transpose) { int64_t b = row / Q, i = row % Q; src = i * batch + b; }
+  const TIn* x = in + src * ch;
+  float s = 0.f, ss = 0.f;
+  for (int c = lane; c < ch; c += 32) { float v = to_f(x[c]); s += v; ss += v * v; }
+  s = warp_sum(s);
+  float mean = s / ch, var;
+  if (variance == 2) {
+    ss = warp_sum(ss);
+    var = ss / ch - mean * mean;
+  } else {
+    float acc = 0.f;
+    for (int c = lane; c < ch; c += 32) { float d = to_f(x[c]) - mean; acc += d * d; }
+    var = warp_sum(acc) / ch;
+  }
+  float inv = rsqrtf(var + eps);
+  // one Newton step: rsqrtf is 2 ulp, the parity bar is tighter than that squared error allows
+  inv = inv * (1.5f - 0.5f * (var + eps) * inv * inv);
+  float* y = out + row * ch;
+  for (int c = lane; c < ch; c += 32) y[c] = (to_f(x[c]) - mean) * inv * gamma[c] + beta[c];
+}
+
+// ---------------------------------------------------------------------------
+// Tiled SGEMM, batched over blockIdx.z:  C[m][n] = epi(sum_k A(m,k) B(k,n) + bias[n])
+//   A(m,k) = TA ? A[k*lda + m] : A[m*lda + k]
+//   B(k,n) = TB ? B[n*ldb + k] : B[k*ldb + n]
+// 64x64x16 tile, 256 threads, 4x4 micro-tile, every load and store bounds-checked.
+enum { EPI_NONE = 0, EPI_RELU = 1, EPI_SIGMOID_FROM_COL = 2 };
+
+template <bool TA, bool TB, int EPI>
+__global__ void __launch_bounds__(256)
+sgemm_kernel(int M, int N, int K, const float* __restrict__ A, int64_t lda, int64_t strideA,
+             const float* __restrict__ B, int64_t ldb, int64_t strideB, float* __restrict__ C,
+             int64_t ldc, int64_t strideC, const float* __restrict__ bias, int epi_col0) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  A += (int64_t)blockIdx.z * strideA;
+  B += (int64_t)blockIdx.z * strideB;
+  C += (int64_t)blockIdx.z * strideC;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int t = threadIdx.x;
+  const int tx = t & 15, ty = t >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int idx = t + 256 * r;
+      int m, k;
+      if (TA) { m = idx & 63; k = idx >> 6; } else { k = idx & 15; m = idx >> 4; }
+      int gm = m0 + m, gk = k0 + k;
+      float v = 0.f;
+      if (gm < M && gk < K) v = TA ? A[(int64_t)gk * lda + gm] : A[(int64_t)gm * lda + gk];
+      As[k][m] = v;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int idx = t + 256 * r;
+      int n, k;
+      if (TB) { k = idx & 15; n = idx >> 4; } else { n = idx & 63; k = idx >> 6; }
+      int gn = n0 + n, gk = k0 + k;
+      float v = 0.f;
+      if (gn < N && gk < K) v = TB ? B[(int64_t)gn * ldb + gk] : B[(int64_t)gk * ldb + gn];
+      Bs[k][n] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float v = acc[i][j] + (bias ? bias[gn] : 0.f);
+      if (EPI == EPI_RELU) v = fmaxf(v, 0.f);
+      if (EPI == EPI_SIGMOID_FROM_COL) { if (gn >= epi_col0) v = sigmoidf_(v); }
+      C[(int64_t)gm * ldc + gn] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Triangle multiplication glue.
+// p4: [pairs][4c] = (ap | ag | bp | bg).  a[h][p] = mask[p] * ap * sigmoid(ag), b likewise,
+// channel-major.  32x32 tile transpose through shared memory so both sides coalesce.
+__global__ void trimul_gate_kernel(const float* __restrict__ p4, const float* __restrict__ mask,
+                                   int64_t pairs, int c, float* __restrict__ a, float* __restrict__ b) {
+  __shared__ float ta[32][33];
+  __shared__ float tb[32][33];
+  int64_t p0 = (int64_t)blockIdx.x * 32;
+  int h0 = blockIdx.y * 32;
+  int tx = threadIdx.x, ty = threadIdx.y;   // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    int64_t p = p0 + r;
+    int h = h0 + tx;
+    float va = 0.f, vb = 0.f;
+    if (p < pairs && h < c) {
+      const float* row = p4 + p * 4 * c;
+      float m = mask[p];
+      va = row[h] * sigmoidf_(row[c + h]) * m;
+      vb = row[2 * c + h] * sigmoidf_(row[3 * c + h]) * m;
+    }
+    ta[r][tx] = va;
+    tb[r][tx] = vb;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    int h = h0 + r;
+    int64_t p = p0 + tx;
+    if (h < c && p < pairs) {
+      a[(int64_t)h * pairs + p] = ta[tx][r];
+      b[(int64_t)h * pairs + p] = tb[tx][r];
+    }
+  }
+}
+
+// LayerNorm over the hidden channel of a channel-major tensor x[h][p] -> xn[p][h].
+// One block handles 32 pairs; the tile [c][32] sits in shared memory (c <= 512).
+__global__ void center_norm_kernel(const float* __restrict__ x, int64_t pairs, int c,
+                                   const float* __restrict__ gamma, const float* __restrict__ beta,
+                                   float eps, int variance, float prescale, float* __restrict__ xn) {
+  extern __shared__ float tile[];   // [c][33]
+  int64_t p0 = (int64_t)blockIdx.x * 32;
+  int tx = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int h = w; h < c; h += nw) {
+    int64_t p = p0 + tx;
+    tile[h * 33 + tx] = p < pairs ? x[(int64_t)h * pairs + p] * prescale : 0.f;
+  }
+  __syncthreads();
+  // warp w normalises pairs w, w+nw, ...
+  for (int r = w; r < 32; r += nw) {
+    int64_t p = p0 + r;
+    if (p >= pairs) continue;
+    float s = 0.f, ss = 0.f;
+    for (int h = tx; h < c; h += 32) { float v = tile[h * 33 + r]; s += v; ss += v * v; }
+    s = warp_sum(s);
+    float mean = s / c, var;
+    if (variance == 2) { ss = warp_sum(ss); var = ss / c - mean * mean; }
+    else {
+      float acc = 0.f;
+      for (int h = tx; h < c; h += 32) { float d = tile[h * 33 + r] - mean; acc += d * d; }
+      var = warp_sum(acc) / c;
+    }
+    float inv = rsqrtf(var + eps);
+    inv = inv * (1.5f - 0.5f * (var + eps) * inv * inv);
+    for (int h = tx; h < c; h += 32) xn[p * c + h] = (tile[h * 33 + r] - mean) * inv * gamma[h] + beta[h];
+  }
+}
+
+// out[dst(r)][c] = (resid ? resid[dst(r)][c] : 0) + proj[r][c] * (gate ? sigmoid(gate[r][c]) : 1)
+// dst(r) follows the transposed-orientation rule of the attention operator.
+template <typename TAct>
+__global__ void finish_kernel(const float* __restrict__ proj, const float* __restrict__ gate,
+                              const TAct* __restrict__ resid, int64_t rows, int ch, int transpose,
+                              int batch, int Q, TAct* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = rows * ch;
+  if (idx >= total) return;
+  int64_t r = idx / ch;
+  int c = (int)(idx % ch);
+  int64_t dst = r;
+  if (transpose) { int64_t b = r / Q, i = r % Q; dst = i * batch + b; }
+  float v = proj[idx];
+  if (gate) v *= sigmoidf_(gate[idx]);
+  if (resid) v += to_f(resid[dst * ch + c]);
+  out[dst * ch + c] = from_f<TAct>(v);
+}
+
+template <typename TIn>
+__global__ void to_float_kernel(const TIn* __restrict__ in, int64_t n, float* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = to_f(in[i]);
+}
+
+// ---------------------------------------------------------------------------
+// Pair bias: out[h][dst(p)] = LN(pair[p,:]) . W[:,h] for p = i*Q + j, dst = j*Q+i if swap.
+// One warp per pair row; `normalized` != 0 skips the LayerNorm (input already normalised).
+template <typename TIn>
+__global__ void pair_bias_kernel(const TIn* __restrict__ pair, int Q, int ch, int heads,
+                                 const float* __restrict__ gamma, const float* __restrict__ beta,
+                                 const float* __restrict__ w, float eps, int variance, int normalized,
+                                 int swap, float* __restrict__ out) {
+  int lane = threadIdx.x & 31;
+  int64_t pairs = (int64_t)Q * Q;
+  int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (p >= pairs) return;
+  const TIn* x = pair + p * ch;
+  float mean = 0.f, inv = 1.f;
+  if (!normalized) {
+    float s = 0.f, ss = 0.f;
+    for (int c = lane; c < ch; c += 32) { float v = to_f(x[c]); s += v; ss += v * v; }
+    s = warp_sum(s);
+    mean = s / ch;
+    float var;
+    if (variance == 2) { ss = warp_sum(ss); var = ss / ch - mean * mean; }
+    else {
+      float acc = 0.f;
+      for (int c = lane; c < ch; c += 32) { float d = to_f(x[c]) - mean; acc += d * d; }
+      var = warp_sum(acc) / ch;
+    }
+    inv = rsqrtf(var + eps);
+    inv = inv * (1.5f - 0.5f * (var + eps) * inv * inv);
+  }
+  int64_t dst = p;
+  if (swap) { int64_t i = p / Q, j = p % Q; dst = j * Q + i; }
+  for (int h = 0; h < heads; ++h) {
+    float acc = 0.f;
+    for (int c = lane; c < ch; c += 32) {
+      float v = to_f(x[c]);
+      if (!normalized) v = (v - mean) * inv * gamma[c] + beta[c];
+      acc = fmaf(v, w[c * heads + h], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[(int64_t)h * pairs + dst] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Gated attention core, float32, online softmax.  One warp per query, 8 queries
+// per block, key/value tiles of 32 rows staged in shared memory.
+//   qkvg: [rows][4*HD] = (q | k | v | sigmoid(gate)) in logical row order
+//   bias: [H][Q][Q] or null; mask: indexed b*Q+j, or j*batch+b when transpose
+//   mask_mode 0: logit += 1e9*(m-1); 1: logit += (m > 0 ? 0 : -1e9)
+//   clamp: limit the logit to +-1e8 after all terms are added
+//   out: [rows][HD] = softmax(.) v * gate
+__global__ void __launch_bounds__(256)
+attention_kernel(const float* __restrict__ qkvg, const float* __restrict__ bias,
+                 const float* __restrict__ mask, int batch, int Q, int heads, int d,
+                 int transpose, int mask_mode, int clamp, float scale, float* __restrict__ out) {
+  extern __shared__ float sm[];
+  const int HD = heads * d;
+  const int ld = 4 * HD;
+  float* Ks = sm;                    // [32][d+1]
+  float* Vs = Ks + 32 * (d + 1);     // [32][d+1]
+  float* Qs = Vs + 32 * (d + 1);     // [8][d]
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int qi = blockIdx.x * 8 + w;
+  const bool active = qi < Q;
+  const int64_t rowbase = (int64_t)b * Q;
+  if (active) for (int e = lane; e < d; e += 32) Qs[w * d + e] = qkvg[(rowbase + qi) * ld + h * d + e];
+  float run_max = -INFINITY, run_sum = 0.f, o0 = 0.f, o1 = 0.f;
+  for (int j0 = 0; j0 < Q; j0 += 32) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 32 * d; idx += 256) {
+      int j = idx / d, e = idx % d;
+      float kv = 0.f, vv = 0.f;
+      if (j0 + j < Q) {
+        const float* row = qkvg + (rowbase + j0 + j) * ld + h * d + e;
+        kv = row[HD];
+        vv = row[2 * HD];
+      }
+      Ks[j * (d + 1) + e] = kv;
+      Vs[j * (d + 1) + e] = vv;
+    }
+    __syncthreads();
+    if (!active) continue;
+    int j = j0 + lane;
+    float logit = -INFINITY;
+    if (j < Q) {
+      float dot = 0.f;
+      for (int e = 0; e < d; ++e) dot = fmaf(Qs[w * d + e], Ks[lane * (d + 1) + e], dot);
+      float m = mask[transpose ? (int64_t)j * batch + b : rowbase + j];
+      logit = dot * scale;
+      logit += mask_mode == 0 ? 1e9f * (m - 1.0f) : (m > 0.f ? 0.f : -1e9f);
+      if (bias) logit += bias[((int64_t)h * Q + qi) * Q + j];
+      if (clamp) logit = fminf(fmaxf(logit, -1e8f), 1e8f);
+    }
+    float tile_max = warp_max(logit);
+    float new_max = fmaxf(run_max, tile_max);
+    float corr = __expf(run_max - new_max);   // exp(-inf) = 0 on the first tile
+    float p = j < Q ? expf(logit - new_max) : 0.f;
+    run_sum = run_sum * corr + warp_sum(p);
+    run_max = new_max;
+    o0 *= corr; o1 *= corr;
+    int lim = min(32, Q - j0);
+    for (int jj = 0; jj < lim; ++jj) {
+      float pj = __shfl_sync(0xffffffffu, p, jj);
+      if (lane < d) o0 = fmaf(pj, Vs[jj * (d + 1) + lane], o0);
+      if (lane + 32 < d) o1 = fmaf(pj, Vs[jj * (d + 1) + lane + 32], o1);
+    }
+  }
+  if (!active) return;
+  const float* grow = qkvg + (rowbase + qi) * ld + 3 * HD + h * d;
+  float* orow = out + (rowbase + qi) * HD + h * d;
+  if (lane < d) orow[lane] = o0 / run_sum * grow[lane];
+  if (lane + 32 < d) orow[lane + 32] = o1 / run_sum * grow[lane + 32];
+}
+
+// ---------------------------------------------------------------------------
+// Transition glue: SwiGLU over a [rows][2*inter] tensor, gate half first.
+__global__ void swiglu_kernel(const float* __restrict__ wide, int64_t rows, int inter, float* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * inter) return;
+  int64_t r = idx / inter;
+  int i = (int)(idx % inter);
+  float g = wide[r * 2 * inter + i];
+  float v = wide[r * 2 * inter + inter + i];
+  out[idx] = g * sigmoidf_(g) * v;
+}
+
+// ---------------------------------------------------------------------------
+// Outer product mean glue.
+// rows [S*N][c]: multiply every row by its mask value.
+__global__ void mask_rows_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ mask,
+                                 int64_t rows, int c) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * c) return;
+  float m = mask[idx / c];
+  a[idx] *= m;
+  b[idx] *= m;
+}
+
+// outer: [(i - i0)*c + a][j*c + b] for i in [i0, i0+ni); out[i][j][z] =
+// (sum_ab outer * wout[(a*c+b)][z] + bout[z]) / (eps + count(i,j)), + resid.
+// One block per (i, group of JT columns j); thread z loops over the c*c products.
+template <typename TAct, int JT>
+__global__ void opm_output_kernel(const float* __restrict__ outer, const float* __restrict__ wout,
+                                  const float* __restrict__ bout, const float* __restrict__ mask,
+                                  int S, int N, int c, int cz, int i0, float norm_eps,
+                                  int bias_after_norm, const TAct* __restrict__ resid,
+                                  TAct* __restrict__ out) {
+  extern __shared__ float sm[];     // [JT][c*c] + counts[JT]
+  const int cc = c * c;
+  float* tile = sm;
+  float* counts = sm + JT * cc;
+  const int i = i0 + blockIdx.y;
+  const int j0 = blockIdx.x * JT;
+  const int64_t ldo = (int64_t)N * c;
+  for (int idx = threadIdx.x; idx < JT * cc; idx += blockDim.x) {
+    int jj = idx / cc, ab = idx % cc, a = ab / c, b2 = ab % c;
+    int j = j0 + jj;
+    tile[idx] = j < N ? outer[((int64_t)(i - i0) * c + a) * ldo + (int64_t)j * c + b2] : 0.f;
+  }
+  if (threadIdx.x < JT) {
+    int j = j0 + threadIdx.x;
+    float cnt = 0.f;
+    if (j < N) for (int s = 0; s < S; ++s) cnt += mask[(int64_t)s * N + i] * mask[(int64_t)s * N + j];
+    counts[threadIdx.x] = cnt;
+  }
+  __syncthreads();
+  for (int z = threadIdx.x; z < cz; z += blockDim.x) {
+    float acc[JT];
+#pragma unroll
+    for (int jj = 0; jj < JT; ++jj) acc[jj] = 0.f;
+    for (int ab = 0; ab < cc; ++ab) {
+      float wv = wout[(int64_t)ab * cz + z];
+#pragma unroll
+      for (int jj = 0; jj < JT; ++jj) acc[jj] = fmaf(tile[jj * cc + ab], wv, acc[jj]);
+    }
+#pragma unroll
+    for (int jj = 0; jj < JT; ++jj) {
+      int j = j0 + jj;
+      if (j >= N) continue;
+      float v;
+      if (bias_after_norm) v = acc[jj] / fmaxf(counts[jj], 1.0f) + bout[z];
+      else v = (acc[jj] + bout[z]) / (norm_eps + counts[jj]);
+      int64_t o = ((int64_t)i * N + j) * cz + z;
+      if (resid) v += to_f(resid[o]);
+      out[o] = from_f<TAct>(v);
+    }
+  }
+}
+
+// int5 decode: one thread per value.  value = code*scale + zero.
+__global__ void int5_decode_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
+                                   const __half* __restrict__ zeros, int64_t elements, int block,
+                                   float* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= elements) return;
+  int64_t g = i / block;
+  int within = (int)(i % block);
+  int bit = within * 5;
+  const uint8_t* base = codes + g * (block * 5 / 8);
+  unsigned two = base[bit >> 3] | ((unsigned)base[(bit >> 3) + 1] << 8);
+  unsigned code = (two >> (bit & 7)) & 31u;
+  out[i] = fmaf((float)code, __half2float(scales[g]), __half2float(zeros[g]));
+}
+
+}  // namespace simt

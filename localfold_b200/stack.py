@@ -1,0 +1,212 @@
+"""Block and stack runners: the order and residual wiring of the pair stack.
+
+Mirrors ``EvoformerBlockGpu`` / ``EvoformerStackGpu`` / ``ExtraMsaPairStackGpu``
+(``webgpu/af2/evoformer/block.js:1783-1824``, ``webgpu/af2/evoformer/stack.js:44,163``)
+and ``Af3PairformerStackGpu`` (``webgpu/af3/trunk/pairformer-block.js:246-343``).
+Every update is added into the running pair, which stays resident on the device
+for the whole stack (``pairTensor`` / ``pairBuffer`` in the reference).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from . import _native as nat
+from .operators import (AttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, OuterProductMeanGpu,
+                        PreparedWeights, TransitionGpu, _Buffer, _device, _precision, _variance,
+                        SINGLE_ATTENTION_AF3_ORDER, TRANSITION_AF3_ORDER, TRANSITION_WEIGHT_ORDER,
+                        prepare_attention_weights, prepare_grid_attention_weights,
+                        prepare_triangle_weights)
+
+
+class PreparedPairBlock:
+    """Resident weights of the five pair updates of one block."""
+
+    def __init__(self, device, w, c_z, c_hidden):
+        self.device = device
+        af3 = "pairAttention1" in w
+        self.af3 = af3
+        self.tri_out = prepare_triangle_weights(device, w["triangleMultiplicationOutgoing"], c_z, c_hidden)
+        self.tri_in = prepare_triangle_weights(device, w["triangleMultiplicationIncoming"], c_z, c_hidden)
+        if af3:
+            self.att_start = prepare_grid_attention_weights(device, w["pairAttention1"], c_z)
+            self.att_end = prepare_grid_attention_weights(device, w["pairAttention2"], c_z)
+            self.heads = int(w["pairAttention1"]["heads"])
+            t = w["pairTransition"]
+            self.transition_hidden = np.asarray(t["transition2"]).shape[0]
+            self.transition = PreparedWeights(device, nat.WEIGHTS_TRANSITION_AF3,
+                                              {"channels": c_z, "hidden": self.transition_hidden},
+                                              [t[k] for k in TRANSITION_AF3_ORDER])
+        else:
+            s, e = w["triangleAttentionStarting"], w["triangleAttentionEnding"]
+            self.heads = int(s["heads"])
+            self.att_start = prepare_attention_weights(device, s["attention"], c_z, s["heads"],
+                                                       dict(s["pairBias"], source="normalized-input"))
+            self.att_end = prepare_attention_weights(device, e["attention"], c_z, e["heads"],
+                                                     dict(e["pairBias"], source="normalized-input"))
+            t = w["pairTransition"]
+            self.transition_hidden = np.asarray(t["firstBias"]).size
+            self.transition = PreparedWeights(device, nat.WEIGHTS_TRANSITION_AF2,
+                                              {"channels": c_z, "hidden": self.transition_hidden},
+                                              [t[k] for k in TRANSITION_WEIGHT_ORDER])
+
+    def struct(self):
+        return nat.PairBlockWeights(self.tri_out.handle, self.tri_in.handle, self.att_start.handle,
+                                    self.att_end.handle, self.transition.handle)
+
+    def close(self):
+        for w in (self.tri_out, self.tri_in, self.att_start, self.att_end, self.transition):
+            w.close()
+
+
+class PairStackGpu:
+    """The five pair updates of ``n_blocks`` blocks on a resident pair
+    (``ExtraMsaPairStackGpu`` without its OuterProductMean:
+    ``webgpu/af2/evoformer/block.js:1663-1713``; ``encodePairTrack``:
+    ``webgpu/af3/trunk/pair-track.js:929``)."""
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+        self.blocks = []
+        self.shape = None
+
+    def prepare(self, block_weights, c_z, c_hidden):
+        self.close()
+        self.blocks = [w if isinstance(w, PreparedPairBlock) else PreparedPairBlock(self.device, w, c_z, c_hidden)
+                       for w in block_weights]
+        self.shape = (c_z, c_hidden)
+        self._table = (nat.PairBlockWeights * len(self.blocks))(*[b.struct() for b in self.blocks])
+        return self
+
+    def run(self, pair, mask, options=None, first_block=0, n_blocks=None, dialect=None):
+        """Updates ``pair`` (device tensor: in place; numpy: returns a new array)."""
+        opts = options or {}
+        dev = self.device
+        c_z, c_hidden = self.shape
+        af3 = self.blocks[0].af3
+        swap = -1
+        if af3:
+            if dialect is None or dialect.get("swapTransposedBias") not in (True, False):
+                raise ValueError("dialect.swapTransposedBias has no default")
+            swap = 1 if dialect["swapTransposedBias"] else 0
+        p = _Buffer(pair)
+        m = _Buffer(mask)
+        n = int(round((p.count // c_z) ** 0.5))
+        if n * n * c_z != p.count:
+            raise nat.RangeError(f"pair has {p.count} values; expected length*length*{c_z}")
+        if m.count != n * n:
+            raise nat.RangeError(f"mask has {m.count} values; expected {n * n}")
+        if p.is_device:
+            target, output = p, pair
+        else:
+            output = np.array(pair, np.float32, copy=True).reshape(n, n, c_z)
+            target = _Buffer(output)
+        count = len(self.blocks) - first_block if n_blocks is None else n_blocks
+        desc = nat.PairStackDesc(n, c_z, c_hidden, self.blocks[0].heads, self.blocks[0].transition_hidden,
+                                 _variance(opts, "fast" if af3 else "two-pass"), _precision(opts), swap,
+                                 float(opts.get("epsilon") or 1e-5),
+                                 nat.SPACE_DEVICE if p.is_device else nat.SPACE_HOST, target.dtype,
+                                 target.ptr, m.ptr, self._table, len(self.blocks), first_block, count)
+        res = nat.Result()
+        dev.check(dev.lib.lf_pair_stack_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
+        return {"pair": output, "elapsedMilliseconds": float(res.elapsed_ms),
+                "memory": {"peakBytes": int(res.peak_bytes)}, "launches": int(res.launches), "blocks": count}
+
+    def close(self):
+        for b in self.blocks:
+            b.close()
+        self.blocks = []
+
+
+class EvoformerBlockGpu:
+    """One whole AF2 Evoformer block (``webgpu/af2/evoformer/block.js:1536-1613,1783-1824``):
+    msa += rowAttention(msa, pair); msa += columnAttention(msa); msa += transition(msa);
+    pair += outerProductMean(msa); then the five pair updates."""
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+
+    def run(self, input, options=None):
+        opts = dict(options or {})
+        dev = self.device
+        S, n, cm, cz = (int(input[k]) for k in ("sequences", "length", "cM", "cZ"))
+        co, ch = int(input["cOuter"]), int(input["triangleHidden"])
+        w = input["weights"]
+        msa = np.array(input["msa"], np.float32, copy=True).reshape(S, n, cm)
+        pair = np.array(input["pair"], np.float32, copy=True).reshape(n, n, cz)
+        msa_mask, pair_mask = input["msaMask"], input["pairMask"]
+        elapsed = 0.0
+        launches = 0
+        row = w["msaRowAttention"]
+        sub = dict(opts, residual=True)
+        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": S, "queryLength": n,
+                                   "channels": cm, "heads": row["heads"], "weights": row["attention"],
+                                   "pairBias": dict(row["pairBias"], source="separate", activations=pair,
+                                                    channels=cz)}, sub)
+        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        col = w["msaColumnAttention"]
+        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": n, "queryLength": S,
+                                   "channels": cm, "heads": col["heads"], "transpose": True,
+                                   "weights": col["attention"]}, sub)
+        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        t = w["msaTransition"]
+        r = TransitionGpu(dev).run({"activations": msa, "rows": S * n, "channels": cm,
+                                    "hiddenChannels": np.asarray(t["firstBias"]).size, "weights": t}, sub)
+        msa = r["output"].reshape(S, n, cm); elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        r = OuterProductMeanGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
+                                          "cM": cm, "cOuter": co, "cZ": cz, "weights": w["outerProductMean"]},
+                                         sub, out=pair)
+        pair = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        stack = PairStackGpu(dev).prepare([w], cz, ch)
+        try:
+            r = stack.run(pair, pair_mask, opts)
+        finally:
+            dev.synchronize()
+            stack.close()
+        elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        return {"msa": msa, "pair": r["pair"], "elapsedMilliseconds": elapsed, "memory": r["memory"],
+                "launches": launches}
+
+
+class Af3PairformerStackGpu:
+    """``Af3PairformerStackGpu.run(state, blocks, dialect, options)``
+    (``webgpu/af3/trunk/pairformer-block.js:290-343``): per block the five pair
+    updates, then single += singleAttention(single, pairLogits(pair)) and
+    single += transition(single) (``cpu/af3/trunk/pairformer.js:505-539``)."""
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+
+    def run(self, state, blocks, dialect, options=None):
+        if dialect is None or dialect.get("swapTransposedBias") not in (True, False):
+            raise ValueError("dialect.swapTransposedBias has no default")
+        opts = dict(options or {})
+        dev = self.device
+        n = int(state["tokens"])
+        cz, cs = int(blocks[0]["pairChannels"]), int(blocks[0]["singleChannels"])
+        first = int(opts.get("firstBlock", 0))
+        pair = np.array(state["pair"], np.float32, copy=True).reshape(n, n, cz)
+        single = None if state.get("single") is None else np.array(state["single"], np.float32, copy=True).reshape(n, cs)
+        stack = PairStackGpu(dev).prepare(blocks, cz, cz)
+        elapsed, launches = 0.0, 0
+        sub = {"precision": opts.get("precision", "f32"), "residual": True}
+        try:
+            for b in range(first, len(blocks)):
+                r = stack.run(pair, state["pairMask"], opts, first_block=b, n_blocks=1, dialect=dialect)
+                pair = r["pair"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+                if single is not None:
+                    w = blocks[b]
+                    r = Af3SingleAttentionGpu(dev).run(single, pair, state["seqMask"],
+                                                       {"n": n, "channels": cs, "pairChannels": cz}, w, sub)
+                    single = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+                    r = Af3TransitionGpu(dev).run(single, {"rows": n, "channels": cs, "factor": 4},
+                                                  w["singleTransition"], sub)
+                    single = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+                if opts.get("onBlockDone"):
+                    opts["onBlockDone"](b)
+        finally:
+            dev.synchronize()
+            stack.close()
+        return {"pair": pair, "single": single, "elapsedMilliseconds": elapsed,
+                "memory": {"peakBytes": 0}, "launches": launches}
