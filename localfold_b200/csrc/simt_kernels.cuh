@@ -77,7 +77,7 @@ sgemm_kernel(int M, int N, int K, const float* __restrict__ A, int64_t lda, int6
   A += (int64_t)blockIdx.z * strideA;
   B += (int64_t)blockIdx.z * strideB;
   C += (int64_t)blockIdx.z * strideC;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
   const int t = threadIdx.x;
   const int tx = t & 15, ty = t >> 4;
   float acc[4][4];
