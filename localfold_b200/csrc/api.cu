@@ -56,6 +56,7 @@ lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out) 
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device_ordinal) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
   tc::configure_once();
+  if (cudaMalloc(&ctx->tc_status, 16) == cudaSuccess) cudaMemset(ctx->tc_status, 0, 16);
   *out = ctx;
   return LF_OK;
 }
@@ -65,6 +66,7 @@ void lf_context_destroy(lf_context* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->arena) cudaFree(ctx->arena);
+  if (ctx->tc_status) cudaFree(ctx->tc_status);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -76,7 +78,7 @@ const char* lf_last_error(const lf_context* ctx) { return ctx ? ctx->error.c_str
 lf_status lf_context_synchronize(lf_context* ctx) {
   if (!ctx) return LF_ERR_ARGUMENT;
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return LF_OK;
+  return tc::check_status(ctx);
 }
 
 uint64_t lf_context_launch_count(const lf_context* ctx) { return ctx ? ctx->launches : 0; }
@@ -103,10 +105,6 @@ void lf_context_release_scratch(lf_context* ctx) {
 
 namespace {
 
-enum { TRI_LN_G, TRI_LN_B, TRI_W4, TRI_B4, TRI_LNO_G, TRI_LNO_B, TRI_WZ, TRI_BZ, TRI_WG, TRI_BG, TRI_COUNT };
-enum { ATT_LN_G, ATT_LN_B, ATT_W4, ATT_B4, ATT_WO, ATT_BO, ATT_PLN_G, ATT_PLN_B, ATT_WB, ATT_COUNT };
-enum { TRN_LN_G, TRN_LN_B, TRN_W1, TRN_B1, TRN_W2, TRN_B2, TRN_COUNT };
-enum { OPM_LN_G, OPM_LN_B, OPM_WL, OPM_BL, OPM_WR, OPM_BR, OPM_WOUT, OPM_BOUT, OPM_COUNT };
 
 typedef std::vector<float> hvec;
 
@@ -470,8 +468,8 @@ void tri_f32(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
          f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
   sgemm(ctx, cur, false, false, simt::EPI_NONE, (int)P, 4 * c, cz, zn, cz, 0, f[TRI_W4], 4 * c, 0, p4, 4 * c, 0, f[TRI_B4], 0, 1);
-  LAUNCH(ctx, cur, simt::trimul_gate_kernel, dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
-         a.mask, P, c, ga, gb);
+  LAUNCH(ctx, cur, (simt::trimul_gate_kernel<float>), dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
+         a.mask, P, c, n, n, ga, gb);
   if (!a.incoming)   // x[i][j] = sum_k a[i][k] b[j][k]
     sgemm(ctx, cur, false, true, 0, n, n, n, ga, n, P, gb, n, P, x, n, P, nullptr, 0, c);
   else               // x[i][j] = sum_k b[k][i] a[k][j]
@@ -480,7 +478,7 @@ void tri_f32(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   float* xn = p4;
   float* proj = p4 + P * c;
   float* gate = p4 + P * c + P * cz;   // needs 4c >= c + 2cz: checked by the caller
-  LAUNCH(ctx, cur, simt::center_norm_kernel, lf_ceil_div(P, 32), 256, (size_t)c * 33 * sizeof(float), x, P, c,
+  LAUNCH(ctx, cur, (simt::center_norm_kernel<float>), lf_ceil_div(P, 32), 256, (size_t)c * 33 * sizeof(float), x, P, c, n, n,
          f[TRI_LNO_G], f[TRI_LNO_B], a.eps, a.variance, a.divide ? 1.0f / n : 1.0f, xn);
   sgemm(ctx, cur, false, false, 0, (int)P, cz, c, xn, c, 0, f[TRI_WZ], cz, 0, proj, cz, 0, f[TRI_BZ], 0, 1);
   sgemm(ctx, cur, false, false, 0, (int)P, cz, cz, zn, cz, 0, f[TRI_WG], cz, 0, gate, cz, 0, f[TRI_BG], 0, 1);
@@ -488,10 +486,44 @@ void tri_f32(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
          a.residual ? (const T*)a.z : (const T*)nullptr, P, cz, 0, 1, 1, (T*)a.out);
 }
 
+// 16-bit path: float32 LayerNorm statistics and gates, fp16 operands a, b, x with
+// float32 accumulation on the tensor cores for the contraction.
+template <typename T>
+lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
+  const int64_t P = (int64_t)a.n * a.n;
+  const int cz = a.cz, c = a.c, n = a.n;
+  const int ld = (n + 7) / 8 * 8;           // TMA row strides are multiples of 16 bytes
+  const int64_t plane = (int64_t)n * ld;
+  const auto& f = a.w->f;
+  float* zn = cur.take<float>(P * cz);
+  float* p4 = cur.take<float>(P * 4 * c);
+  op16* ga = cur.take<op16>(plane * c);
+  op16* gb = cur.take<op16>(plane * c);
+  op16* x = cur.take<op16>(plane * c);
+  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
+         f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
+  sgemm(ctx, cur, false, false, simt::EPI_NONE, (int)P, 4 * c, cz, zn, cz, 0, f[TRI_W4], 4 * c, 0, p4, 4 * c, 0, f[TRI_B4], 0, 1);
+  LAUNCH(ctx, cur, (simt::trimul_gate_kernel<op16>), dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
+         a.mask, P, c, n, ld, ga, gb);
+  // x is stored as fp16 scaled by a power of two near 1/sqrt(n) so that sums over n terms
+  // stay far from the fp16 limits; the centre LayerNorm undoes the scale exactly.
+  const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
+  LF_TRY(tc::contract(ctx, cur, ga, gb, x, n, ld, c, a.incoming, xscale));
+  float* xn = p4;
+  float* proj = p4 + P * c;
+  float* gate = p4 + P * c + P * cz;
+  LAUNCH(ctx, cur, (simt::center_norm_kernel<op16>), lf_ceil_div(P, 32), 256, (size_t)c * 33 * sizeof(float), x, P, c, n, ld,
+         f[TRI_LNO_G], f[TRI_LNO_B], a.eps, a.variance, (a.divide ? 1.0f / n : 1.0f) / xscale, xn);
+  sgemm(ctx, cur, false, false, 0, (int)P, cz, c, xn, c, 0, f[TRI_WZ], cz, 0, proj, cz, 0, f[TRI_BZ], 0, 1);
+  sgemm(ctx, cur, false, false, 0, (int)P, cz, cz, zn, cz, 0, f[TRI_WG], cz, 0, gate, cz, 0, f[TRI_BG], 0, 1);
+  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(P * cz, 256), 256, 0, proj, gate,
+         a.residual ? (const T*)a.z : (const T*)nullptr, P, cz, 0, 1, 1, (T*)a.out);
+  return LF_OK;
+}
+
 lf_status tri_dispatch(lf_context* ctx, ArenaCursor& cur, const TriArgs& a, int precision) {
-  if (precision == LF_PRECISION_BF16 && tc::triangle_supported(a.n, a.cz, a.c)) {
-    return tc::triangle_run(ctx, cur, a.n, a.cz, a.c, a.incoming, a.variance, a.eps, a.residual, a.divide,
-                            a.act_dtype, a.z, a.mask, a.out, a.w);
+  if (precision == LF_PRECISION_BF16 && tc::contract_supported(a.n, a.c)) {
+    return a.act_dtype == LF_DTYPE_BF16 ? tri_bf16<bf16>(ctx, cur, a) : tri_bf16<float>(ctx, cur, a);
   }
   if (a.act_dtype == LF_DTYPE_BF16) tri_f32<bf16>(ctx, cur, a); else tri_f32<float>(ctx, cur, a);
   return LF_OK;
@@ -545,10 +577,7 @@ void att_f32(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
 }
 
 lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int precision) {
-  if (precision == LF_PRECISION_BF16 && tc::attention_supported(a.batch, a.Q, a.ch, a.heads, a.d, a.bias_mode)) {
-    return tc::attention_run(ctx, cur, a.batch, a.Q, a.ch, a.heads, a.d, a.transpose, a.variance, a.eps, a.residual,
-                             a.bias_mode, a.bias_swap, a.mask_mode, a.clamp, a.act_dtype, a.act, a.mask, a.out, a.w);
-  }
+  (void)precision;
   if (a.act_dtype == LF_DTYPE_BF16) att_f32<bf16>(ctx, cur, a); else att_f32<float>(ctx, cur, a);
   return LF_OK;
 }
@@ -584,10 +613,7 @@ void trn_f32(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
 }
 
 lf_status trn_dispatch(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a, int precision) {
-  if (precision == LF_PRECISION_BF16 && tc::transition_supported(a.ch, a.hidden, a.swiglu)) {
-    return tc::transition_run(ctx, cur, a.rows, a.ch, a.hidden, a.swiglu, a.variance, a.eps, a.residual, a.act_dtype,
-                              a.act, a.out, a.w);
-  }
+  (void)precision;
   if (a.act_dtype == LF_DTYPE_BF16) trn_f32<bf16>(ctx, cur, a); else trn_f32<float>(ctx, cur, a);
   return LF_OK;
 }
@@ -609,6 +635,7 @@ lf_status run_with_arena(lf_context* ctx, lf_result* r, bool timed, F body) {
     cudaEventRecord(ctx->ev1, ctx->stream);
     LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
+    LF_TRY(tc::check_status(ctx));
   }
   LF_CUDA(ctx, cudaGetLastError());
   if (r) { r->elapsed_ms = ms; r->peak_bytes = ctx->arena_peak; r->launches = (uint32_t)(ctx->launches - before); }

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -14,6 +15,10 @@
 #include "../../include/localfold_pairstack.h"
 
 typedef __nv_bfloat16 bf16;
+// Operand type of the tensor-core kernels: fp16 (11-bit significand) for the bounded
+// intermediates (normalised activations, gated projections, probabilities); products
+// accumulate in float32.  The pair stream itself is float32 or bf16.
+typedef __half op16;
 
 struct lf_context {
   int device = 0;
@@ -28,7 +33,14 @@ struct lf_context {
   uint64_t launches = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int sm_count = 148;
+  void* tc_status = nullptr;   // device word the tensor-core kernels set when a bounded wait expires
 };
+
+// Slots of lf_weights::f per operator kind.
+enum { TRI_LN_G, TRI_LN_B, TRI_W4, TRI_B4, TRI_LNO_G, TRI_LNO_B, TRI_WZ, TRI_BZ, TRI_WG, TRI_BG, TRI_COUNT };
+enum { ATT_LN_G, ATT_LN_B, ATT_W4, ATT_B4, ATT_WO, ATT_BO, ATT_PLN_G, ATT_PLN_B, ATT_WB, ATT_COUNT };
+enum { TRN_LN_G, TRN_LN_B, TRN_W1, TRN_B1, TRN_W2, TRN_B2, TRN_COUNT };
+enum { OPM_LN_G, OPM_LN_B, OPM_WL, OPM_BL, OPM_WR, OPM_BR, OPM_WOUT, OPM_BOUT, OPM_COUNT };
 
 // Canonical device-resident weights.  Every linear is stored (in,out) row-major
 // float32 in `f[...]`; tensor-core kernels keep extra bf16 repacks in `h[...]`.

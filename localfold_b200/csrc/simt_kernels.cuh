@@ -9,9 +9,11 @@ namespace simt {
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
 template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -141,9 +143,11 @@ sgemm_kernel(int M, int N, int K, const float* __restrict__ A, int64_t lda, int6
 // ---------------------------------------------------------------------------
 // Triangle multiplication glue.
 // p4: [pairs][4c] = (ap | ag | bp | bg).  a[h][p] = mask[p] * ap * sigmoid(ag), b likewise,
-// channel-major.  32x32 tile transpose through shared memory so both sides coalesce.
+// channel-major with row stride ld >= n (plane = n*ld elements).  32x32 tile transpose
+// through shared memory so both sides coalesce.
+template <typename TOut>
 __global__ void trimul_gate_kernel(const float* __restrict__ p4, const float* __restrict__ mask,
-                                   int64_t pairs, int c, float* __restrict__ a, float* __restrict__ b) {
+                                   int64_t pairs, int c, int n, int ld, TOut* __restrict__ a, TOut* __restrict__ b) {
   __shared__ float ta[32][33];
   __shared__ float tb[32][33];
   int64_t p0 = (int64_t)blockIdx.x * 32;
@@ -167,15 +171,17 @@ __global__ void trimul_gate_kernel(const float* __restrict__ p4, const float* __
     int h = h0 + r;
     int64_t p = p0 + tx;
     if (h < c && p < pairs) {
-      a[(int64_t)h * pairs + p] = ta[tx][r];
-      b[(int64_t)h * pairs + p] = tb[tx][r];
+      int64_t o = ((int64_t)h * n + p / n) * ld + p % n;
+      a[o] = from_f<TOut>(ta[tx][r]);
+      b[o] = from_f<TOut>(tb[tx][r]);
     }
   }
 }
 
-// LayerNorm over the hidden channel of a channel-major tensor x[h][p] -> xn[p][h].
+// LayerNorm over the hidden channel of a channel-major tensor x[h][i][ld] -> xn[p][h].
 // One block handles 32 pairs; the tile [c][32] sits in shared memory (c <= 512).
-__global__ void center_norm_kernel(const float* __restrict__ x, int64_t pairs, int c,
+template <typename TIn>
+__global__ void center_norm_kernel(const TIn* __restrict__ x, int64_t pairs, int c, int n, int ld,
                                    const float* __restrict__ gamma, const float* __restrict__ beta,
                                    float eps, int variance, float prescale, float* __restrict__ xn) {
   extern __shared__ float tile[];   // [c][33]
@@ -183,7 +189,7 @@ __global__ void center_norm_kernel(const float* __restrict__ x, int64_t pairs, i
   int tx = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int h = w; h < c; h += nw) {
     int64_t p = p0 + tx;
-    tile[h * 33 + tx] = p < pairs ? x[(int64_t)h * pairs + p] * prescale : 0.f;
+    tile[h * 33 + tx] = p < pairs ? to_f(x[((int64_t)h * n + p / n) * ld + p % n]) * prescale : 0.f;
   }
   __syncthreads();
   // warp w normalises pairs w, w+nw, ...

@@ -1,23 +1,250 @@
+// tcgen05 / TMEM / TMA kernels for sm_100a.
 #include "tc_kernels.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+#include "tc05.cuh"
 
 namespace tc {
 
-void configure_once() {}
+using namespace tc05;
+
+// ---------------------------------------------------------------------------
+// host helpers
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_once;
+
+void configure_once();
+
+static lf_status make_map_f16_3d(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1,
+                                  uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
+                                  uint32_t b1) {
+  if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LF_OK;
+}
+
+lf_status check_status(lf_context* ctx) {
+  if (!ctx->tc_status) return LF_OK;
+  Status st;
+  if (cudaMemcpy(&st, ctx->tc_status, sizeof st, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return lf_fail(ctx, LF_ERR_CUDA, "reading the kernel status word failed: %s", cudaGetErrorString(cudaGetLastError()));
+  if (st.code != 0) {
+    cudaMemset(ctx->tc_status, 0, sizeof st);
+    return lf_fail(ctx, LF_ERR_TIMEOUT, "a bounded wait expired in a tensor-core kernel (wait %u, block %u)", st.where, st.block);
+  }
+  return LF_OK;
+}
+
 lf_status prepare_weights(lf_context*, lf_weights*) { return LF_OK; }
-bool triangle_supported(int, int, int) { return false; }
-lf_status triangle_run(lf_context* ctx, ArenaCursor&, int, int, int, int, int, float, int, int, int, const void*,
-                       const float*, void*, const lf_weights*) {
-  return lf_fail(ctx, LF_ERR_UNSUPPORTED, "tensor-core triangle path not built");
+
+// ---------------------------------------------------------------------------
+// Triangle contraction.
+//
+// One 128 x 256 output tile of one channel per work item, K stepped by 64 through
+// a 4-stage TMA ring, float32 accumulators double-buffered in TMEM (2 x 256
+// columns) so the epilogue of a tile overlaps the main loop of the next.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = epilogue.
+// MAJOR 0: both operands K-major (outgoing).  MAJOR 1: both MN-major (incoming),
+// fetched as 64 x 64 boxes whose rows are k.
+
+constexpr int CT_BM = 128, CT_BN = 256, CT_BK = 64, CT_STAGES = 4;
+constexpr int CT_A_BYTES = CT_BM * CT_BK * 2;   // 16 KiB
+constexpr int CT_B_BYTES = CT_BN * CT_BK * 2;   // 32 KiB
+constexpr int CT_STAGE_BYTES = CT_A_BYTES + CT_B_BYTES;
+constexpr int CT_SMEM = CT_STAGES * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int CT_THREADS = 192;
+
+template <int MAJOR>
+__global__ void __launch_bounds__(CT_THREADS, 1)
+contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                op16* __restrict__ x, int n, int ld, int c, float scale, Status* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CT_STAGES * CT_STAGE_BYTES);
+  uint64_t* full = bars;                       // [STAGES]
+  uint64_t* empty = bars + CT_STAGES;          // [STAGES]
+  uint64_t* tmem_full = bars + 2 * CT_STAGES;  // [2]
+  uint64_t* tmem_empty = tmem_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (n + CT_BM - 1) / CT_BM, tiles_n = (n + CT_BN - 1) / CT_BN;
+  const int tiles_per_h = tiles_m * tiles_n;
+  const int total = c * tiles_per_h;
+  const int kblocks = (n + CT_BK - 1) / CT_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CT_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&mapA);
+      prefetch_tensormap(&mapB);
+      int stage = 0; uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        const int h = t / tiles_per_h, rem = t % tiles_per_h, mi = rem / tiles_n, nj = rem % tiles_n;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks && ok; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, status, 1)) { ok = false; break; }
+          uint8_t* sA = smem + stage * CT_STAGE_BYTES;
+          uint8_t* sB = sA + CT_A_BYTES;
+          mbar_expect_tx(&full[stage], CT_STAGE_BYTES);
+          if (MAJOR == 0) {
+            tma_load_3d(sA, &mapA, &full[stage], kb * CT_BK, mi * CT_BM, h);
+            tma_load_3d(sB, &mapB, &full[stage], kb * CT_BK, nj * CT_BN, h);
+          } else {
+#pragma unroll
+            for (int q = 0; q < CT_BM / 64; ++q) tma_load_3d(sA + q * 8192, &mapA, &full[stage], mi * CT_BM + q * 64, kb * CT_BK, h);
+#pragma unroll
+            for (int q = 0; q < CT_BN / 64; ++q) tma_load_3d(sB + q * 8192, &mapB, &full[stage], nj * CT_BN + q * 64, kb * CT_BK, h);
+          }
+          if (++stage == CT_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(CT_BM, CT_BN, MAJOR, MAJOR);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < total; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * CT_BN;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * CT_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + CT_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < CT_BK / 16; ++kk) {
+            uint64_t adesc, bdesc;
+            if (MAJOR == 0) {
+              adesc = make_smem_desc(a_addr + kk * 32, 16, 1024);
+              bdesc = make_smem_desc(b_addr + kk * 32, 16, 1024);
+            } else {
+              adesc = make_smem_desc(a_addr + kk * 2048, 8192, 1024);
+              bdesc = make_smem_desc(b_addr + kk * 2048, 8192, 1024);
+            }
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == CT_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int row = q * 32 + lane;
+    int it = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++it) {
+      const int h = t / tiles_per_h, rem = t % tiles_per_h, mi = rem / tiles_n, nj = rem % tiles_n;
+      const int buf = it & 1;
+      if (!mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_flag, status, 4)) break;
+      tc_fence_after();
+      const int gi = mi * CT_BM + row;
+      op16* dst_row = x + ((int64_t)h * n + gi) * ld;
+#pragma unroll 1
+      for (int cc = 0; cc < CT_BN / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * CT_BN + cc * 32, r);
+        tmem_ld_wait();
+        const int gj0 = nj * CT_BN + cc * 32;
+        if (gi < n) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int gj = gj0 + v * 8;
+            if (gj < ld) {
+              uint4 pk;
+              pk.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
+              pk.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
+              pk.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
+              pk.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+              *reinterpret_cast<uint4*>(dst_row + gj) = pk;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) drain_after_abort();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
-bool attention_supported(int, int, int, int, int, int) { return false; }
-lf_status attention_run(lf_context* ctx, ArenaCursor&, int, int, int, int, int, int, int, float, int, int, int, int, int,
-                        int, const void*, const float*, void*, const lf_weights*) {
-  return lf_fail(ctx, LF_ERR_UNSUPPORTED, "tensor-core attention path not built");
+
+void configure_once() {
+  std::call_once(g_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+      cudaGetLastError();
+    cudaFuncSetAttribute(contract_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
+    cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
+    cudaGetLastError();
+  });
 }
-bool transition_supported(int, int, int) { return false; }
-lf_status transition_run(lf_context* ctx, ArenaCursor&, int64_t, int, int, int, int, float, int, int, const void*, void*,
-                         const lf_weights*) {
-  return lf_fail(ctx, LF_ERR_UNSUPPORTED, "tensor-core transition path not built");
+
+bool contract_supported(int n, int c) { return n >= 1 && c >= 1 && g_encode != nullptr; }
+
+lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int n, int ld, int c,
+                   int incoming, float scale) {
+  if (cur.dry) return LF_OK;
+  if (ld % 8 != 0 || ld < n) return lf_fail(ctx, LF_ERR_ARGUMENT, "contraction row stride %d must be a multiple of 8 and at least %d", ld, n);
+  CUtensorMap mapA, mapB;
+  const uint64_t row_bytes = (uint64_t)ld * 2, plane_bytes = (uint64_t)n * ld * 2;
+  if (!incoming) {
+    LF_TRY(make_map_f16_3d(ctx, &mapA, a, n, n, c, row_bytes, plane_bytes, CT_BK, CT_BM));
+    LF_TRY(make_map_f16_3d(ctx, &mapB, b, n, n, c, row_bytes, plane_bytes, CT_BK, CT_BN));
+  } else {
+    // A(i,k) = b[h][k][i], B(j,k) = a[h][k][j]: boxes of 64 (i or j) x 64 (k)
+    LF_TRY(make_map_f16_3d(ctx, &mapA, b, n, n, c, row_bytes, plane_bytes, 64, CT_BK));
+    LF_TRY(make_map_f16_3d(ctx, &mapB, a, n, n, c, row_bytes, plane_bytes, 64, CT_BK));
+  }
+  const int tiles = c * ((n + CT_BM - 1) / CT_BM) * ((n + CT_BN - 1) / CT_BN);
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  if (!incoming)
+    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
+  else
+    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
+  ctx->launches++;
+  return LF_OK;
 }
 
 }  // namespace tc

@@ -1,0 +1,62 @@
+"""bf16 tensor-core path against the CPU oracle (float32 reference arithmetic).
+
+Tolerances: per operator 8e-3 relative L2 (the reference's bound for its
+half-precision arms: ``tools/gpu/check-evoformer-attention.js:162``,
+``tools/gpu/check-triangle.js:59``); per block 2e-3 on the block's output pair,
+the bound this library is specified to.  Masked positions must stay exact.
+"""
+import numpy as np
+import pytest
+
+from localfold_b200 import synthetic as syn
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+OP_TOL = 8e-3
+BLOCK_TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import localfold_b200 as lf
+    return lf.Device(0)
+
+
+@pytest.mark.parametrize("n", [64, 203, 300])
+@pytest.mark.parametrize("incoming", [False, True])
+def test_triangle_bf16(dev, n, incoming):
+    import localfold_b200 as lf
+    d = syn.draw(300 + n)
+    z = d.normal(n, n, 128)
+    mask = syn.residue_pair_mask(n, 0.05)
+    w = syn.af2_triangle_weights(d, 128, 128)
+    cls = lf.TriangleMultiplicationIncomingGpu if incoming else lf.TriangleMultiplicationOutgoingGpu
+    got = cls(dev).run({"shape": {"length": n, "cZ": 128, "cHidden": 128}, "z": z, "mask": mask, "weights": w},
+                       {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.trimul_af2(z, mask, w, 128, 1e-5, incoming)
+    assert np.isfinite(got).all()
+    assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+def test_triangle_bf16_af3_channels_64(dev):
+    import localfold_b200 as lf
+    n, c = 96, 64
+    d = syn.draw(31)
+    pair = d.normal(n, n, c)
+    mask = syn.residue_pair_mask(n, 0.1)
+    w = syn.af3_triangle_weights(d, c)
+    for direction in ("outgoing", "incoming"):
+        got = lf.af3_triangle_multiplication(dev, pair, mask, n, c, direction, w, {"precision": "bf16"})["output"]
+        want = oracle.trimul_af3(pair, mask, w, direction == "incoming")
+        assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+def test_af2_pair_block_bf16(dev):
+    import localfold_b200 as lf
+    n = 64
+    pair, mask, weights = syn.af2_pair_block(0, n, masked_tail=0.05)
+    want = oracle.af2_pair_block(pair, mask, weights[0], 128)
+    stack = lf.PairStackGpu(dev).prepare(weights, 128, 128)
+    got = stack.run(pair, mask, {"precision": "bf16", "variance": "two-pass"})
+    stack.close()
+    assert oracle.relative_l2(got["pair"], want) <= BLOCK_TOL
