@@ -1,0 +1,298 @@
+"""Benchmark of the pair-stack hot path: one AF2 pair-stack block per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--length L]
+
+A step is one block of the 48-block AF2 Evoformer pair stack (triangle
+multiplication outgoing + incoming, triangle attention starting + ending node,
+pair transition) on a resident N x N x 128 pair tensor: BASELINE config 4's
+shape (N = 2048, c_z = 128, c = 128, 4 x 32 heads, 4x transition, seed 4, mask
+of ones), synthetic N(0,1) pair and N(0, 1/fan_in) weights.  Successive steps
+are successive blocks of the stack on the same pair, as in the stack runner.
+
+The JSON line reports ms per block (lower is better) with the pair resident in
+HBM (`value`), the same through the host-buffer API with copies in the timed
+region (`e2e`), the live roofline of the triangle contraction kernel, and the
+CPU oracle timed on this host on a bounded sample (`cpu_baseline`).
+
+`--impl reference` times the reference's CPU implementation of the same block
+(the C restatement under oracle/; the reference itself is JavaScript and no
+JavaScript engine exists on these machines) on all host cores, on a bounded
+sample, scaled to the full workload by algorithmic FLOPs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+C_Z = 128
+C_HIDDEN = 128
+HEADS = 4
+
+
+def block_flops(n: int) -> float:
+    """AF2 pair block: 1536 N^3 + 985088 N^2 (contractions + attention + dense)."""
+    return 1536.0 * n ** 3 + 985088.0 * n ** 2
+
+
+def contraction_flops(n: int) -> float:
+    return 256.0 * n ** 3
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(sample_n: int, full_n: int, threads: int | None = None):
+    """Times the CPU oracle on one AF2 pair block at `sample_n` and scales to `full_n` by FLOPs."""
+    from localfold_b200 import synthetic as syn
+    from oracle import oracle
+    if threads:
+        oracle.set_threads(threads)
+    cores = oracle.max_threads() if not threads else threads
+    pair, mask, weights = syn.af2_pair_block(4, sample_n)
+    t0 = time.perf_counter()
+    oracle.af2_pair_block(pair, mask, weights[0], C_HIDDEN)
+    seconds = time.perf_counter() - t0
+    scaled_ms = seconds * 1e3 * block_flops(full_n) / block_flops(sample_n)
+    return {"value": scaled_ms, "unit": "ms/block", "cores": cores, "kind": "port",
+            "sample": f"one AF2 pair block at N={sample_n} ({seconds:.2f} s on {cores} threads), scaled to "
+                      f"N={full_n} by algorithmic FLOPs (1536 N^3 + 985088 N^2)",
+            "sample_seconds": seconds}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    full_n = args.length
+    times = []
+    sample_n = args.cpu_sample
+    res = None
+    for i in range(args.warmup + args.steps):
+        res = cpu_sample(sample_n, full_n)
+        if i >= args.warmup:
+            times.append(res["value"])
+        if sum(times) and (time.perf_counter() - START) > 240:
+            break
+    ms = float(np.mean(times))
+    line = {
+        "impl": "reference", "metric": "pair_stack_block_ms", "value": ms, "unit": "ms/block", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate / f32 store", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": ms, "unit": "ms/block", "cores": res["cores"], "kind": "port", "sample": res["sample"]},
+        "e2e": {"value": ms, "unit": "ms/block", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, n_gpus):
+    return {"workload": f"AF2 Evoformer pair-stack block, N={args.length}, c_z=128, tri-mult c=128, "
+                        f"tri-attention 4x32, transition 4x, seed 4, mask ones (BASELINE config 4 shape)",
+            "length": args.length, "precision": args.precision, "pair_dtype": "f32",
+            "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} independent replicas",
+            "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * 4 / 2 ** 20)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--length", type=int, default=2048)
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--cpu-sample", type=int, default=384, help="N of the CPU oracle's bounded sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import localfold_b200 as lf
+    from localfold_b200 import synthetic as syn
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    # a non-default stream: the library and the timing events share it
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    dev = lf.Device(local_rank, stream=stream.cuda_stream)
+
+    n = args.length
+    pair_h, mask_h, weights = syn.af2_pair_block(4 + rank, n, blocks=2)
+    stack = lf.PairStackGpu(dev).prepare(weights, C_Z, C_HIDDEN)
+    opts = {"precision": args.precision, "variance": "two-pass"}
+    pair_d = torch.from_numpy(pair_h).cuda()
+    mask_d = torch.from_numpy(mask_h).cuda()
+
+    def step(i):
+        stack.run(pair_d, mask_d, opts, first_block=i % 2, n_blocks=1)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = dev.launch_count()
+    dev.profile(True)
+    dev.profile_read()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    families = dev.profile_read()
+    dev.profile(False)
+    launches = dev.launch_count() - launches0
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_block = total_ms / args.steps
+    finite = bool(torch.isfinite(pair_d).all().item())
+
+    # end to end through the host-buffer API: pinned host pair in, pair out, every step
+    e2e = None
+    if not args.no_e2e:
+        pinned = torch.empty((n, n, C_Z), dtype=torch.float32, pin_memory=True)
+        pinned.copy_(torch.from_numpy(pair_h))
+        mask_p = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+        mask_p.copy_(torch.from_numpy(mask_h))
+        host_pair, host_mask = pinned.numpy(), mask_p.numpy()
+        reps = max(2, min(args.steps, 3))
+        stack.run(host_pair, host_mask, opts, first_block=0, n_blocks=1, inplace=True)   # warm the staging arena
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(reps):
+            stack.run(host_pair, host_mask, opts, first_block=i % 2, n_blocks=1, inplace=True)
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) * 1e3 / reps
+        if world > 1:
+            t = torch.tensor([wall], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            wall = float(t.item())
+        e2e = {"value": wall, "unit": "ms/block", "h2d_bytes_per_step": int(pinned.numel() * 4 + mask_p.numel() * 4),
+               "d2h_bytes_per_step": int(pinned.numel() * 4)}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ct_ms, ct_launches = families["triangle_contract"]
+        roofline = None
+        if ct_launches:
+            per_launch_ms = ct_ms / ct_launches
+            achieved = contraction_flops(n) / (per_launch_ms * 1e-3) / 1e12
+            roofline = {"kernel": "triangle contraction (tcgen05, 128 batched NxNxN GEMMs)", "bound": "tensor",
+                        "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                        "frac": achieved / peaks["tflops_sustained"], "traffic": None,
+                        "peak_source": peaks["source"] + " (sustained cuBLAS bf16; the kernel runs inside a long step)",
+                        "launch_ms": per_launch_ms, "flops_per_launch": contraction_flops(n)}
+        cpu = None
+        if not args.no_cpu:
+            cpu = cpu_sample(args.cpu_sample, n)
+        line = {
+            "metric": "pair_stack_block_ms", "value": ms_per_block, "unit": "ms/block", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_block, "higher_is_better": False,
+            "scaling": "weak" if world > 1 else "strong", "vs_baseline": None,
+            "dtype": "f16 operands / f32 accumulate (pair stream f32)" if args.precision == "bf16" else "f32",
+            "data": "synthetic", "config": workload_config(args, world),
+            "tflops_block": block_flops(n) / (ms_per_block * 1e-3) / 1e12,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "kernel_ms_per_step": {k: v[0] / args.steps for k, v in families.items() if v[1]},
+            "clocks": clocks, "finite": finite,
+        }
+        print(json.dumps(line))
+    stack.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+START = time.perf_counter()
+
+if __name__ == "__main__":
+    main()

@@ -91,6 +91,24 @@ LF_API lf_status lf_context_reserve(lf_context* ctx, uint64_t bytes);
 LF_API void lf_context_release_scratch(lf_context* ctx);
 LF_API const char* lf_version(void);
 
+/* Per-kernel timing, the counterpart of the reference's timestamp-query
+ * profile (webgpu/runtime/execution.js:673-703): when enabled, every kernel
+ * launch is bracketed by CUDA events on the context's stream.
+ * lf_context_profile_read synchronises, then returns and clears the device
+ * time and launch count accumulated for one kernel family. */
+typedef enum lf_kernel_family {
+  LF_KERNEL_SIMT = 0,              /* float32 SIMT kernels (all of them)        */
+  LF_KERNEL_TRIANGLE_CONTRACT = 1, /* tcgen05 triangle contraction              */
+  LF_KERNEL_LN_GEMM = 2,           /* tcgen05 LayerNorm + projection kernels    */
+  LF_KERNEL_TRIANGLE_OUTPUT = 3,   /* tcgen05 centre-norm + output projection   */
+  LF_KERNEL_ATTENTION = 4,         /* tcgen05 attention core                    */
+  LF_KERNEL_TRANSITION = 5,        /* tcgen05 fused transition                  */
+  LF_KERNEL_ELEMENTWISE = 6,       /* memory-bound vectorised kernels           */
+  LF_KERNEL_FAMILY_COUNT = 7
+} lf_kernel_family;
+LF_API lf_status lf_context_profile(lf_context* ctx, int enable);
+LF_API lf_status lf_context_profile_read(lf_context* ctx, int family, double* total_ms, uint64_t* launches);
+
 /* ---- weights ------------------------------------------------------------ */
 
 typedef enum lf_weight_kind {

@@ -18,6 +18,9 @@ PAIR_BIAS_NONE, PAIR_BIAS_SEPARATE, PAIR_BIAS_NORMALIZED_INPUT = 0, 1, 2
 (WEIGHTS_TRIANGLE_AF2, WEIGHTS_TRIANGLE_AF3, WEIGHTS_ATTENTION_AF2, WEIGHTS_GRID_ATTENTION_AF3,
  WEIGHTS_TRANSITION_AF2, WEIGHTS_TRANSITION_AF3, WEIGHTS_OPM_AF2, WEIGHTS_SINGLE_ATTENTION_AF3) = range(1, 9)
 
+KERNEL_FAMILIES = ("simt", "triangle_contract", "ln_gemm", "triangle_output", "attention", "transition",
+                   "elementwise")
+
 c_void_p, c_int32, c_int64, c_float = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float
 
 
@@ -92,7 +95,7 @@ class PairStackDesc(ctypes.Structure):
 
 EXPORTS = (
     "lf_version", "lf_context_create", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
-    "lf_context_launch_count", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
+    "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
 )
@@ -117,6 +120,9 @@ def load():
     lib.lf_context_synchronize.argtypes = [c_void_p]
     lib.lf_context_launch_count.argtypes = [c_void_p]
     lib.lf_context_launch_count.restype = ctypes.c_uint64
+    lib.lf_context_profile.argtypes = [c_void_p, ctypes.c_int]
+    lib.lf_context_profile_read.argtypes = [c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double),
+                                            ctypes.POINTER(ctypes.c_uint64)]
     lib.lf_context_reserve.argtypes = [c_void_p, ctypes.c_uint64]
     lib.lf_context_release_scratch.argtypes = [c_void_p]
     lib.lf_context_release_scratch.restype = None

@@ -12,6 +12,22 @@
 // ---------------------------------------------------------------------------
 // context
 
+static void profile_collect(lf_context* ctx) {
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& t : ctx->timed) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) {
+      ctx->family_ms[t.family] += ms;
+      ctx->family_launches[t.family] += 1;
+    }
+    cudaEventDestroy(t.start);
+    cudaEventDestroy(t.stop);
+  }
+  ctx->timed.clear();
+  cudaGetLastError();
+}
+
+
 lf_status lf_arena_ensure(lf_context* ctx, size_t bytes) {
   if (bytes <= ctx->arena_bytes) return LF_OK;
   // Work that still reads the old arena must finish before it is freed.
@@ -64,7 +80,7 @@ lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out) 
 void lf_context_destroy(lf_context* ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
-  cudaStreamSynchronize(ctx->stream);
+  profile_collect(ctx);
   if (ctx->arena) cudaFree(ctx->arena);
   if (ctx->tc_status) cudaFree(ctx->tc_status);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
@@ -82,6 +98,25 @@ lf_status lf_context_synchronize(lf_context* ctx) {
 }
 
 uint64_t lf_context_launch_count(const lf_context* ctx) { return ctx ? ctx->launches : 0; }
+
+lf_status lf_context_profile(lf_context* ctx, int enable) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  cudaSetDevice(ctx->device);
+  profile_collect(ctx);
+  ctx->profiling = enable != 0;
+  return LF_OK;
+}
+
+lf_status lf_context_profile_read(lf_context* ctx, int family, double* total_ms, uint64_t* launches) {
+  if (!ctx || family < 0 || family >= LF_KERNEL_FAMILY_COUNT) return LF_ERR_ARGUMENT;
+  cudaSetDevice(ctx->device);
+  profile_collect(ctx);
+  if (total_ms) *total_ms = ctx->family_ms[family];
+  if (launches) *launches = ctx->family_launches[family];
+  ctx->family_ms[family] = 0;
+  ctx->family_launches[family] = 0;
+  return LF_OK;
+}
 
 lf_status lf_context_reserve(lf_context* ctx, uint64_t bytes) {
   if (!ctx) return LF_ERR_ARGUMENT;
@@ -398,7 +433,9 @@ namespace {
 #define LAUNCH(ctx, cur, kernel, grid, block, smem, ...)                     \
   do {                                                                       \
     if (!(cur).dry) {                                                        \
+      lf_prof_begin((ctx), LF_KERNEL_SIMT);                                  \
       kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);       \
+      lf_prof_end((ctx));                                                    \
       (ctx)->launches++;                                                     \
     }                                                                        \
   } while (0)
@@ -502,9 +539,13 @@ lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   op16* x = cur.take<op16>(plane * c);
   LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
          f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
-  sgemm(ctx, cur, false, false, simt::EPI_NONE, (int)P, 4 * c, cz, zn, cz, 0, f[TRI_W4], 4 * c, 0, p4, 4 * c, 0, f[TRI_B4], 0, 1);
-  LAUNCH(ctx, cur, (simt::trimul_gate_kernel<op16>), dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
-         a.mask, P, c, n, ld, ga, gb);
+  if (tc::ln_gemm_supported(a.w)) {
+    LF_TRY(tc::triangle_project(ctx, cur, a.z, a.act_dtype, a.mask, n, ld, a.variance, a.eps, a.w, ga, gb));
+  } else {
+    sgemm(ctx, cur, false, false, simt::EPI_NONE, (int)P, 4 * c, cz, zn, cz, 0, f[TRI_W4], 4 * c, 0, p4, 4 * c, 0, f[TRI_B4], 0, 1);
+    LAUNCH(ctx, cur, (simt::trimul_gate_kernel<op16>), dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
+           a.mask, P, c, n, ld, ga, gb);
+  }
   // x is stored as fp16 scaled by a power of two near 1/sqrt(n) so that sums over n terms
   // stay far from the fp16 limits; the centre LayerNorm undoes the scale exactly.
   const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
@@ -576,8 +617,36 @@ void att_f32(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
          a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
 }
 
+// 16-bit path: tensor-core LayerNorm + q/k/v/gate/bias projection, then the attention core.
+template <typename T>
+lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
+  const int64_t R = (int64_t)a.batch * a.Q;
+  const int HD = a.heads * a.d, c = a.ch;
+  const auto& f = a.w->f;
+  op16* q = cur.take<op16>(R * HD);
+  op16* k = cur.take<op16>(R * HD);
+  op16* v = cur.take<op16>(R * HD);
+  op16* g = cur.take<op16>(R * HD);
+  float* bias = a.bias_mode ? cur.take<float>((int64_t)a.heads * a.Q * a.Q) : nullptr;
+  float* qkvg = cur.take<float>(R * 4 * HD);
+  float* o = cur.take<float>(R * HD);
+  float* proj = cur.take<float>(R * c);
+  LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
+                               a.bias_swap, a.w, q, k, v, g, bias));
+  LAUNCH(ctx, cur, simt::unpack_qkvg_kernel, lf_ceil_div(R * HD, 256), 256, 0, q, k, v, g, R, HD, qkvg);
+  size_t smem = (size_t)(2 * 32 * (a.d + 1) + 8 * a.d) * sizeof(float);
+  LAUNCH(ctx, cur, simt::attention_kernel, dim3(lf_ceil_div(a.Q, 8), a.batch, a.heads), 256, smem, qkvg, bias, a.mask,
+         a.batch, a.Q, a.heads, a.d, a.transpose, a.mask_mode, a.clamp, 1.0f, o);
+  sgemm(ctx, cur, false, false, 0, (int)R, c, HD, o, HD, 0, f[ATT_WO], c, 0, proj, c, 0, f[ATT_BO], 0, 1);
+  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
+         a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
+  return LF_OK;
+}
+
 lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int precision) {
-  (void)precision;
+  if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && tc::ln_gemm_supported(a.w)) {
+    return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
+  }
   if (a.act_dtype == LF_DTYPE_BF16) att_f32<bf16>(ctx, cur, a); else att_f32<float>(ctx, cur, a);
   return LF_OK;
 }
@@ -624,12 +693,12 @@ lf_status run_with_arena(lf_context* ctx, lf_result* r, bool timed, F body) {
   cudaSetDevice(ctx->device);
   ArenaCursor dry{ctx, 0, true};
   LF_TRY(body(dry));
-  LF_TRY(lf_arena_ensure(ctx, dry.offset));
+  LF_TRY(lf_arena_ensure(ctx, dry.peak));
   uint64_t before = ctx->launches;
   if (timed) cudaEventRecord(ctx->ev0, ctx->stream);
   ArenaCursor cur{ctx, 0, false};
   LF_TRY(body(cur));
-  if (cur.offset > ctx->arena_peak) ctx->arena_peak = cur.offset;
+  if (cur.peak > ctx->arena_peak) ctx->arena_peak = cur.peak;
   float ms = 0.f;
   if (timed) {
     cudaEventRecord(ctx->ev1, ctx->stream);

@@ -34,7 +34,26 @@ struct lf_context {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int sm_count = 148;
   void* tc_status = nullptr;   // device word the tensor-core kernels set when a bounded wait expires
+  // Optional per-kernel-family timing (CUDA events on the context's stream).
+  bool profiling = false;
+  struct Timed { int family; cudaEvent_t start, stop; };
+  std::vector<Timed> timed;
+  double family_ms[LF_KERNEL_FAMILY_COUNT] = {0};
+  uint64_t family_launches[LF_KERNEL_FAMILY_COUNT] = {0};
 };
+
+static inline void lf_prof_begin(lf_context* ctx, int family) {
+  if (!ctx->profiling) return;
+  lf_context::Timed t{family, nullptr, nullptr};
+  cudaEventCreate(&t.start);
+  cudaEventCreate(&t.stop);
+  cudaEventRecord(t.start, ctx->stream);
+  ctx->timed.push_back(t);
+}
+static inline void lf_prof_end(lf_context* ctx) {
+  if (!ctx->profiling || ctx->timed.empty()) return;
+  cudaEventRecord(ctx->timed.back().stop, ctx->stream);
+}
 
 // Slots of lf_weights::f per operator kind.
 enum { TRI_LN_G, TRI_LN_B, TRI_W4, TRI_B4, TRI_LNO_G, TRI_LNO_B, TRI_WZ, TRI_BZ, TRI_WG, TRI_BG, TRI_COUNT };
@@ -87,11 +106,13 @@ struct ArenaCursor {
   lf_context* ctx;
   size_t offset;
   bool dry;       // planning pass: only adds sizes up
+  size_t peak = 0;   // high-water mark (callers may rewind `offset` between operators)
   template <typename T>
   T* take(size_t count) {
     size_t bytes = lf_align_up(count * sizeof(T), 256);
     T* p = dry ? nullptr : reinterpret_cast<T*>(ctx->arena + offset);
     offset += bytes;
+    if (offset > peak) peak = offset;
     return p;
   }
 };

@@ -231,6 +231,20 @@ __global__ void finish_kernel(const float* __restrict__ proj, const float* __res
   out[dst * ch + c] = from_f<TAct>(v);
 }
 
+// q, k, v, gate as four fp16 [rows][HD] tensors -> one float32 [rows][4*HD] tensor
+__global__ void unpack_qkvg_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
+                                   const __half* __restrict__ g, int64_t rows, int HD, float* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * HD) return;
+  int64_t r = idx / HD;
+  int c = (int)(idx % HD);
+  float* o = out + r * 4 * HD + c;
+  o[0] = __half2float(q[idx]);
+  o[HD] = __half2float(k[idx]);
+  o[2 * HD] = __half2float(v[idx]);
+  o[3 * HD] = __half2float(g[idx]);
+}
+
 template <typename TIn>
 __global__ void to_float_kernel(const TIn* __restrict__ in, int64_t n, float* __restrict__ out) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;

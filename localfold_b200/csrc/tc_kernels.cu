@@ -49,7 +49,41 @@ lf_status check_status(lf_context* ctx) {
   return LF_OK;
 }
 
-lf_status prepare_weights(lf_context*, lf_weights*) { return LF_OK; }
+bool ln_gemm_supported(const lf_weights* w) { return w && !w->h.empty() && w->h[0] != nullptr; }
+
+// bf16/fp16 repacks for the tensor-core kernels: h[0] = swizzled fp16 image of the fused
+// projection W^T (plus the pair-bias projection rows for attention), h[1] = its bias vector.
+lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
+  const bool tri = w->kind == LF_WEIGHTS_TRIANGLE_AF2 || w->kind == LF_WEIGHTS_TRIANGLE_AF3;
+  const bool att = w->kind == LF_WEIGHTS_ATTENTION_AF2 || w->kind == LF_WEIGHTS_GRID_ATTENTION_AF3;
+  if (tri && w->dims.channels == 128 && w->dims.hidden == 128) {
+    op16* img = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img, 512 * 256));
+    w->owned.push_back(img);
+    LF_CUDA(ctx, cudaMemsetAsync(img, 0, 512 * 256, ctx->stream));
+    pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0);
+    w->h.assign(2, nullptr);
+    w->h[0] = img;
+  } else if (att && w->dims.channels == 128 && w->dims.heads * w->dims.head_dim == 128 && w->dims.heads <= 16 &&
+             !w->has_pair_norm) {
+    op16* img = nullptr;
+    float* bias = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img, 528 * 256));
+    w->owned.push_back(img);
+    LF_CUDA(ctx, cudaMalloc(&bias, 528 * sizeof(float)));
+    w->owned.push_back(bias);
+    LF_CUDA(ctx, cudaMemsetAsync(img, 0, 528 * 256, ctx->stream));
+    LF_CUDA(ctx, cudaMemsetAsync(bias, 0, 528 * sizeof(float), ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(bias, w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    pack_weight_image(ctx, w->f[ATT_W4], 128, 512, 528, 0, 512, img, 0);
+    if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512);
+    w->h.assign(2, nullptr);
+    w->h[0] = img;
+    w->h[1] = bias;
+  }
+  LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return LF_OK;
+}
 
 // ---------------------------------------------------------------------------
 // Triangle contraction.
@@ -217,6 +251,7 @@ void configure_once() {
       cudaGetLastError();
     cudaFuncSetAttribute(contract_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
+    configure_ln_gemm();
     cudaGetLastError();
   });
 }
@@ -239,10 +274,12 @@ lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16*
   }
   const int tiles = c * ((n + CT_BM - 1) / CT_BM) * ((n + CT_BN - 1) / CT_BN);
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_CONTRACT);
   if (!incoming)
     contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
   else
     contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
+  lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
 }

@@ -20,4 +20,18 @@ bool contract_supported(int n, int c);
 lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int n, int ld, int c,
                    int incoming, float scale);
 
+// LayerNorm + projection kernels for 128-channel activations (weights repacked by
+// prepare_weights into lf_weights::h).
+bool ln_gemm_supported(const lf_weights* w);
+void configure_ln_gemm();
+void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0);
+// a, b [c][n][ld] fp16 = mask * (LN(z) Wp + bp) * sigmoid(LN(z) Wg + bg)
+lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
+                           int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
+// q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 [batch*Q][128] in logical row order and the
+// pair bias [heads][Q][Q] float32 (null = none) from the normalised input
+lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
+                            int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
+                            const lf_weights* w, op16* q, op16* k, op16* v, op16* g, float* bias);
+
 }  // namespace tc

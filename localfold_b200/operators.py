@@ -81,6 +81,19 @@ class Device:
     def launch_count(self) -> int:
         return int(self.lib.lf_context_launch_count(self.handle))
 
+    def profile(self, enable: bool):
+        """Bracket every kernel launch with CUDA events (off by default)."""
+        self.check(self.lib.lf_context_profile(self.handle, 1 if enable else 0))
+
+    def profile_read(self) -> dict:
+        """{family: (total device ms, launches)} accumulated since the last read."""
+        out = {}
+        for index, name in enumerate(nat.KERNEL_FAMILIES):
+            ms, count = ctypes.c_double(), ctypes.c_uint64()
+            self.check(self.lib.lf_context_profile_read(self.handle, index, ctypes.byref(ms), ctypes.byref(count)))
+            out[name] = (ms.value, int(count.value))
+        return out
+
     def reserve(self, nbytes: int):
         self.check(self.lib.lf_context_reserve(self.handle, int(nbytes)))
 

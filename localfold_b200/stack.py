@@ -79,8 +79,9 @@ class PairStackGpu:
         self._table = (nat.PairBlockWeights * len(self.blocks))(*[b.struct() for b in self.blocks])
         return self
 
-    def run(self, pair, mask, options=None, first_block=0, n_blocks=None, dialect=None):
-        """Updates ``pair`` (device tensor: in place; numpy: returns a new array)."""
+    def run(self, pair, mask, options=None, first_block=0, n_blocks=None, dialect=None, inplace=False):
+        """Updates ``pair`` (device tensor: in place; numpy: returns a new array, or
+        updates the given float32 array when ``inplace``)."""
         opts = options or {}
         dev = self.device
         c_z, c_hidden = self.shape
@@ -98,6 +99,10 @@ class PairStackGpu:
         if m.count != n * n:
             raise nat.RangeError(f"mask has {m.count} values; expected {n * n}")
         if p.is_device:
+            target, output = p, pair
+        elif inplace:
+            if p.keep is not pair and not np.shares_memory(p.keep, pair):
+                raise ValueError("inplace needs a contiguous float32 array")
             target, output = p, pair
         else:
             output = np.array(pair, np.float32, copy=True).reshape(n, n, c_z)

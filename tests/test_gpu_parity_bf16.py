@@ -60,3 +60,34 @@ def test_af2_pair_block_bf16(dev):
     got = stack.run(pair, mask, {"precision": "bf16", "variance": "two-pass"})
     stack.close()
     assert oracle.relative_l2(got["pair"], want) <= BLOCK_TOL
+
+
+@pytest.mark.parametrize("n", [64, 77])
+@pytest.mark.parametrize("transpose", [False, True])
+def test_triangle_attention_af2_bf16(dev, n, transpose):
+    import localfold_b200 as lf
+    d = syn.draw(500 + n)
+    z = d.normal(n, n, 128)
+    mask = syn.residue_pair_mask(n, 0.1)
+    t = syn.af2_attention_weights(d, 128, 4, 128)
+    pb = dict(t["pairBias"], source="normalized-input")
+    inp = {"activations": z, "mask": mask, "batch": n, "queryLength": n, "channels": 128, "heads": 4,
+           "transpose": transpose, "weights": t["attention"], "pairBias": pb}
+    got = lf.AttentionGpu(dev).run(inp, {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], transpose, pb)
+    assert np.isfinite(got).all()
+    assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+@pytest.mark.parametrize("transpose,swap", [(False, False), (True, False), (True, True)])
+def test_grid_attention_af3_bf16(dev, transpose, swap):
+    import localfold_b200 as lf
+    n = 72
+    d = syn.draw(600)
+    z = d.normal(n, n, 128)
+    mask = (d.rng.random((n, n)) > 0.1).astype(np.float32)
+    w = syn.af3_grid_attention_weights(d, 128, 4, 32)
+    got = lf.Af3GridSelfAttentionGpu(dev).run(z, mask, {"n": n, "channels": 128, "transpose": transpose}, w,
+                                              {"swapTransposedBias": swap}, {"precision": "bf16"})["output"]
+    want = oracle.grid_attention_af3(z, mask, w, transpose, swap)
+    assert oracle.relative_l2(got, want) <= OP_TOL
