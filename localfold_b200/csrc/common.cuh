@@ -70,6 +70,7 @@ struct lf_weights {
   std::vector<float*> f;     // named by the per-kind enums in weights.cuh
   std::vector<void*> h;      // bf16 repacks (tensor-core path)
   std::vector<void*> owned;  // every device allocation, for destroy
+  int bias_flags = 0;        // per 128-column group of the fused projection: bias is non-zero
   bool has_gate_bias = false, has_out_bias = false, has_pair_norm = false, has_pair_proj = false;
 };
 

@@ -3,7 +3,9 @@
 
 #include <cuda.h>
 
+#include <cmath>
 #include <mutex>
+#include <vector>
 
 #include "tc05.cuh"
 
@@ -61,7 +63,7 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     LF_CUDA(ctx, cudaMalloc(&img, 512 * 256));
     w->owned.push_back(img);
     LF_CUDA(ctx, cudaMemsetAsync(img, 0, 512 * 256, ctx->stream));
-    pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0);
+    pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0, 1.0f);
     w->h.assign(2, nullptr);
     w->h[0] = img;
   } else if (att && w->dims.channels == 128 && w->dims.heads * w->dims.head_dim == 128 && w->dims.heads <= 16 &&
@@ -74,9 +76,23 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->owned.push_back(bias);
     LF_CUDA(ctx, cudaMemsetAsync(img, 0, 528 * 256, ctx->stream));
     LF_CUDA(ctx, cudaMemsetAsync(bias, 0, 528 * sizeof(float), ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(bias, w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
-    pack_weight_image(ctx, w->f[ATT_W4], 128, 512, 528, 0, 512, img, 0);
-    if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512);
+    // the query columns carry the head_dim^-1/2 logit scale
+    const float qs = 1.0f / sqrtf((float)w->dims.head_dim);
+    pack_weight_image(ctx, w->f[ATT_W4], 128, 128, 528, 0, 512, img, 0, qs);
+    pack_weight_image(ctx, w->f[ATT_W4], 128, 384, 528, 128, 512, img, 128, 1.0f);
+    if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512, 1.0f);
+    {
+      std::vector<float> hb(512);
+      LF_CUDA(ctx, cudaMemcpyAsync(hb.data(), w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      for (int i = 0; i < 128; ++i) hb[i] *= qs;
+      w->bias_flags = 0;
+      for (int grp = 0; grp < 4; ++grp)
+        for (int i = 0; i < 128; ++i)
+          if (hb[grp * 128 + i] != 0.f) { w->bias_flags |= 1 << grp; break; }
+      LF_CUDA(ctx, cudaMemcpyAsync(bias, hb.data(), 512 * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
     w->h.assign(2, nullptr);
     w->h[0] = img;
     w->h[1] = bias;

@@ -24,7 +24,8 @@ lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16*
 // prepare_weights into lf_weights::h).
 bool ln_gemm_supported(const lf_weights* w);
 void configure_ln_gemm();
-void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0);
+void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0,
+                       float scale);
 // a, b [c][n][ld] fp16 = mask * (LN(z) Wp + bp) * sigmoid(LN(z) Wg + bg)
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
                            int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);

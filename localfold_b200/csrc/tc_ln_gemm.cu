@@ -9,8 +9,9 @@
 // TMEM accumulators, and finished by eight epilogue warps (bias, sigmoid gates,
 // mask, layout change) while the next chunk's MMAs run.
 //
-// Warp roles: 0..7 epilogue (TMEM lane quadrant = warp % 4, column half = warp / 4),
-// 8..11 LayerNorm producers, 12 MMA issuer and TMEM owner.
+// Warp roles: 0..15 epilogue (TMEM lane quadrant = warp % 4, quarter of the columns =
+// warp / 4), 16..23 LayerNorm producers, 24 MMA issuer and TMEM owner.  The many warps are
+// there to hide arithmetic latency: each role's per-element work is a short dependent chain.
 #include <cuda.h>
 
 #include "tc05.cuh"
@@ -20,7 +21,8 @@ namespace tc {
 
 using namespace tc05;
 
-constexpr int LG_THREADS = 13 * 32;
+constexpr int LG_THREADS = 25 * 32;
+constexpr int LG_EPI_WARPS = 16, LG_PROD_WARPS = 8, LG_MMA_WARP = 24;
 constexpr int LG_ROWS = 128;
 constexpr int LG_K = 128;
 constexpr int LG_A_BYTES = LG_ROWS * LG_K * 2;          // 32 KiB per stage, two 16 KiB k-atoms
@@ -50,13 +52,20 @@ struct LnGemmParams {
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
   float* out_bias;          // [heads][Q][Q]
   int heads, bias_swap;
-  float q_scale;
+  int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
   Status* status;
 };
 
 enum { LG_EPI_TRIANGLE = 0, LG_EPI_ATTENTION = 1 };
 
-__device__ __forceinline__ float sigmoid_fast(float v) { return __frcp_rn(1.0f + __expf(-v)); }
+// sigmoid(v) = 0.5 + 0.5 * tanh(v / 2): one MUFU operation.  tanh.approx.f32 has a relative
+// error of 2^-11, so the gate is good to about 2.4e-4 absolute - the precision of the fp16
+// operand it multiplies.
+__device__ __forceinline__ float sigmoid_fast(float v) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * v));
+  return fmaf(0.5f, t, 0.5f);
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmParams p) {
@@ -66,7 +75,9 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
   uint8_t* sW = smem;
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
   float* sBias = reinterpret_cast<float*>(sA + 2 * LG_A_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 544);
+  float* sGamma = sBias + 544;      // [128]
+  float* sBeta = sGamma + 128;      // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sBeta + 128);
   uint64_t* a_full = bars;          // [2]
   uint64_t* a_empty = bars + 2;     // [2]
   uint64_t* acc_full = bars + 4;    // [2]
@@ -79,10 +90,10 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&a_full[s], 4);
+      mbar_init(&a_full[s], LG_PROD_WARPS);
       mbar_init(&a_empty[s], 1);
       mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], 8);
+      mbar_init(&acc_empty[s], LG_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -93,87 +104,108 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
     uint4* dst = reinterpret_cast<uint4*>(sW);
     for (int i = threadIdx.x; i < w_bytes / 16; i += LG_THREADS) dst[i] = src[i];
     for (int i = threadIdx.x; i < p.n_pad; i += LG_THREADS) sBias[i] = p.bias[i];
+    if (threadIdx.x < 128) { sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
     fence_async_smem();
   }
-  if (warp == 12) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == LG_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp >= 8 && warp < 12) {
+  if (warp >= LG_EPI_WARPS && warp < LG_MMA_WARP) {
     // ---------------- LayerNorm producers ----------------
-    const int pw = warp - 8;
-    const float4 g4 = reinterpret_cast<const float4*>(p.gamma)[lane];
-    const float4 b4 = reinterpret_cast<const float4*>(p.beta)[lane];
+    // Eight lanes share a row (16 channels each), so one warp instruction covers four rows and a
+    // row statistic needs three shuffle steps.  Each warp owns 16 rows of the tile, handled as two
+    // groups of two row-quads; the loads of a group are all issued before any is consumed.
+    const int pw = warp - LG_EPI_WARPS;
+    const int sub = lane >> 3, j = lane & 7;
     int it = 0;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
       const int s = it & 1;
       if (!mbar_wait(&a_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 10)) break;
       uint8_t* tile = sA + s * LG_A_BYTES;
-      // 16 rows per batch: all loads of a batch are issued before any is consumed, which
-      // keeps 64 rows (32 KiB) in flight per SM across the four producer warps
 #pragma unroll 1
-      for (int r0 = 0; r0 < 32; r0 += 16) {
-        float4 vals[16];
+      for (int grp = 0; grp < 2; ++grp) {
+        float v[2][16];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int64_t r = t * LG_ROWS + pw * 32 + r0 + u;
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < 2; ++u) {
+          const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
+          const int64_t r = t * LG_ROWS + row;
           if (r < p.rows) {
             int64_t src = r;
             if (p.transpose) { int64_t b = r / p.Q, i = r % p.Q; src = i * p.batch + b; }
             if (p.act_bf16) {
-              const uint2 raw = reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K)[lane];
-              const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-              const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-              v = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K + 16 * j);
+#pragma unroll
+              for (int w4 = 0; w4 < 2; ++w4) {
+                const uint4 raw = g[w4];
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                  v[u][w4 * 8 + e * 2] = __low2float(h2);
+                  v[u][w4 * 8 + e * 2 + 1] = __high2float(h2);
+                }
+              }
             } else {
-              v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + src * LG_K)[lane];
+              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + src * LG_K + 16 * j);
+#pragma unroll
+              for (int w4 = 0; w4 < 4; ++w4) {
+                const float4 f = g[w4];
+                v[u][w4 * 4] = f.x; v[u][w4 * 4 + 1] = f.y; v[u][w4 * 4 + 2] = f.z; v[u][w4 * 4 + 3] = f.w;
+              }
             }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[u][e] = 0.f;
           }
-          vals[u] = v;
         }
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int row = pw * 32 + r0 + u;
+        for (int u = 0; u < 2; ++u) {
+          const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
           const bool valid = t * LG_ROWS + row < p.rows;
-          const float4 v = vals[u];
-          float sum = v.x + v.y + v.z + v.w;
+          float sum = 0.f;
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+          for (int e = 0; e < 16; ++e) sum += v[u][e];
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
           const float mean = sum * (1.0f / LG_K);
-          float var;
+          float sq = 0.f;
           if (p.variance == 2) {
-            float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            var = sq * (1.0f / LG_K) - mean * mean;
+            for (int e = 0; e < 16; ++e) sq = fmaf(v[u][e], v[u][e], sq);
           } else {
-            const float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
-            float sq = dx * dx + dy * dy + dz * dz + dw * dw;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            var = sq * (1.0f / LG_K);
+            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; sq = fmaf(d, d, sq); }
           }
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          const float var = p.variance == 2 ? sq * (1.0f / LG_K) - mean * mean : sq * (1.0f / LG_K);
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
-          uint2 packed = make_uint2(0u, 0u);
-          if (valid) {
-            packed.x = pack_half2((v.x - mean) * inv * g4.x + b4.x, (v.y - mean) * inv * g4.y + b4.y);
-            packed.y = pack_half2((v.z - mean) * inv * g4.z + b4.z, (v.w - mean) * inv * g4.w + b4.w);
+          uint32_t packed[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 gm = *reinterpret_cast<const float2*>(sGamma + 16 * j + 2 * e);
+            const float2 bt = *reinterpret_cast<const float2*>(sBeta + 16 * j + 2 * e);
+            packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
           }
-          // channels 4*lane .. 4*lane+3: k-atom lane/16, 16-byte chunk (lane%16)/2, 8-byte half lane%2
-          const uint32_t off = (uint32_t)(lane >> 4) * (LG_ROWS * 128) +
-                               swizzle128_offset((uint32_t)row, (uint32_t)((lane & 15) >> 1)) + (uint32_t)(lane & 1) * 8u;
-          *reinterpret_cast<uint2*>(tile + off) = packed;
+          // channels 16j .. 16j+15: k-atom j/4, 16-byte chunks 2*(j%4) and 2*(j%4)+1 of the row
+          uint8_t* base = tile + (uint32_t)(j >> 2) * (LG_ROWS * 128);
+          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2))) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2 + 1))) =
+              make_uint4(packed[4], packed[5], packed[6], packed[7]);
         }
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[s]);
     }
-  } else if (warp == 12) {
+  } else if (warp == LG_MMA_WARP) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       int it = 0;
@@ -188,13 +220,29 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
           const int b = g & 1;
           if (!mbar_wait(&acc_empty[b], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t idesc = make_idesc_f16(LG_ROWS, p.chunk_n[j], 0, 0);
-          const uint32_t w_addr = smem_u32(sW) + p.chunk_row0[j] * 128;
+          if (EPI == LG_EPI_TRIANGLE) {
+            // D[channel][pair row]: weights are the A operand (128 projection rows, then 128 gate
+            // rows of operand j), the normalised tile is the B operand (N = 128 pair rows)
+            const uint32_t idesc = make_idesc_f16(128, LG_ROWS, 0, 0);
 #pragma unroll
-          for (int kk = 0; kk < LG_K / 16; ++kk) {
-            const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (LG_ROWS * 128) + (kk & 3) * 32, 16, 1024);
-            const uint64_t bdesc = make_smem_desc(w_addr + (kk >> 2) * (p.n_pad * 128) + (kk & 3) * 32, 16, 1024);
-            umma_f16(tmem_base + b * 256, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
+            for (int grp = 0; grp < 2; ++grp) {
+              const uint32_t w_addr = smem_u32(sW) + (j * 256 + grp * 128) * 128;
+#pragma unroll
+              for (int kk = 0; kk < LG_K / 16; ++kk) {
+                const uint64_t wdesc = make_smem_desc(w_addr + (kk >> 2) * (p.n_pad * 128) + (kk & 3) * 32, 16, 1024);
+                const uint64_t xdesc = make_smem_desc(a_addr + (kk >> 2) * (LG_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+                umma_f16(tmem_base + b * 256 + grp * 128, wdesc, xdesc, idesc, kk != 0 ? 1u : 0u);
+              }
+            }
+          } else {
+            const uint32_t idesc = make_idesc_f16(LG_ROWS, p.chunk_n[j], 0, 0);
+            const uint32_t w_addr = smem_u32(sW) + p.chunk_row0[j] * 128;
+#pragma unroll
+            for (int kk = 0; kk < LG_K / 16; ++kk) {
+              const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (LG_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+              const uint64_t bdesc = make_smem_desc(w_addr + (kk >> 2) * (p.n_pad * 128) + (kk & 3) * 32, 16, 1024);
+              umma_f16(tmem_base + b * 256, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&acc_full[b]);
         }
@@ -204,7 +252,7 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
     }
   } else {
     // ---------------- epilogue ----------------
-    const int q = warp & 3, half = warp >> 2;
+    const int q = warp & 3, part = warp >> 2;   // part: which quarter of the chunk's columns
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint32_t g = 0;
@@ -218,48 +266,77 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
         tc_fence_after();
         const uint32_t acc = tmem_base + lane_addr + b * 256;
         if (EPI == LG_EPI_TRIANGLE) {
-          // chunk j = (projection h 0..127 | gate h 0..127) of operand j (0 = a, 1 = b)
-          const float m = valid ? p.mask[r] : 0.f;
-          const int64_t i = valid ? r / p.n : 0, k = valid ? r % p.n : 0;
-          op16* dst = (j == 0 ? p.out_a : p.out_b) + i * p.ld + k;
-          const int64_t plane = (int64_t)p.n * p.ld;
-          const float* bias = sBias + j * 256;
+          // TMEM lane = hidden channel h, columns = the tile's pair rows (projection at 0..127,
+          // gate at 128..255).  Each thread owns one channel and writes runs of consecutive k.
+          const int h = row;
+          const float bias_p = sBias[j * 256 + h], bias_g = sBias[j * 256 + 128 + h];
+          op16* plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.n * p.ld;
+          const bool vec = (p.n & 7) == 0;
 #pragma unroll 1
-          for (int h0 = half * 64; h0 < half * 64 + 64; h0 += 32) {
-            uint32_t pv[32], gv[32];
-            tmem_ld32(acc + h0, pv);
-            tmem_ld32(acc + 128 + h0, gv);
+          for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
+            uint32_t pv[16], gv[16];
+            tmem_ld16(acc + c0, pv);
+            tmem_ld16(acc + 128 + c0, gv);
             tmem_ld_wait();
-            if (valid) {
+            const int64_t r0 = t * LG_ROWS + c0;
 #pragma unroll
-              for (int e = 0; e < 32; ++e) {
-                const int h = h0 + e;
-                const float val = m * (__uint_as_float(pv[e]) + bias[h]) * sigmoid_fast(__uint_as_float(gv[e]) + bias[128 + h]);
-                dst[h * plane] = __float2half_rn(val);
+            for (int grp = 0; grp < 2; ++grp) {
+              const int64_t r8 = r0 + grp * 8;
+              if (r8 >= p.rows) break;
+              float val[8];
+              if (vec) {
+                const float4 m0 = __ldg(reinterpret_cast<const float4*>(p.mask + r8));
+                const float4 m1 = __ldg(reinterpret_cast<const float4*>(p.mask + r8) + 1);
+                const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  val[e] = mm[e] * (__uint_as_float(pv[grp * 8 + e]) + bias_p) * sigmoid_fast(__uint_as_float(gv[grp * 8 + e]) + bias_g);
+                uint4 pk;
+                pk.x = pack_half2(val[0], val[1]); pk.y = pack_half2(val[2], val[3]);
+                pk.z = pack_half2(val[4], val[5]); pk.w = pack_half2(val[6], val[7]);
+                const int64_t i = r8 / p.n, k = r8 % p.n;
+                *reinterpret_cast<uint4*>(plane_base + i * p.ld + k) = pk;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int64_t r = r8 + e;
+                  if (r < p.rows) {
+                    const float v1 = __ldg(p.mask + r) * (__uint_as_float(pv[grp * 8 + e]) + bias_p) *
+                                     sigmoid_fast(__uint_as_float(gv[grp * 8 + e]) + bias_g);
+                    plane_base[(r / p.n) * p.ld + r % p.n] = __float2half_rn(v1);
+                  }
+                }
               }
             }
           }
         } else {
           if (j < 2) {
-            // chunk 0 = (q | k), chunk 1 = (v | gate); this warp's half picks the tensor
-            op16* out = j == 0 ? (half == 0 ? p.out_q : p.out_k) : (half == 0 ? p.out_v : p.out_g);
-            const float* bias = sBias + j * 256 + half * 128;
-            const float mul = (j == 0 && half == 0) ? p.q_scale : 1.0f;
-            const bool gate = (j == 1 && half == 1);
+            // chunk 0 = (q | k), chunk 1 = (v | gate): parts 0,1 take the first tensor, 2,3 the second
+            const int second = part >> 1, col0 = (part & 1) * 64;
+            op16* out = j == 0 ? (second ? p.out_k : p.out_q) : (second ? p.out_g : p.out_v);
+            const float4* bias4 = reinterpret_cast<const float4*>(sBias + j * 256 + second * 128 + col0);
+            const bool gate = (j == 1 && second == 1);
+            const bool has_bias = (p.bias_flags >> (j * 2 + second)) & 1;
 #pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-              uint32_t v[32];
-              tmem_ld32(acc + half * 128 + c0, v);
+            for (int c0 = 0; c0 < 64; c0 += 16) {
+              uint32_t v[16];
+              tmem_ld16(acc + second * 128 + col0 + c0, v);
               tmem_ld_wait();
               if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(out + r * 128 + c0);
+                uint4* dst = reinterpret_cast<uint4*>(out + r * 128 + col0 + c0);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
+                for (int e = 0; e < 2; ++e) {
                   float f[8];
 #pragma unroll
-                  for (int u = 0; u < 8; ++u) {
-                    float x = __uint_as_float(v[e * 8 + u]) + bias[c0 + e * 8 + u];
-                    f[u] = gate ? sigmoid_fast(x) : x * mul;
+                  for (int u = 0; u < 8; ++u) f[u] = __uint_as_float(v[e * 8 + u]);
+                  if (has_bias) {
+                    const float4 b0 = bias4[(c0 >> 2) + e * 2], b1 = bias4[(c0 >> 2) + e * 2 + 1];
+                    f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+                    f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+                  }
+                  if (gate) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) f[u] = sigmoid_fast(f[u]);
                   }
                   uint4 pk;
                   pk.x = pack_half2(f[0], f[1]); pk.y = pack_half2(f[2], f[3]);
@@ -268,7 +345,7 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
                 }
               }
             }
-          } else if (half == 0) {
+          } else if (part == 0) {
             // chunk 2: pair bias, one column per head; logical row r = (q index, k index)
             uint32_t v[16];
             tmem_ld16(acc, v);
@@ -293,27 +370,28 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) drain_after_abort();
-  if (warp == 12) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == LG_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // W (in,out) float32 [K][n_out] -> fp16 image of W^T in the swizzled K-major layout
 // ([K/64 atoms][n_pad rows][128 B]); rows >= n_out are zero.
 __global__ void pack_weight_image_kernel(const float* __restrict__ w, int K, int n_out, int n_pad, int col0, int ld,
-                                         op16* __restrict__ img, int row0) {
+                                         op16* __restrict__ img, int row0, float scale) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_out * K) return;
   int n = idx / K, k = idx % K;
   int row = row0 + n;
   size_t off = (size_t)(k >> 6) * ((size_t)n_pad * 128) + (size_t)row * 128 + ((((k & 63) >> 3) ^ (row & 7)) << 4) + (k & 7) * 2;
-  img[off / 2] = __float2half_rn(w[(size_t)k * ld + col0 + n]);
+  img[off / 2] = __float2half_rn(w[(size_t)k * ld + col0 + n] * scale);
 }
 
-void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0) {
+void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0,
+                       float scale) {
   int total = n_out * K;
-  pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0);
+  pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0, scale);
 }
 
-static int ln_gemm_smem(int n_pad) { return n_pad * 256 + 2 * LG_A_BYTES + 544 * 4 + 128 + 1024; }
+static int ln_gemm_smem(int n_pad) { return n_pad * 256 + 2 * LG_A_BYTES + (544 + 256) * 4 + 128 + 1024; }
 
 void configure_ln_gemm() {
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512));
@@ -351,7 +429,8 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
   p.chunk_row0[0] = 0; p.chunk_row0[1] = 256; p.chunk_row0[2] = 512;
   p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.heads = heads; p.bias_swap = bias_swap;
-  p.q_scale = 1.0f / sqrtf((float)head_dim);
+  p.bias_flags = w->bias_flags;
+  (void)head_dim;
   p.status = (Status*)ctx->tc_status;
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
