@@ -529,7 +529,7 @@ template <typename T>
 lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   const int64_t P = (int64_t)a.n * a.n;
   const int cz = a.cz, c = a.c, n = a.n;
-  const int ld = (n + 7) / 8 * 8;           // TMA row strides are multiples of 16 bytes
+  const int ld = (n + 15) / 16 * 16;        // rows start on 32-byte boundaries (TMA needs 16, the 256-bit stores 32)
   const int64_t plane = (int64_t)n * ld;
   const auto& f = a.w->f;
   float* zn = cur.take<float>(P * cz);
@@ -627,16 +627,16 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   op16* k = cur.take<op16>(R * HD);
   op16* v = cur.take<op16>(R * HD);
   op16* g = cur.take<op16>(R * HD);
-  float* bias = a.bias_mode ? cur.take<float>((int64_t)a.heads * a.Q * a.Q) : nullptr;
-  float* qkvg = cur.take<float>(R * 4 * HD);
+  const int ldb = (a.Q + 7) / 8 * 8;
+  op16* bias = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
+  op16* o16 = cur.take<op16>(R * HD);
   float* o = cur.take<float>(R * HD);
   float* proj = cur.take<float>(R * c);
+  if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
   LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
-                               a.bias_swap, a.w, q, k, v, g, bias));
-  LAUNCH(ctx, cur, simt::unpack_qkvg_kernel, lf_ceil_div(R * HD, 256), 256, 0, q, k, v, g, R, HD, qkvg);
-  size_t smem = (size_t)(2 * 32 * (a.d + 1) + 8 * a.d) * sizeof(float);
-  LAUNCH(ctx, cur, simt::attention_kernel, dim3(lf_ceil_div(a.Q, 8), a.batch, a.heads), 256, smem, qkvg, bias, a.mask,
-         a.batch, a.Q, a.heads, a.d, a.transpose, a.mask_mode, a.clamp, 1.0f, o);
+                               a.bias_swap, a.w, q, k, v, g, bias, ldb));
+  LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
+  LAUNCH(ctx, cur, (simt::to_float_kernel<op16>), lf_ceil_div(R * HD, 256), 256, 0, o16, R * HD, o);
   sgemm(ctx, cur, false, false, 0, (int)R, c, HD, o, HD, 0, f[ATT_WO], c, 0, proj, c, 0, f[ATT_BO], 0, 1);
   LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
          a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
@@ -644,7 +644,7 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
 }
 
 lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int precision) {
-  if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && tc::ln_gemm_supported(a.w)) {
+  if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && a.heads == 4 && a.d == 32 && tc::ln_gemm_supported(a.w)) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
   }
   if (a.act_dtype == LF_DTYPE_BF16) att_f32<bf16>(ctx, cur, a); else att_f32<float>(ctx, cur, a);

@@ -39,6 +39,11 @@ static lf_status make_map_f16_3d(lf_context* ctx, CUtensorMap* map, const void* 
   return LF_OK;
 }
 
+lf_status make_map_f16_3d_ext(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1) {
+  return make_map_f16_3d(ctx, map, base, d0, d1, d2, stride1_bytes, stride2_bytes, b0, b1);
+}
+
 lf_status check_status(lf_context* ctx) {
   if (!ctx->tc_status) return LF_OK;
   Status st;
@@ -268,6 +273,7 @@ void configure_once() {
     cudaFuncSetAttribute(contract_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     configure_ln_gemm();
+    configure_attention();
     cudaGetLastError();
   });
 }

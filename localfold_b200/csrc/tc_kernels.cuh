@@ -30,9 +30,14 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
                            int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 [batch*Q][128] in logical row order and the
-// pair bias [heads][Q][Q] float32 (null = none) from the normalised input
+// pair bias [heads][Q][ldb] fp16 (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
-                            const lf_weights* w, op16* q, op16* k, op16* v, op16* g, float* bias);
+                            const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
+// out[b*Q+i][128] = (softmax_j(q_i.k_j + bias[h][i][j] + mask term_j) v_j) * gate, 4 heads x 32
+void configure_attention();
+lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,
+                         const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose, int mask_mode,
+                         int clamp, op16* out);
 
 }  // namespace tc

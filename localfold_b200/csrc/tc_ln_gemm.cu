@@ -50,7 +50,8 @@ struct LnGemmParams {
   int n, ld;
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
-  float* out_bias;          // [heads][Q][Q]
+  op16* out_bias;           // [heads][Q][ldb] fp16
+  int ldb;
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
   Status* status;
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
           const int64_t r = t * LG_ROWS + row;
           if (r < p.rows) {
             int64_t src = r;
-            if (p.transpose) { int64_t b = r / p.Q, i = r % p.Q; src = i * p.batch + b; }
+            if (p.transpose) { const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q; src = (int64_t)(ur % uq) * p.batch + ur / uq; }
             if (p.act_bf16) {
               const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K + 16 * j);
 #pragma unroll
@@ -271,43 +272,48 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
           const int h = row;
           const float bias_p = sBias[j * 256 + h], bias_g = sBias[j * 256 + 128 + h];
           op16* plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.n * p.ld;
-          const bool vec = (p.n & 7) == 0;
+          const bool vec = (p.n & 15) == 0;
+          const uint32_t un = (uint32_t)p.n;
+          // rows of this warp's quarter: r0 .. r0+31, as (i, k) with 32-bit arithmetic
+          const uint32_t r0 = (uint32_t)(t * LG_ROWS) + part * 32;
+          uint32_t ii = r0 / un, kk0 = r0 % un;
 #pragma unroll 1
           for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
             uint32_t pv[16], gv[16];
             tmem_ld16(acc + c0, pv);
             tmem_ld16(acc + 128 + c0, gv);
             tmem_ld_wait();
-            const int64_t r0 = t * LG_ROWS + c0;
-#pragma unroll
-            for (int grp = 0; grp < 2; ++grp) {
-              const int64_t r8 = r0 + grp * 8;
-              if (r8 >= p.rows) break;
-              float val[8];
+            const int64_t r16 = t * LG_ROWS + c0;
+            if (r16 < p.rows) {
               if (vec) {
-                const float4 m0 = __ldg(reinterpret_cast<const float4*>(p.mask + r8));
-                const float4 m1 = __ldg(reinterpret_cast<const float4*>(p.mask + r8) + 1);
-                const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+                const float4* m4 = reinterpret_cast<const float4*>(p.mask + r16);
+                uint32_t pk[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  val[e] = mm[e] * (__uint_as_float(pv[grp * 8 + e]) + bias_p) * sigmoid_fast(__uint_as_float(gv[grp * 8 + e]) + bias_g);
-                uint4 pk;
-                pk.x = pack_half2(val[0], val[1]); pk.y = pack_half2(val[2], val[3]);
-                pk.z = pack_half2(val[4], val[5]); pk.w = pack_half2(val[6], val[7]);
-                const int64_t i = r8 / p.n, k = r8 % p.n;
-                *reinterpret_cast<uint4*>(plane_base + i * p.ld + k) = pk;
+                for (int g4 = 0; g4 < 4; ++g4) {
+                  const float4 m = __ldg(m4 + g4);
+                  const float mm[4] = {m.x, m.y, m.z, m.w};
+                  float val[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    val[e] = mm[e] * (__uint_as_float(pv[g4 * 4 + e]) + bias_p) * sigmoid_fast(__uint_as_float(gv[g4 * 4 + e]) + bias_g);
+                  pk[g4 * 2] = pack_half2(val[0], val[1]);
+                  pk[g4 * 2 + 1] = pack_half2(val[2], val[3]);
+                }
+                st_global_v8(plane_base + (int64_t)ii * p.ld + kk0, pk);
               } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int64_t r = r8 + e;
+                for (int e = 0; e < 16; ++e) {
+                  const int64_t r = r16 + e;
                   if (r < p.rows) {
-                    const float v1 = __ldg(p.mask + r) * (__uint_as_float(pv[grp * 8 + e]) + bias_p) *
-                                     sigmoid_fast(__uint_as_float(gv[grp * 8 + e]) + bias_g);
-                    plane_base[(r / p.n) * p.ld + r % p.n] = __float2half_rn(v1);
+                    const uint32_t ur = (uint32_t)r;
+                    const float v1 = __ldg(p.mask + r) * (__uint_as_float(pv[e]) + bias_p) * sigmoid_fast(__uint_as_float(gv[e]) + bias_g);
+                    plane_base[(int64_t)(ur / un) * p.ld + ur % un] = __float2half_rn(v1);
                   }
                 }
               }
             }
+            kk0 += 16;
+            if (kk0 >= un) { kk0 -= un; ++ii; }
           }
         } else {
           if (j < 2) {
@@ -323,26 +329,24 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
               tmem_ld16(acc + second * 128 + col0 + c0, v);
               tmem_ld_wait();
               if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(out + r * 128 + col0 + c0);
+                float f[16];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  float f[8];
+                for (int u = 0; u < 16; ++u) f[u] = __uint_as_float(v[u]);
+                if (has_bias) {
 #pragma unroll
-                  for (int u = 0; u < 8; ++u) f[u] = __uint_as_float(v[e * 8 + u]);
-                  if (has_bias) {
-                    const float4 b0 = bias4[(c0 >> 2) + e * 2], b1 = bias4[(c0 >> 2) + e * 2 + 1];
-                    f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
-                    f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+                  for (int u4 = 0; u4 < 4; ++u4) {
+                    const float4 bb = bias4[(c0 >> 2) + u4];
+                    f[u4 * 4] += bb.x; f[u4 * 4 + 1] += bb.y; f[u4 * 4 + 2] += bb.z; f[u4 * 4 + 3] += bb.w;
                   }
-                  if (gate) {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) f[u] = sigmoid_fast(f[u]);
-                  }
-                  uint4 pk;
-                  pk.x = pack_half2(f[0], f[1]); pk.y = pack_half2(f[2], f[3]);
-                  pk.z = pack_half2(f[4], f[5]); pk.w = pack_half2(f[6], f[7]);
-                  dst[e] = pk;
                 }
+                if (gate) {
+#pragma unroll
+                  for (int u = 0; u < 16; ++u) f[u] = sigmoid_fast(f[u]);
+                }
+                uint32_t pk[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) pk[u] = pack_half2(f[2 * u], f[2 * u + 1]);
+                st_global_v8(out + r * 128 + col0 + c0, pk);
               }
             }
           } else if (part == 0) {
@@ -351,12 +355,13 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
             tmem_ld16(acc, v);
             tmem_ld_wait();
             if (valid) {
-              const int64_t qi = r / p.Q, ki = r % p.Q;
-              const int64_t dst = p.bias_swap ? ki * p.Q + qi : r;
-              const int64_t qq = (int64_t)p.Q * p.Q;
+              const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q;
+              const int64_t qi = ur / uq, ki = ur % uq;
+              const int64_t dst = p.bias_swap ? ki * p.ldb + qi : qi * p.ldb + ki;
+              const int64_t qq = (int64_t)p.Q * p.ldb;
 #pragma unroll
               for (int h = 0; h < 16; ++h)
-                if (h < p.heads) p.out_bias[h * qq + dst] = __uint_as_float(v[h]);
+                if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]));
             }
           }
         }
@@ -419,7 +424,7 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
 
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
-                            const lf_weights* w, op16* q, op16* k, op16* v, op16* g, float* bias) {
+                            const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb) {
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
   p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
@@ -428,7 +433,7 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   p.n_chunks = bias ? 3 : 2;
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
   p.chunk_row0[0] = 0; p.chunk_row0[1] = 256; p.chunk_row0[2] = 512;
-  p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.heads = heads; p.bias_swap = bias_swap;
+  p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.ldb = ldb; p.heads = heads; p.bias_swap = bias_swap;
   p.bias_flags = w->bias_flags;
   (void)head_dim;
   p.status = (Status*)ctx->tc_status;

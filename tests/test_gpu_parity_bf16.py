@@ -62,7 +62,7 @@ def test_af2_pair_block_bf16(dev):
     assert oracle.relative_l2(got["pair"], want) <= BLOCK_TOL
 
 
-@pytest.mark.parametrize("n", [64, 77])
+@pytest.mark.parametrize("n", [64, 77, 260])
 @pytest.mark.parametrize("transpose", [False, True])
 def test_triangle_attention_af2_bf16(dev, n, transpose):
     import localfold_b200 as lf
@@ -90,4 +90,24 @@ def test_grid_attention_af3_bf16(dev, transpose, swap):
     got = lf.Af3GridSelfAttentionGpu(dev).run(z, mask, {"n": n, "channels": 128, "transpose": transpose}, w,
                                               {"swapTransposedBias": swap}, {"precision": "bf16"})["output"]
     want = oracle.grid_attention_af3(z, mask, w, transpose, swap)
+    assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+def test_triangle_attention_bf16_fully_masked_row(dev):
+    """A residue masked out everywhere: its row of the pair mask is all zero, so every key of
+    that batch row is masked and the softmax must come out uniform, not 0/0."""
+    import localfold_b200 as lf
+    n = 150
+    d = syn.draw(700)
+    z = d.normal(n, n, 128)
+    res = np.ones(n, np.float32)
+    res[[3, 77, 149]] = 0
+    mask = np.outer(res, res).astype(np.float32)
+    t = syn.af2_attention_weights(d, 128, 4, 128)
+    pb = dict(t["pairBias"], source="normalized-input")
+    inp = {"activations": z, "mask": mask, "batch": n, "queryLength": n, "channels": 128, "heads": 4,
+           "weights": t["attention"], "pairBias": pb}
+    got = lf.AttentionGpu(dev).run(inp, {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], False, pb)
+    assert np.isfinite(got).all()
     assert oracle.relative_l2(got, want) <= OP_TOL
