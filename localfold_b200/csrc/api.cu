@@ -537,8 +537,9 @@ lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   op16* ga = cur.take<op16>(plane * c);
   op16* gb = cur.take<op16>(plane * c);
   op16* x = cur.take<op16>(plane * c);
-  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
-         f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
+  if (!tc::ln_gemm_supported(a.w))
+    LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
+           f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
   if (tc::ln_gemm_supported(a.w)) {
     LF_TRY(tc::triangle_project(ctx, cur, a.z, a.act_dtype, a.mask, n, ld, a.variance, a.eps, a.w, ga, gb));
   } else {
@@ -550,6 +551,12 @@ lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   // stay far from the fp16 limits; the centre LayerNorm undoes the scale exactly.
   const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
   LF_TRY(tc::contract(ctx, cur, ga, gb, x, n, ld, c, a.incoming, xscale));
+  if (tc::ln_gemm_supported(a.w)) {
+    const float xs = xscale * (a.divide ? (float)n : 1.0f);
+    LF_TRY(tc::triangle_output(ctx, cur, x, n, ld, a.eps * xs * xs, a.z, a.act_dtype, a.variance, a.eps, a.w,
+                               a.residual ? a.z : nullptr, a.out));
+    return LF_OK;
+  }
   float* xn = p4;
   float* proj = p4 + P * c;
   float* gate = p4 + P * c + P * cz;
@@ -630,16 +637,12 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   const int ldb = (a.Q + 7) / 8 * 8;
   op16* bias = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
   op16* o16 = cur.take<op16>(R * HD);
-  float* o = cur.take<float>(R * HD);
-  float* proj = cur.take<float>(R * c);
   if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
   LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
                                a.bias_swap, a.w, q, k, v, g, bias, ldb));
   LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
-  LAUNCH(ctx, cur, (simt::to_float_kernel<op16>), lf_ceil_div(R * HD, 256), 256, 0, o16, R * HD, o);
-  sgemm(ctx, cur, false, false, 0, (int)R, c, HD, o, HD, 0, f[ATT_WO], c, 0, proj, c, 0, f[ATT_BO], 0, 1);
-  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
-         a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
+  LF_TRY(tc::attention_output(ctx, cur, o16, a.batch, a.Q, a.transpose, a.w, a.residual ? a.act : nullptr, a.out, a.act_dtype));
+  (void)f; (void)c;
   return LF_OK;
 }
 

@@ -2,6 +2,7 @@
 #include "tc_kernels.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <cmath>
 #include <mutex>
@@ -24,19 +25,23 @@ static std::once_flag g_once;
 
 void configure_once();
 
-static lf_status make_map_f16_3d(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1,
-                                  uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0,
-                                  uint32_t b1) {
+lf_status make_map_f16_3d_box(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2) {
   if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
-  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return LF_OK;
+}
+
+static lf_status make_map_f16_3d(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1,
+                                 uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1) {
+  return make_map_f16_3d_box(ctx, map, base, d0, d1, d2, stride1_bytes, stride2_bytes, b0, b1, 1);
 }
 
 lf_status make_map_f16_3d_ext(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
@@ -69,8 +74,40 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->owned.push_back(img);
     LF_CUDA(ctx, cudaMemsetAsync(img, 0, 512 * 256, ctx->stream));
     pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0, 1.0f);
-    w->h.assign(2, nullptr);
+    w->h.assign(4, nullptr);
     w->h[0] = img;
+    // output kernel: rows 0..127 = (diag(gain) Wz)^T, rows 128..255 = Wg^T, plus the folded vectors
+    std::vector<float> wz(128 * 128), g(128), b(128), bz(128), bg(128), fold(384);
+    LF_CUDA(ctx, cudaMemcpyAsync(wz.data(), w->f[TRI_WZ], wz.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(g.data(), w->f[TRI_LNO_G], 512, cudaMemcpyDeviceToHost, ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(b.data(), w->f[TRI_LNO_B], 512, cudaMemcpyDeviceToHost, ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(bz.data(), w->f[TRI_BZ], 512, cudaMemcpyDeviceToHost, ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(bg.data(), w->f[TRI_BG], 512, cudaMemcpyDeviceToHost, ctx->stream));
+    LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    std::vector<float> wfold(128 * 128);
+    for (int cc = 0; cc < 128; ++cc) {
+      double s1 = 0, t = bz[cc];
+      for (int h = 0; h < 128; ++h) {
+        const float wf = g[h] * wz[h * 128 + cc];
+        wfold[h * 128 + cc] = wf;
+        s1 += (double)__half2float(__float2half_rn(wf));   // what the tensor core will multiply by
+        t += (double)b[h] * wz[h * 128 + cc];
+      }
+      fold[cc] = (float)s1;
+      fold[128 + cc] = (float)t;
+      fold[256 + cc] = bg[cc];
+    }
+    float* dfold = nullptr; float* dw = nullptr; op16* img2 = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&dfold, fold.size() * 4)); w->owned.push_back(dfold);
+    LF_CUDA(ctx, cudaMalloc(&dw, wfold.size() * 4)); w->owned.push_back(dw);
+    LF_CUDA(ctx, cudaMalloc(&img2, 256 * 256)); w->owned.push_back(img2);
+    LF_CUDA(ctx, cudaMemcpyAsync(dfold, fold.data(), fold.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LF_CUDA(ctx, cudaMemcpyAsync(dw, wfold.data(), wfold.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    pack_weight_image(ctx, dw, 128, 128, 256, 0, 128, img2, 0, 1.0f);
+    pack_weight_image(ctx, w->f[TRI_WG], 128, 128, 256, 0, 128, img2, 128, 1.0f);
+    LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    w->h[2] = img2;
+    w->h[3] = dfold;
   } else if (att && w->dims.channels == 128 && w->dims.heads * w->dims.head_dim == 128 && w->dims.heads <= 16 &&
              !w->has_pair_norm) {
     op16* img = nullptr;
@@ -98,9 +135,13 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
       LF_CUDA(ctx, cudaMemcpyAsync(bias, hb.data(), 512 * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
       LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
-    w->h.assign(2, nullptr);
+    w->h.assign(4, nullptr);
     w->h[0] = img;
     w->h[1] = bias;
+    op16* img2 = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img2, 128 * 256)); w->owned.push_back(img2);
+    pack_weight_image(ctx, w->f[ATT_WO], 128, 128, 128, 0, 128, img2, 0, 1.0f);
+    w->h[2] = img2;
   }
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return LF_OK;

@@ -34,6 +34,10 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
+lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,
+                           const lf_weights* w, const void* resid, void* out, int act_dtype);
+lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int n, int ld, float x_eps, const void* z,
+                          int act_dtype, int variance, float eps, const lf_weights* w, const void* resid, void* out);
 // out[b*Q+i][128] = (softmax_j(q_i.k_j + bias[h][i][j] + mask term_j) v_j) * gate, 4 heads x 32
 void configure_attention();
 lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,

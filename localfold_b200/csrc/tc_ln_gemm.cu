@@ -39,7 +39,8 @@ struct LnGemmParams {
   int variance;             // 1 two-pass, 2 fast
   const uint8_t* wimg;      // swizzled fp16 image of W^T: [2 atoms][n_pad rows][128 B]
   int n_pad;
-  const float* bias;        // [n_pad]
+  const float* bias;        // [n_bias]
+  int n_bias;
   int n_chunks;
   int chunk_n[LG_MAX_CHUNKS];
   int chunk_row0[LG_MAX_CHUNKS];
@@ -54,10 +55,18 @@ struct LnGemmParams {
   int ldb;
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
+  // output epilogues (attention output projection, triangle output): out = resid + f(acc)
+  int a_is_op16;            // the A operand is an fp16 [rows][128] tensor copied as is (no LayerNorm)
+  const void* resid;        // pair rows (memory order) to add, or null
+  void* out;                // pair rows written in the same memory order
+  int out_bf16;
+  // triangle output: tiles follow pair rows (i, 128 k's); x is fetched by TMA as an MN-major operand
+  int tile_per_row;         // tiles per pair row i (0 = rows are tiled linearly)
+  float x_eps;              // epsilon of the centre LayerNorm in the units x is stored in
   Status* status;
 };
 
-enum { LG_EPI_TRIANGLE = 0, LG_EPI_ATTENTION = 1 };
+enum { LG_EPI_TRIANGLE = 0, LG_EPI_ATTENTION = 1, LG_EPI_OUTPUT = 2, LG_EPI_TRI_OUT = 3 };
 
 // sigmoid(v) = 0.5 + 0.5 * tanh(v / 2): one MUFU operation.  tanh.approx.f32 has a relative
 // error of 2^-11, so the gate is good to about 2.4e-4 absolute - the precision of the fp16
@@ -68,29 +77,51 @@ __device__ __forceinline__ float sigmoid_fast(float v) {
   return fmaf(0.5f, t, 0.5f);
 }
 
+// Rows of tile t: linear tiling, or (i, k-tile) tiles that never straddle a pair row.
+__device__ __forceinline__ void tile_rows(const LnGemmParams& p, int64_t t, int64_t& base, int& count) {
+  if (p.tile_per_row) {
+    const int64_t i = t / p.tile_per_row;
+    const int kt = (int)(t % p.tile_per_row);
+    base = i * p.n + (int64_t)kt * LG_ROWS;
+    const int left = p.n - kt * LG_ROWS;
+    count = left < LG_ROWS ? left : LG_ROWS;
+  } else {
+    base = t * LG_ROWS;
+    const int64_t left = p.rows - base;
+    count = left < LG_ROWS ? (int)left : LG_ROWS;
+  }
+}
+
 template <int EPI>
-__global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmParams p) {
+__global__ void __launch_bounds__(LG_THREADS, 1)
+ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int w_bytes = p.n_pad * 256;
   uint8_t* sW = smem;
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
-  float* sBias = reinterpret_cast<float*>(sA + 2 * LG_A_BYTES);
+  uint8_t* sX = sA + 2 * LG_A_BYTES;                  // triangle output only: 2 stages of the raw x tile
+  float* sBias = reinterpret_cast<float*>(sX + (EPI == LG_EPI_TRI_OUT ? 2 * LG_A_BYTES : 0));
+  float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
   float* sGamma = sBias + 544;      // [128]
   float* sBeta = sGamma + 128;      // [128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sBeta + 128);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 512);
   uint64_t* a_full = bars;          // [2]
   uint64_t* a_empty = bars + 2;     // [2]
   uint64_t* acc_full = bars + 4;    // [2]
   uint64_t* acc_empty = bars + 6;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* x_full = bars + 8;      // [2] TMA bytes of the x tile
+  uint64_t* stat_full = bars + 10;  // [2] row statistics of the x tile written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int64_t tiles = p.tile_per_row ? (int64_t)p.n * p.tile_per_row : (p.rows + LG_ROWS - 1) / LG_ROWS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&stat_full[s], 4);
       mbar_init(&a_full[s], LG_PROD_WARPS);
       mbar_init(&a_empty[s], 1);
       mbar_init(&acc_full[s], 1);
@@ -104,7 +135,7 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
     const uint4* src = reinterpret_cast<const uint4*>(p.wimg);
     uint4* dst = reinterpret_cast<uint4*>(sW);
     for (int i = threadIdx.x; i < w_bytes / 16; i += LG_THREADS) dst[i] = src[i];
-    for (int i = threadIdx.x; i < p.n_pad; i += LG_THREADS) sBias[i] = p.bias[i];
+    for (int i = threadIdx.x; i < p.n_bias; i += LG_THREADS) sBias[i] = p.bias[i];
     if (threadIdx.x < 128) { sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
     fence_async_smem();
   }
@@ -126,17 +157,40 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
       const int s = it & 1;
       if (!mbar_wait(&a_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 10)) break;
       uint8_t* tile = sA + s * LG_A_BYTES;
+      int64_t row_base;
+      int row_count;
+      tile_rows(p, t, row_base, row_count);
+      if (EPI == LG_EPI_TRI_OUT && pw == 0 && lane == 0) {
+        // x[h][i][k0 .. k0+127] for all 128 channels: two boxes of 64 pairs x 128 channels
+        const int i = (int)(t / p.tile_per_row), k0 = (int)(t % p.tile_per_row) * LG_ROWS;
+        mbar_expect_tx(&x_full[s], LG_A_BYTES);
+        tma_load_3d(sX + s * LG_A_BYTES, &mapX, &x_full[s], k0, i, 0);
+        tma_load_3d(sX + s * LG_A_BYTES + LG_A_BYTES / 2, &mapX, &x_full[s], k0 + 64, i, 0);
+      }
 #pragma unroll 1
       for (int grp = 0; grp < 2; ++grp) {
         float v[2][16];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
-          const int64_t r = t * LG_ROWS + row;
-          if (r < p.rows) {
+          const int64_t r = row_base + row;
+          if (row < row_count) {
             int64_t src = r;
-            if (p.transpose) { const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q; src = (int64_t)(ur % uq) * p.batch + ur / uq; }
-            if (p.act_bf16) {
+            if (p.transpose && !p.a_is_op16) { const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q; src = (int64_t)(ur % uq) * p.batch + ur / uq; }
+            if (p.a_is_op16) {
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const op16*>(p.act) + src * LG_K + 16 * j);
+#pragma unroll
+              for (int w4 = 0; w4 < 2; ++w4) {
+                const uint4 raw = g[w4];
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&words[e]));
+                  v[u][w4 * 8 + e * 2] = f2.x;
+                  v[u][w4 * 8 + e * 2 + 1] = f2.y;
+                }
+              }
+            } else if (p.act_bf16) {
               const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K + 16 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 2; ++w4) {
@@ -165,7 +219,12 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
-          const bool valid = t * LG_ROWS + row < p.rows;
+          const bool valid = row < row_count;
+          uint32_t packed[8];
+          if (p.a_is_op16) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) packed[e] = pack_half2(v[u][2 * e], v[u][2 * e + 1]);
+          } else {
           float sum = 0.f;
 #pragma unroll
           for (int e = 0; e < 16; ++e) sum += v[u][e];
@@ -187,12 +246,12 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
           const float var = p.variance == 2 ? sq * (1.0f / LG_K) - mean * mean : sq * (1.0f / LG_K);
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
-          uint32_t packed[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float2 gm = *reinterpret_cast<const float2*>(sGamma + 16 * j + 2 * e);
             const float2 bt = *reinterpret_cast<const float2*>(sBeta + 16 * j + 2 * e);
             packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
+          }
           }
           // channels 16j .. 16j+15: k-atom j/4, 16-byte chunks 2*(j%4) and 2*(j%4)+1 of the row
           uint8_t* base = tile + (uint32_t)(j >> 2) * (LG_ROWS * 128);
@@ -205,6 +264,30 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[s]);
+      if (EPI == LG_EPI_TRI_OUT && pw < 4) {
+        // statistics of the centre LayerNorm: one thread per pair reads its 128 channels from the
+        // raw x tile (row h of the tile = 128 bytes of 64 pairs, 128-byte swizzled)
+        if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 14)) break;
+        const int pr = pw * 32 + lane;
+        const uint8_t* xt = sX + s * LG_A_BYTES + (pr >> 6) * (LG_A_BYTES / 2);
+        const uint32_t chunk = (uint32_t)((pr & 63) >> 3), within = (uint32_t)(pr & 7) * 2u;
+        float sum = 0.f, sq = 0.f;
+#pragma unroll 8
+        for (int h = 0; h < 128; ++h) {
+          const float xv = __half2float(*reinterpret_cast<const __half*>(xt + swizzle128_offset((uint32_t)h, chunk) + within));
+          sum += xv;
+          sq = fmaf(xv, xv, sq);
+        }
+        const float mean = sum * (1.0f / 128.0f);
+        float var = sq * (1.0f / 128.0f) - mean * mean;
+        if (p.variance != 2) var = fmaxf(var, 0.f);
+        float inv = rsqrtf(var + p.x_eps);
+        inv = inv * (1.5f - 0.5f * (var + p.x_eps) * inv * inv);
+        sStat[s * 256 + pr] = inv;
+        sStat[s * 256 + 128 + pr] = inv * mean;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stat_full[s]);
+      }
     }
   } else if (warp == LG_MMA_WARP) {
     // ---------------- MMA issuer ----------------
@@ -235,6 +318,28 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
                 umma_f16(tmem_base + b * 256 + grp * 128, wdesc, xdesc, idesc, kk != 0 ? 1u : 0u);
               }
             }
+          } else if (EPI == LG_EPI_TRI_OUT) {
+            // columns 0..127: x tile (MN-major A, raw) times the gain-folded output projection;
+            // columns 128..255: normalised pair tile (K-major A) times the output gate weights
+            if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 15) ||
+                !mbar_wait(&stat_full[s], (it >> 1) & 1, abort_flag, p.status, 16)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t x_addr = smem_u32(sX + s * LG_A_BYTES);
+            const uint32_t w_addr = smem_u32(sW);
+            const uint32_t idesc_x = make_idesc_f16(LG_ROWS, 128, 1, 0);
+            const uint32_t idesc_z = make_idesc_f16(LG_ROWS, 128, 0, 0);
+#pragma unroll
+            for (int kk = 0; kk < LG_K / 16; ++kk) {
+              const uint64_t adesc = make_smem_desc(x_addr + kk * 2048, LG_A_BYTES / 2, 1024);
+              const uint64_t bdesc = make_smem_desc(w_addr + (kk >> 2) * (p.n_pad * 128) + (kk & 3) * 32, 16, 1024);
+              umma_f16(tmem_base + b * 256, adesc, bdesc, idesc_x, kk != 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kk = 0; kk < LG_K / 16; ++kk) {
+              const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (LG_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+              const uint64_t bdesc = make_smem_desc(w_addr + 128 * 128 + (kk >> 2) * (p.n_pad * 128) + (kk & 3) * 32, 16, 1024);
+              umma_f16(tmem_base + b * 256 + 128, adesc, bdesc, idesc_z, kk != 0 ? 1u : 0u);
+            }
           } else {
             const uint32_t idesc = make_idesc_f16(LG_ROWS, p.chunk_n[j], 0, 0);
             const uint32_t w_addr = smem_u32(sW) + p.chunk_row0[j] * 128;
@@ -258,9 +363,13 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint32_t g = 0;
     bool ok = true;
-    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-      const int64_t r = t * LG_ROWS + row;
-      const bool valid = r < p.rows;
+    int it = 0;
+    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+      int64_t row_base;
+      int row_count;
+      tile_rows(p, t, row_base, row_count);
+      const int64_t r = row_base + row;
+      const bool valid = row < row_count;
       for (int j = 0; j < p.n_chunks; ++j, ++g) {
         const int b = g & 1;
         if (!mbar_wait(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
@@ -314,6 +423,81 @@ __global__ void __launch_bounds__(LG_THREADS, 1) ln_gemm_kernel(const LnGemmPara
             }
             kk0 += 16;
             if (kk0 >= un) { kk0 -= un; ++ii; }
+          }
+        } else if (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) {
+          // thread = pair row; this warp's quarter = 32 output channels, two runs of 16
+          int64_t dst = r;
+          if (EPI == LG_EPI_OUTPUT && p.transpose && valid) {
+            const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q;
+            dst = (int64_t)(ur % uq) * p.batch + ur / uq;
+          }
+          float rs = 0.f, rm = 0.f;
+          if (EPI == LG_EPI_TRI_OUT) {
+            if (!mbar_wait(&stat_full[it & 1], (it >> 1) & 1, abort_flag, p.status, 17)) { ok = false; break; }
+            rs = sStat[(it & 1) * 256 + row];
+            rm = sStat[(it & 1) * 256 + 128 + row];
+          }
+#pragma unroll 1
+          for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
+            uint32_t v1[16], v2[16];
+            tmem_ld16(acc + c0, v1);
+            if (EPI == LG_EPI_TRI_OUT) tmem_ld16(acc + 128 + c0, v2);
+            tmem_ld_wait();
+            if (valid) {
+              float o[16];
+              if (EPI == LG_EPI_TRI_OUT) {
+                // (x - mean) * inv folded: inv * acc - inv*mean * s1[c] + t[c], gated
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                  const float lin = fmaf(rs, __uint_as_float(v1[e]), fmaf(-rm, sBias[c0 + e], sBias[128 + c0 + e]));
+                  o[e] = lin * sigmoid_fast(__uint_as_float(v2[e]) + sBias[256 + c0 + e]);
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v1[e]) + sBias[c0 + e];
+              }
+              if (p.out_bf16) {
+                bf16* op = reinterpret_cast<bf16*>(p.out) + dst * 128 + c0;
+                if (p.resid) {
+                  const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.resid) + dst * 128 + c0);
+#pragma unroll
+                  for (int w4 = 0; w4 < 2; ++w4) {
+                    const uint4 raw = rp[w4];
+                    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                      o[w4 * 8 + e * 2] += __low2float(h2);
+                      o[w4 * 8 + e * 2 + 1] += __high2float(h2);
+                    }
+                  }
+                }
+                uint32_t pk[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+                  pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                st_global_v8(op, pk);
+              } else {
+                float* op = reinterpret_cast<float*>(p.out) + dst * 128 + c0;
+                if (p.resid) {
+                  const float4* rp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.resid) + dst * 128 + c0);
+#pragma unroll
+                  for (int w4 = 0; w4 < 4; ++w4) {
+                    const float4 f = rp[w4];
+                    o[w4 * 4] += f.x; o[w4 * 4 + 1] += f.y; o[w4 * 4 + 2] += f.z; o[w4 * 4 + 3] += f.w;
+                  }
+                }
+                uint32_t pk[8];
+#pragma unroll
+                for (int half8 = 0; half8 < 2; ++half8) {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) pk[e] = __float_as_uint(o[half8 * 8 + e]);
+                  st_global_v8(op + half8 * 8, pk);
+                }
+              }
+            }
           }
         } else {
           if (j < 2) {
@@ -396,11 +580,15 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
   pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0, scale);
 }
 
-static int ln_gemm_smem(int n_pad) { return n_pad * 256 + 2 * LG_A_BYTES + (544 + 256) * 4 + 128 + 1024; }
+static int ln_gemm_smem(int n_pad, bool tri_out = false) {
+  return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (544 + 256 + 512) * 4 + 256 + 1024;
+}
 
 void configure_ln_gemm() {
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_ATTENTION>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(528));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, true));
   cudaGetLastError();
 }
 
@@ -410,13 +598,13 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
   LnGemmParams p{};
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)n * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
-  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4];
+  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
   p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
   p.mask = mask; p.out_a = a; p.out_b = b; p.n = n; p.ld = ld; p.status = (Status*)ctx->tc_status;
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(p);
+  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -429,7 +617,7 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   LnGemmParams p{};
   p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
   p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = eps; p.variance = variance;
-  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 528; p.bias = (const float*)w->h[1];
+  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 528; p.bias = (const float*)w->h[1]; p.n_bias = 528;
   p.n_chunks = bias ? 3 : 2;
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
   p.chunk_row0[0] = 0; p.chunk_row0[1] = 256; p.chunk_row0[2] = 512;
@@ -440,7 +628,54 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(p);
+  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(CUtensorMap{}, p);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  return LF_OK;
+}
+
+lf_status make_map_f16_3d_box(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
+
+// out[dst(r)] = resid[dst(r)] + o[r] Wo + bo, r in logical order, dst the transposed-orientation rule
+lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,
+                           const lf_weights* w, const void* resid, void* out, int act_dtype) {
+  if (cur.dry) return LF_OK;
+  LnGemmParams p{};
+  p.act = o; p.a_is_op16 = 1; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
+  p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = 1e-5f; p.variance = 1;
+  p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 128; p.bias = w->f[ATT_BO]; p.n_bias = 128;
+  p.n_chunks = 1; p.chunk_n[0] = 128; p.chunk_row0[0] = 0;
+  p.resid = resid; p.out = out; p.out_bf16 = act_dtype == LF_DTYPE_BF16;
+  p.status = (Status*)ctx->tc_status;
+  const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
+  // the fp16 rows are in logical order; the transposed scatter happens in the epilogue
+  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128), ctx->stream>>>(CUtensorMap{}, p);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  return LF_OK;
+}
+
+// out = resid + (LN_c(x) Wz + bz) * sigmoid(LN(z) Wg + bg); x is [128][n][ld] fp16 stored scaled by xscale
+lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int n, int ld, float x_eps, const void* z,
+                          int act_dtype, int variance, float eps, const lf_weights* w, const void* resid, void* out) {
+  if (cur.dry) return LF_OK;
+  CUtensorMap mapX;
+  LF_TRY(make_map_f16_3d_box(ctx, &mapX, x, n, n, 128, (uint64_t)ld * 2, (uint64_t)n * ld * 2, 64, 1, 128));
+  LnGemmParams p{};
+  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)n * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 256; p.bias = (const float*)w->h[3]; p.n_bias = 384;
+  p.n_chunks = 1; p.chunk_n[0] = 256; p.chunk_row0[0] = 0;
+  p.n = n; p.ld = ld; p.tile_per_row = (n + LG_ROWS - 1) / LG_ROWS; p.x_eps = x_eps;
+  p.resid = resid; p.out = out; p.out_bf16 = act_dtype == LF_DTYPE_BF16;
+  p.status = (Status*)ctx->tc_status;
+  const int64_t tiles = (int64_t)n * p.tile_per_row;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_OUTPUT);
+  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, true), ctx->stream>>>(mapX, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
