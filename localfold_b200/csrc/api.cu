@@ -685,7 +685,8 @@ void trn_f32(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
 }
 
 lf_status trn_dispatch(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a, int precision) {
-  (void)precision;
+  if (precision == LF_PRECISION_BF16 && !a.swiglu && tc::transition_supported(a.w))
+    return tc::transition_run(ctx, cur, a.act, a.act_dtype, a.rows, a.variance, a.eps, a.w, a.residual ? a.act : nullptr, a.out);
   if (a.act_dtype == LF_DTYPE_BF16) trn_f32<bf16>(ctx, cur, a); else trn_f32<float>(ctx, cur, a);
   return LF_OK;
 }

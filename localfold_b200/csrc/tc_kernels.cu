@@ -143,6 +143,19 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     pack_weight_image(ctx, w->f[ATT_WO], 128, 128, 128, 0, 128, img2, 0, 1.0f);
     w->h[2] = img2;
   }
+  if (w->kind == LF_WEIGHTS_TRANSITION_AF2 && w->dims.channels == 128 && w->dims.hidden == 512) {
+    // per 128-wide hidden chunk: W1 slice image (rows = hidden columns, K = 128 inputs), then W2 slice
+    // image (rows = 128 outputs, K = the chunk's 128 hidden channels)
+    op16* img = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img, 4 * 65536));
+    w->owned.push_back(img);
+    for (int cidx = 0; cidx < 4; ++cidx) {
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 128, 128, cidx * 128, 512, img + cidx * 32768, 0, 1.0f);
+      pack_weight_image(ctx, w->f[TRN_W2] + (size_t)cidx * 128 * 128, 128, 128, 128, 0, 128, img + cidx * 32768 + 16384, 0, 1.0f);
+    }
+    w->h.assign(1, nullptr);
+    w->h[0] = img;
+  }
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return LF_OK;
 }
@@ -315,6 +328,7 @@ void configure_once() {
     cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     configure_ln_gemm();
     configure_attention();
+    configure_transition();
     cudaGetLastError();
   });
 }

@@ -44,4 +44,10 @@ lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const
                          const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose, int mask_mode,
                          int clamp, op16* out);
 
+// Fused AF2 pair transition (128 channels, 512 hidden): out = resid + relu(LN(x) W1 + b1) W2 + b2
+void configure_transition();
+bool transition_supported(const lf_weights* w);
+lf_status transition_run(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int64_t rows, int variance,
+                         float eps, const lf_weights* w, const void* resid, void* out);
+
 }  // namespace tc

@@ -1,0 +1,373 @@
+// Fused pair transition on tcgen05 for 128-channel activations, 512 hidden (AF2 form):
+//   out = resid + relu(LN(x) W1 + b1) W2 + b2
+// The 4x-wide hidden never leaves the SM: it is produced 128 columns at a time into TMEM,
+// passed through bias + ReLU into a swizzled fp16 shared-memory tile, and consumed at once by
+// the second GEMM, whose float32 accumulator stays in TMEM across the four chunks.  The weights
+// (256 KiB as fp16) do not fit beside the tiles, so each chunk's W1/W2 slices (64 KiB, pre-swizzled
+// images) stream from L2 through a two-stage bulk-copy ring.
+//
+// Warp roles: 0..15 epilogue (TMEM lane quadrant = warp % 4, 32 of 128 columns = warp / 4),
+// 16..23 LayerNorm producers, 24 MMA issuer and TMEM owner, 25 weight streamer.
+#include <cuda.h>
+
+#include "tc05.cuh"
+#include "tc_kernels.cuh"
+
+namespace tc {
+
+using namespace tc05;
+
+constexpr int TR_THREADS = 26 * 32;
+constexpr int TR_ROWS = 128;
+constexpr int TR_TILE_BYTES = TR_ROWS * 128 * 2;   // 32 KiB: 128 rows x 128 fp16, two k-atoms
+constexpr int TR_W_STAGE = 2 * TR_TILE_BYTES;      // W1 slice + W2 slice
+constexpr int TR_CHUNKS = 4;
+constexpr int TR_SMEM = 2 * TR_W_STAGE + 2 * TR_TILE_BYTES + (512 + 128 + 256) * 4 + 256 + 1024;
+
+struct TransitionParams {
+  const void* act;
+  int act_bf16;
+  int64_t rows;
+  const float* gamma; const float* beta;
+  float eps; int variance;
+  const uint8_t* wimg;      // [4 chunks][W1 slice image 32 KiB | W2 slice image 32 KiB]
+  const float* b1;          // [512]
+  const float* b2;          // [128]
+  const void* resid;
+  void* out;
+  Status* status;
+};
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const TransitionParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sW = smem;                              // [2 stages][W1 slice | W2 slice]
+  uint8_t* sA = sW + 2 * TR_W_STAGE;               // normalised activations (A of GEMM 1)
+  uint8_t* sH = sA + TR_TILE_BYTES;                // hidden chunk (A of GEMM 2)
+  float* sB1 = reinterpret_cast<float*>(sH + TR_TILE_BYTES);   // [512]
+  float* sB2 = sB1 + 512;                          // [128]
+  float* sGamma = sB2 + 128;                       // [128]
+  float* sBeta = sGamma + 128;                     // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sBeta + 128);
+  uint64_t* a_full = bars;            // count 8 producer warps
+  uint64_t* a_empty = bars + 1;       // MMA commit
+  uint64_t* w_full = bars + 2;        // [2] bulk bytes
+  uint64_t* w_empty = bars + 4;       // [2] MMA commit
+  uint64_t* hacc_full = bars + 6;     // [2] MMA commit
+  uint64_t* hacc_empty = bars + 8;    // [2] count 16
+  uint64_t* h_full = bars + 10;       // count 16: hidden tile written
+  uint64_t* h_empty = bars + 11;      // MMA commit: GEMM 2 has read the hidden tile
+  uint64_t* out_full = bars + 12;     // MMA commit
+  uint64_t* out_empty = bars + 13;    // count 16
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles = (p.rows + TR_ROWS - 1) / TR_ROWS;
+
+  if (threadIdx.x == 0) {
+    mbar_init(a_full, 8); mbar_init(a_empty, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); mbar_init(&hacc_full[s], 1); mbar_init(&hacc_empty[s], 16); }
+    mbar_init(h_full, 16); mbar_init(h_empty, 1); mbar_init(out_full, 1); mbar_init(out_empty, 16);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  for (int i = threadIdx.x; i < 512; i += TR_THREADS) sB1[i] = p.b1[i];
+  if (threadIdx.x < 128) { sB2[threadIdx.x] = p.b2[threadIdx.x]; sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
+  if (warp == 24) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: hidden accumulators at 0 and 128, output accumulator at 256
+
+  if (warp == 25) {
+    // ---------------- weight streamer ----------------
+    if (lane == 0) {
+      uint32_t g = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait(&w_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 50)) { ok = false; break; }
+          mbar_expect_tx(&w_full[s], TR_W_STAGE);
+          bulk_load(sW + s * TR_W_STAGE, p.wimg + (size_t)c * TR_W_STAGE, TR_W_STAGE, &w_full[s]);
+        }
+      }
+    }
+  } else if (warp >= 16 && warp < 24) {
+    // ---------------- LayerNorm producers (8 lanes per row) ----------------
+    const int pw = warp - 16;
+    const int sub = lane >> 3, j = lane & 7;
+    int it = 0;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
+      if (!mbar_wait(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
+#pragma unroll 1
+      for (int grp = 0; grp < 2; ++grp) {
+        float v[2][16];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
+          const int64_t r = t * TR_ROWS + row;
+          if (r < p.rows) {
+            if (p.act_bf16) {
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + r * 128 + 16 * j);
+#pragma unroll
+              for (int w4 = 0; w4 < 2; ++w4) {
+                const uint4 raw = g[w4];
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                  v[u][w4 * 8 + e * 2] = __low2float(h2);
+                  v[u][w4 * 8 + e * 2 + 1] = __high2float(h2);
+                }
+              }
+            } else {
+              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + r * 128 + 16 * j);
+#pragma unroll
+              for (int w4 = 0; w4 < 4; ++w4) {
+                const float4 f = g[w4];
+                v[u][w4 * 4] = f.x; v[u][w4 * 4 + 1] = f.y; v[u][w4 * 4 + 2] = f.z; v[u][w4 * 4 + 3] = f.w;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[u][e] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
+          const bool valid = t * TR_ROWS + row < p.rows;
+          float sum = 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) sum += v[u][e];
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          const float mean = sum * (1.0f / 128.0f);
+          float sq = 0.f;
+          if (p.variance == 2) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) sq = fmaf(v[u][e], v[u][e], sq);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; sq = fmaf(d, d, sq); }
+          }
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          const float var = p.variance == 2 ? sq * (1.0f / 128.0f) - mean * mean : sq * (1.0f / 128.0f);
+          float inv = rsqrtf(var + p.eps);
+          inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
+          uint32_t packed[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 gm = *reinterpret_cast<const float2*>(sGamma + 16 * j + 2 * e);
+            const float2 bt = *reinterpret_cast<const float2*>(sBeta + 16 * j + 2 * e);
+            packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
+          }
+          uint8_t* base = sA + (uint32_t)(j >> 2) * (TR_ROWS * 128);
+          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2))) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2 + 1))) =
+              make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(a_full);
+    }
+  } else if (warp == 24) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(TR_ROWS, 128, 0, 0);
+      const uint32_t a_addr = smem_u32(sA), h_addr = smem_u32(sH);
+      uint32_t g = 0;      // chunk counter across tiles
+      int it = 0;
+      bool ok = true;
+      auto gemm2 = [&](uint32_t gc, int c) {   // out += hidden chunk x W2 slice of chunk counter gc
+        const uint32_t w2 = smem_u32(sW + (gc & 1) * TR_W_STAGE + TR_TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t adesc = make_smem_desc(h_addr + (kk >> 2) * (TR_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(w2 + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          umma_f16(tmem_base + 256, adesc, bdesc, idesc, (c | kk) != 0 ? 1u : 0u);
+        }
+      };
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+        if (!mbar_wait(a_full, it & 1, abort_flag, p.status, 52)) break;
+        if (!mbar_wait(out_empty, (it & 1) ^ 1, abort_flag, p.status, 53)) break;
+        tc_fence_after();
+        for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
+          const int s = g & 1;
+          if (!mbar_wait(&w_full[s], (g >> 1) & 1, abort_flag, p.status, 54) ||
+              !mbar_wait(&hacc_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 55)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t w1 = smem_u32(sW + s * TR_W_STAGE);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (TR_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+            const uint64_t bdesc = make_smem_desc(w1 + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+            umma_f16(tmem_base + s * 128, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(&hacc_full[s]);
+          if (c == TR_CHUNKS - 1) umma_commit(a_empty);
+          if (c >= 1) {
+            // second GEMM of the previous chunk, once its hidden tile is in shared memory
+            if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 56)) { ok = false; break; }
+            tc_fence_after();
+            gemm2(g - 1, c - 1);
+            umma_commit(h_empty);
+            umma_commit(&w_empty[(g - 1) & 1]);
+          }
+        }
+        if (!ok) break;
+        if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 57)) break;
+        tc_fence_after();
+        gemm2(g - 1, TR_CHUNKS - 1);
+        umma_commit(h_empty);
+        umma_commit(&w_empty[(g - 1) & 1]);
+        umma_commit(out_full);
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3, part = warp >> 2;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const bool out_bf16 = p.act_bf16 != 0;
+    uint32_t g = 0;
+    int it = 0;
+    bool ok = true;
+    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+      const int64_t r = t * TR_ROWS + row;
+      const bool valid = r < p.rows;
+      for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
+        const int s = g & 1;
+        if (!mbar_wait(&hacc_full[s], (g >> 1) & 1, abort_flag, p.status, 58)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t pk[16];
+#pragma unroll
+        for (int half16 = 0; half16 < 2; ++half16) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + lane_addr + s * 128 + part * 32 + half16 * 16, v);
+          tmem_ld_wait();
+          const float* b1 = sB1 + c * 128 + part * 32 + half16 * 16;
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            pk[half16 * 8 + e] = pack_half2(fmaxf(__uint_as_float(v[2 * e]) + b1[2 * e], 0.f),
+                                            fmaxf(__uint_as_float(v[2 * e + 1]) + b1[2 * e + 1], 0.f));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&hacc_empty[s]);
+        // the hidden tile is single-buffered: the previous chunk's second GEMM must have read it
+        if (!mbar_wait(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
+        // hidden columns part*32 .. +31 of this row: k-atom part/2, chunks 4*(part%2) .. +3
+        uint8_t* hb = sH + (uint32_t)(part >> 1) * (TR_ROWS * 128);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+          *reinterpret_cast<uint4*>(hb + swizzle128_offset((uint32_t)row, (uint32_t)((part & 1) * 4 + ch))) =
+              make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(h_full);
+      }
+      if (!ok) break;
+      if (!mbar_wait(out_full, it & 1, abort_flag, p.status, 60)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + lane_addr + 256 + c0, v);
+        tmem_ld_wait();
+        if (valid) {
+          float o[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v[e]) + sB2[c0 + e];
+          if (out_bf16) {
+            if (p.resid) {
+              const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.resid) + r * 128 + c0);
+#pragma unroll
+              for (int w4 = 0; w4 < 2; ++w4) {
+                const uint4 raw = rp[w4];
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                  o[w4 * 8 + e * 2] += __low2float(h2);
+                  o[w4 * 8 + e * 2 + 1] += __high2float(h2);
+                }
+              }
+            }
+            uint32_t ob[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+              ob[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            st_global_v8(reinterpret_cast<bf16*>(p.out) + r * 128 + c0, ob);
+          } else {
+            if (p.resid) {
+              const float4* rp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.resid) + r * 128 + c0);
+#pragma unroll
+              for (int w4 = 0; w4 < 4; ++w4) {
+                const float4 f = rp[w4];
+                o[w4 * 4] += f.x; o[w4 * 4 + 1] += f.y; o[w4 * 4 + 2] += f.z; o[w4 * 4 + 3] += f.w;
+              }
+            }
+            uint32_t ob[8];
+#pragma unroll
+            for (int half8 = 0; half8 < 2; ++half8) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) ob[e] = __float_as_uint(o[half8 * 8 + e]);
+              st_global_v8(reinterpret_cast<float*>(p.out) + r * 128 + c0 + half8 * 8, ob);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(out_empty);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) drain_after_abort();
+  if (warp == 24) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+void configure_transition() {
+  cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
+  cudaGetLastError();
+}
+
+bool transition_supported(const lf_weights* w) { return w && w->h.size() >= 1 && w->h[0] != nullptr; }
+
+lf_status transition_run(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int64_t rows, int variance,
+                         float eps, const lf_weights* w, const void* resid, void* out) {
+  if (cur.dry) return LF_OK;
+  TransitionParams p{};
+  p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = rows;
+  p.gamma = w->f[TRN_LN_G]; p.beta = w->f[TRN_LN_B]; p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[0]; p.b1 = w->f[TRN_B1]; p.b2 = w->f[TRN_B2];
+  p.resid = resid; p.out = out; p.status = (Status*)ctx->tc_status;
+  const int64_t tiles = (rows + TR_ROWS - 1) / TR_ROWS;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  lf_prof_begin(ctx, LF_KERNEL_TRANSITION);
+  transition_kernel<<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  return LF_OK;
+}
+
+}  // namespace tc

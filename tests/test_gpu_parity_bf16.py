@@ -111,3 +111,20 @@ def test_triangle_attention_bf16_fully_masked_row(dev):
     want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], False, pb)
     assert np.isfinite(got).all()
     assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+@pytest.mark.parametrize("rows", [128, 1000, 40000])
+def test_transition_af2_bf16(dev, rows):
+    import localfold_b200 as lf
+    d = syn.draw(800 + rows)
+    act = d.normal(rows, 128)
+    w = syn.af2_transition_weights(d, 128, 4)
+    w["firstBias"] = d.normal(512, std=0.3)
+    w["secondBias"] = d.normal(128, std=0.3)
+    w["layerNormScale"] = 1 + d.normal(128, std=0.1)
+    w["layerNormOffset"] = d.normal(128, std=0.1)
+    got = lf.TransitionGpu(dev).run({"activations": act, "rows": rows, "channels": 128, "hiddenChannels": 512,
+                                     "weights": w}, {"precision": "bf16", "variance": "two-pass"})
+    want = oracle.transition_af2(act, w, 512)
+    assert oracle.relative_l2(got["output"], want) <= OP_TOL
+    assert got["launches"] == 1      # one fused kernel: the 4x-wide hidden is never written out
