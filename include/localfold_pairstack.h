@@ -205,6 +205,22 @@ typedef struct lf_triangle_desc {
 } lf_triangle_desc;
 LF_API lf_status lf_triangle_multiplication_run(lf_context* ctx, const lf_triangle_desc* d, lf_result* r);
 
+/* Triangle multiplication that allocates nothing.  It has no counterpart in the reference; it exists
+ * for hosts that cannot let a library allocate device memory while they run - a server that gave
+ * the whole GPU to its own pool at start-up, or one whose latency rules forbid cudaMalloc/cudaFree
+ * in steady state because they synchronise the device.  Same descriptor and result as
+ * lf_triangle_multiplication_run, with these limits: device-space buffers only, the 16-bit
+ * tensor-core path only (precision LF_PRECISION_BF16), c_z = c_hidden = 128, and length <= 128
+ * (longer inputs are refused with LF_ERR_UNSUPPORTED).  The operands a, b and the product x live in
+ * a fixed 12 MiB array inside the library's device image instead of the scratch arena, so the call
+ * makes no cudaMalloc, cudaFree or other allocating call; every GPU that loads the library holds
+ * that array until the process exits.  The first call on each device looks the array's address up
+ * once (cudaGetSymbolAddress); make that first call before any stream capture.  All calls share
+ * the one array and it keeps the last call's contents (nothing in it needs clearing): two calls
+ * that overlap on the GPU - different contexts or streams on one device - race on it, so run them
+ * one after the other. */
+LF_API lf_status lf_triangle_multiplication_run_static(lf_context* ctx, const lf_triangle_desc* d, lf_result* r);
+
 /* AttentionGpu.run (webgpu/kernels/attention.js:2580-2739): gated multi-head
  * attention over `batch` rows of `query_length` positions with optional pair
  * bias and transposed orientation; and Af3GridSelfAttentionGpu.run

@@ -96,7 +96,8 @@ class PairStackDesc(ctypes.Structure):
 EXPORTS = (
     "lf_version", "lf_context_create", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
     "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
-    "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run", "lf_attention_run",
+    "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
+    "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
 )
 
@@ -133,7 +134,8 @@ def load():
     lib.lf_weights_destroy.restype = None
     lib.lf_int5_decode.argtypes = [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,
                                    c_int64, c_int32, ctypes.c_int, c_void_p]
-    for name, desc in (("lf_triangle_multiplication_run", TriangleDesc), ("lf_attention_run", AttentionDesc),
+    for name, desc in (("lf_triangle_multiplication_run", TriangleDesc),
+                       ("lf_triangle_multiplication_run_static", TriangleDesc), ("lf_attention_run", AttentionDesc),
                        ("lf_transition_run", TransitionDesc), ("lf_outer_product_mean_run", OpmDesc),
                        ("lf_single_attention_run", SingleAttentionDesc), ("lf_pair_stack_run", PairStackDesc)):
         getattr(lib, name).argtypes = [c_void_p, ctypes.POINTER(desc), ctypes.POINTER(Result)]
