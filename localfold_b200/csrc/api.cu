@@ -634,7 +634,7 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   op16* k = cur.take<op16>(R * HD);
   op16* v = cur.take<op16>(R * HD);
   op16* g = cur.take<op16>(R * HD);
-  const int ldb = (a.Q + 7) / 8 * 8;
+  const int ldb = (a.Q + 15) / 16 * 16;   // keys padded to whole groups of 16 (the tiled bias layout)
   op16* bias = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
   op16* o16 = cur.take<op16>(R * HD);
   if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);

@@ -30,7 +30,7 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
                            int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 [batch*Q][128] in logical row order and the
-// pair bias [heads][Q][ldb] fp16 (null = none) from the normalised input
+// pair bias fp16 tiled [heads][ldb/16][Q][16] (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);

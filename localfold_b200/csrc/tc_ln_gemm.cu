@@ -51,7 +51,7 @@ struct LnGemmParams {
   int n, ld;
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
-  op16* out_bias;           // [heads][Q][ldb] fp16
+  op16* out_bias;           // fp16, tiled for the attention core: [heads][ldb/16][Q][16] (head, 16-key group, query, key)
   int ldb;
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
@@ -541,7 +541,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             if (valid) {
               const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q;
               const int64_t qi = ur / uq, ki = ur % uq;
-              const int64_t dst = p.bias_swap ? ki * p.ldb + qi : qi * p.ldb + ki;
+              const int64_t bq = p.bias_swap ? ki : qi, bk = p.bias_swap ? qi : ki;   // bias[h][bq][bk]
+              const int64_t dst = ((bk >> 4) * p.Q + bq) * 16 + (bk & 15);
               const int64_t qq = (int64_t)p.Q * p.ldb;
 #pragma unroll
               for (int h = 0; h < 16; ++h)

@@ -128,3 +128,24 @@ def test_transition_af2_bf16(dev, rows):
     want = oracle.transition_af2(act, w, 512)
     assert oracle.relative_l2(got["output"], want) <= OP_TOL
     assert got["launches"] == 1      # one fused kernel: the 4x-wide hidden is never written out
+
+
+def test_triangle_attention_bf16_peaked_logits(dev):
+    """Logits with a spread of tens of units: rows whose later keys outrun the reference taken from the
+    tile's first keys must take the kernel's two-pass fallback and still match."""
+    import localfold_b200 as lf
+    n = 200
+    d = syn.draw(701)
+    z = d.normal(n, n, 128)
+    mask = syn.residue_pair_mask(n, 0.05)
+    t = syn.af2_attention_weights(d, 128, 4, 128)
+    t["attention"]["queryWeight"] = t["attention"]["queryWeight"] * 4.0
+    t["attention"]["keyWeight"] = t["attention"]["keyWeight"] * 4.0
+    pb = dict(t["pairBias"], source="normalized-input")
+    pb["projectionWeight"] = pb["projectionWeight"] * 5.0
+    inp = {"activations": z, "mask": mask, "batch": n, "queryLength": n, "channels": 128, "heads": 4,
+           "weights": t["attention"], "pairBias": pb}
+    got = lf.AttentionGpu(dev).run(inp, {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], False, pb)
+    assert np.isfinite(got).all()
+    assert oracle.relative_l2(got, want) <= OP_TOL
