@@ -320,6 +320,45 @@ typedef struct lf_pair_stack_desc {
 } lf_pair_stack_desc;
 LF_API lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_result* r);
 
+/* ---- row-sharded pair stack (several GPUs) ------------------------------- */
+
+/* The reference is single-device; for large N this library shards the pair by rows over the GPUs
+ * of one box (one process per GPU).  The host runs the block as a sequence of shard-local steps and
+ * puts the collectives between them (all-gather of the triangle operand b and of the pair bias,
+ * all-to-all transposes of the pair): see localfold_b200/sharded.py.  One entry point runs any
+ * step on the local shard `pair` [rows][length][128] (device memory, 16-bit tensor-core path,
+ * c_z = c_hidden = 128, 4 heads); `buf` holds the step's fp16 device buffers, which the caller
+ * allocates and moves between ranks.  With ld = length rounded up to 16:
+ *   TRIANGLE_PROJECT   buf0 = a, buf1 = b                      [128][rows][ld]
+ *   TRIANGLE_CONTRACT  buf0 = a, buf1 = b of rank `chunk`, buf2 = x [128][rows][ld]: fills
+ *                      x[:, :, chunk*rows : (chunk+1)*rows]    (outgoing form; rows % 16 == 0)
+ *   TRIANGLE_OUTPUT    buf2 = x; pair += output(x, pair)
+ *   ATTENTION_PROJECT  buf0..3 = q, k, v, gate [rows*length][128]; buf4 = this shard's pair bias
+ *                      [4][ld/16][rows][16]
+ *   ATTENTION_CORE     buf0..3; buf4 = every rank's bias [ranks][4][ld/16][rows][16]; buf5 = o
+ *   ATTENTION_OUTPUT   buf5 = o; pair += o Wo + bo
+ *   TRANSITION         pair += transition(pair)
+ * The incoming triangle update and the ending-node attention run as the outgoing / starting forms
+ * on the transposed shard (incoming(z) = outgoing(z^T)^T), with the mask rows of the transposed mask. */
+typedef enum lf_shard_op {
+  LF_SHARD_TRIANGLE_PROJECT = 1, LF_SHARD_TRIANGLE_CONTRACT = 2, LF_SHARD_TRIANGLE_OUTPUT = 3,
+  LF_SHARD_ATTENTION_PROJECT = 4, LF_SHARD_ATTENTION_CORE = 5, LF_SHARD_ATTENTION_OUTPUT = 6,
+  LF_SHARD_TRANSITION = 7
+} lf_shard_op;
+typedef struct lf_shard_step_desc {
+  int32_t op;                  /* lf_shard_op */
+  int32_t rows, length;        /* pair rows on this rank, row length */
+  int32_t ranks, chunk;        /* number of row shards; TRIANGLE_CONTRACT: whose b rows buf1 holds */
+  int32_t variance;            /* lf_variance */
+  float epsilon;
+  int32_t act_dtype;           /* lf_dtype of `pair` */
+  void* pair;
+  const float* mask;           /* [rows][length] */
+  void* buf[6];
+  const lf_weights* weights;
+} lf_shard_step_desc;
+LF_API lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_result* r);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,12 +93,23 @@ class PairStackDesc(ctypes.Structure):
                 ("first_block", c_int32), ("n_blocks", c_int32)]
 
 
+(SHARD_TRIANGLE_PROJECT, SHARD_TRIANGLE_CONTRACT, SHARD_TRIANGLE_OUTPUT, SHARD_ATTENTION_PROJECT,
+ SHARD_ATTENTION_CORE, SHARD_ATTENTION_OUTPUT, SHARD_TRANSITION) = range(1, 8)
+
+
+class ShardStepDesc(ctypes.Structure):
+    _fields_ = [("op", c_int32), ("rows", c_int32), ("length", c_int32), ("ranks", c_int32), ("chunk", c_int32),
+                ("variance", c_int32), ("epsilon", c_float), ("act_dtype", c_int32), ("pair", c_void_p),
+                ("mask", c_void_p), ("buf", c_void_p * 6), ("weights", c_void_p)]
+
+
 EXPORTS = (
     "lf_version", "lf_context_create", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
     "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
+    "lf_pair_shard_step",
 )
 
 _lib = None
@@ -137,7 +148,8 @@ def load():
     for name, desc in (("lf_triangle_multiplication_run", TriangleDesc),
                        ("lf_triangle_multiplication_run_static", TriangleDesc), ("lf_attention_run", AttentionDesc),
                        ("lf_transition_run", TransitionDesc), ("lf_outer_product_mean_run", OpmDesc),
-                       ("lf_single_attention_run", SingleAttentionDesc), ("lf_pair_stack_run", PairStackDesc)):
+                       ("lf_single_attention_run", SingleAttentionDesc), ("lf_pair_stack_run", PairStackDesc),
+                       ("lf_pair_shard_step", ShardStepDesc)):
         getattr(lib, name).argtypes = [c_void_p, ctypes.POINTER(desc), ctypes.POINTER(Result)]
     _lib = lib
     return lib

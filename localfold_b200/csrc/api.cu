@@ -541,7 +541,7 @@ lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
     LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(P, 8), 256, 0, (const T*)a.z, P, cz, f[TRI_LN_G],
            f[TRI_LN_B], a.eps, a.variance, 0, 1, 1, zn);
   if (tc::ln_gemm_supported(a.w)) {
-    LF_TRY(tc::triangle_project(ctx, cur, a.z, a.act_dtype, a.mask, n, ld, a.variance, a.eps, a.w, ga, gb));
+    LF_TRY(tc::triangle_project(ctx, cur, a.z, a.act_dtype, a.mask, n, n, ld, a.variance, a.eps, a.w, ga, gb));
   } else {
     sgemm(ctx, cur, false, false, simt::EPI_NONE, (int)P, 4 * c, cz, zn, cz, 0, f[TRI_W4], 4 * c, 0, p4, 4 * c, 0, f[TRI_B4], 0, 1);
     LAUNCH(ctx, cur, (simt::trimul_gate_kernel<op16>), dim3(lf_ceil_div(P, 32), lf_ceil_div(c, 32)), dim3(32, 8), 0, p4,
@@ -553,7 +553,7 @@ lf_status tri_bf16(lf_context* ctx, ArenaCursor& cur, const TriArgs& a) {
   LF_TRY(tc::contract(ctx, cur, ga, gb, x, n, ld, c, a.incoming, xscale));
   if (tc::ln_gemm_supported(a.w)) {
     const float xs = xscale * (a.divide ? (float)n : 1.0f);
-    LF_TRY(tc::triangle_output(ctx, cur, x, n, ld, a.eps * xs * xs, a.z, a.act_dtype, a.variance, a.eps, a.w,
+    LF_TRY(tc::triangle_output(ctx, cur, x, n, n, ld, a.eps * xs * xs, a.z, a.act_dtype, a.variance, a.eps, a.w,
                                a.residual ? a.z : nullptr, a.out));
     return LF_OK;
   }
@@ -640,7 +640,7 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
   LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
                                a.bias_swap, a.w, q, k, v, g, bias, ldb));
-  LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
+  LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.Q, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
   LF_TRY(tc::attention_output(ctx, cur, o16, a.batch, a.Q, a.transpose, a.w, a.residual ? a.act : nullptr, a.out, a.act_dtype));
   (void)f; (void)c;
   return LF_OK;
@@ -984,6 +984,68 @@ lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_res
     st.flush();
     return LF_OK;
   });
+}
+
+lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_result* r) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!d || !d->weights) return lf_fail(ctx, LF_ERR_ARGUMENT, "shard step: null argument");
+  if (d->rows <= 0 || d->length <= 0 || d->ranks <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "shard dimensions must be positive safe integers");
+  if (d->act_dtype != LF_DTYPE_F32 && d->act_dtype != LF_DTYPE_BF16) return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown activation dtype %d", d->act_dtype);
+  const lf_weights* w = d->weights;
+  const int R = d->rows, n = d->length, ld = (n + 15) / 16 * 16;
+  const bool tri = d->op >= LF_SHARD_TRIANGLE_PROJECT && d->op <= LF_SHARD_TRIANGLE_OUTPUT;
+  const bool att = d->op >= LF_SHARD_ATTENTION_PROJECT && d->op <= LF_SHARD_ATTENTION_OUTPUT;
+  if (tri && !((w->kind == LF_WEIGHTS_TRIANGLE_AF2 || w->kind == LF_WEIGHTS_TRIANGLE_AF3) && tc::ln_gemm_supported(w)))
+    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs triangle weights with cZ = cHidden = 128");
+  if (att && !(w->kind == LF_WEIGHTS_ATTENTION_AF2 && tc::ln_gemm_supported(w) && w->dims.heads == 4 && w->has_pair_proj && !w->has_pair_norm))
+    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs AF2 attention weights: 128 channels, 4 heads, normalized-input pair bias");
+  if (d->op == LF_SHARD_TRANSITION && !tc::transition_supported(w))
+    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs AF2 transition weights 128 -> 512 -> 128");
+  if ((tri || d->op == LF_SHARD_ATTENTION_PROJECT) && d->variance != LF_VARIANCE_TWO_PASS && d->variance != LF_VARIANCE_FAST)
+    return lf_fail(ctx, LF_ERR_ARGUMENT, "variance has no default: pass LF_VARIANCE_TWO_PASS or LF_VARIANCE_FAST");
+  cudaSetDevice(ctx->device);
+  const uint64_t before = ctx->launches;
+  ArenaCursor cur{ctx, 0, false};
+  const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
+  op16** b = (op16**)d->buf;
+  lf_status s = LF_OK;
+  switch (d->op) {
+    case LF_SHARD_TRIANGLE_PROJECT:
+      if (!d->pair || !d->mask || !b[0] || !b[1]) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle project: null buffer");
+      s = tc::triangle_project(ctx, cur, d->pair, d->act_dtype, d->mask, R, n, ld, d->variance, d->epsilon, w, b[0], b[1]);
+      break;
+    case LF_SHARD_TRIANGLE_CONTRACT:
+      if (!b[0] || !b[1] || !b[2]) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle contract: null buffer");
+      if (d->chunk < 0 || d->chunk >= d->ranks) return lf_fail(ctx, LF_ERR_ARGUMENT, "chunk %d is outside %d ranks", d->chunk, d->ranks);
+      if (d->ranks > 1 && R % 16 != 0) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "sharded rows must be a multiple of 16; received %d", R);
+      s = tc::contract_rect(ctx, cur, b[0], b[1], b[2], R, d->ranks > 1 ? R : n, n, ld, ld, (int64_t)R * ld, d->chunk * R, 128, 0, xscale);
+      break;
+    case LF_SHARD_TRIANGLE_OUTPUT:
+      if (!d->pair || !b[2]) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle output: null buffer");
+      s = tc::triangle_output(ctx, cur, b[2], R, n, ld, d->epsilon * xscale * xscale, d->pair, d->act_dtype, d->variance, d->epsilon, w, d->pair, d->pair);
+      break;
+    case LF_SHARD_ATTENTION_PROJECT:
+      if (!d->pair || !b[0] || !b[1] || !b[2] || !b[3] || !b[4]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention project: null buffer");
+      s = tc::attention_project(ctx, cur, d->pair, d->act_dtype, R, n, 0, d->variance, d->epsilon, 4, 32, 0, w, b[0], b[1], b[2], b[3], b[4], ld);
+      break;
+    case LF_SHARD_ATTENTION_CORE:
+      if (!d->mask || !b[0] || !b[1] || !b[2] || !b[3] || !b[4] || !b[5]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention core: null buffer");
+      s = tc::attention_core(ctx, cur, b[0], b[1], b[2], b[3], b[4], ld, R, d->mask, R, n, 0, 0, 1, b[5]);
+      break;
+    case LF_SHARD_ATTENTION_OUTPUT:
+      if (!d->pair || !b[5]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention output: null buffer");
+      s = tc::attention_output(ctx, cur, b[5], R, n, 0, w, d->pair, d->pair, d->act_dtype);
+      break;
+    case LF_SHARD_TRANSITION:
+      if (!d->pair) return lf_fail(ctx, LF_ERR_ARGUMENT, "transition: null buffer");
+      s = tc::transition_run(ctx, cur, d->pair, d->act_dtype, (int64_t)R * n, d->variance, d->epsilon, w, d->pair, d->pair);
+      break;
+    default: return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown shard step %d", d->op);
+  }
+  if (s != LF_OK) return s;
+  LF_CUDA(ctx, cudaGetLastError());
+  if (r) { r->elapsed_ms = 0.f; r->peak_bytes = ctx->arena_peak; r->launches = (uint32_t)(ctx->launches - before); }
+  return LF_OK;
 }
 
 lf_status lf_int5_decode(lf_context* ctx, const uint8_t* payload, uint64_t payload_bytes, uint64_t scale_offset,

@@ -84,10 +84,10 @@ extern "C" lf_status lf_triangle_multiplication_run_static(lf_context* ctx, cons
   ArenaCursor cur{ctx, 0, false};
   const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
   const float xs = xscale * (d->divide_by_length ? (float)n : 1.0f);
-  lf_status s = tc::triangle_project(ctx, cur, d->z, d->act_dtype, d->mask, n, ld, d->variance, d->epsilon, w, a, b);
+  lf_status s = tc::triangle_project(ctx, cur, d->z, d->act_dtype, d->mask, n, n, ld, d->variance, d->epsilon, w, a, b);
   if (s == LF_OK) s = tc::contract(ctx, cur, a, b, x, n, ld, 128, d->incoming ? 1 : 0, xscale);
   if (s == LF_OK)
-    s = tc::triangle_output(ctx, cur, x, n, ld, d->epsilon * xs * xs, d->z, d->act_dtype, d->variance, d->epsilon, w,
+    s = tc::triangle_output(ctx, cur, x, n, n, ld, d->epsilon * xs * xs, d->z, d->act_dtype, d->variance, d->epsilon, w,
                             d->residual ? d->z : nullptr, d->out);
   ctx->profiling = was_profiling;
   if (s != LF_OK) return s;

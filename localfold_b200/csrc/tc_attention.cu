@@ -35,8 +35,8 @@ struct FlashParams {
   int batch, Q, qtiles, qpairs, ktiles;
   int transpose, mask_mode, clamp;
   const float* mask;       // b*Q + j, or j*batch + b when transpose
-  const op16* bias;        // [4][ldb/16][Q][16] fp16 (head, 16-key group, query, key) or null
-  int ldb;
+  const op16* bias;        // [rank][4][ldb/16][bias_rows][16] fp16 (head, 16-key group, query, key) or null
+  int ldb, bias_rows;      // bias_rows = Q for a whole pair (one rank)
   const op16* gate;        // [batch*Q][128] sigmoid(gate)
   op16* out;               // [batch*Q][128]
   Status* status;
@@ -232,8 +232,9 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
       const int qi = (2 * qp + g) * FA_TILE + row;
       const bool qvalid = qi < p.Q;
       // this row's 16 keys of key group kg sit at bias_row + kg * Q * 16: consecutive rows are adjacent, loads coalesce
-      const op16* bias_row = p.bias ? p.bias + (int64_t)head * p.Q * p.ldb + (int64_t)(qvalid ? qi : 0) * 16 : nullptr;
-      const int64_t bias_step = (int64_t)p.Q * 16;
+      const int qb = qvalid ? qi : 0;
+      const op16* bias_row = p.bias ? p.bias + ((int64_t)(qb / p.bias_rows) * 4 + head) * p.bias_rows * p.ldb + (int64_t)(qb % p.bias_rows) * 16 : nullptr;
+      const int64_t bias_step = (int64_t)p.bias_rows * 16;
       float m_run = -INFINITY, l_run = 0.f;
       float O[32];
 #pragma unroll
@@ -403,8 +404,8 @@ lf_status make_map_f16_3d_ext(lf_context* ctx, CUtensorMap* map, const void* bas
                               uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1);
 
 lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,
-                         const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose, int mask_mode,
-                         int clamp, op16* out) {
+                         const op16* bias, int ldb, int bias_rows, const float* mask, int batch, int Q, int transpose,
+                         int mask_mode, int clamp, op16* out) {
   if (cur.dry) return LF_OK;
   CUtensorMap mq, mk, mv;
   const uint64_t row = 256, plane = (uint64_t)Q * 256;
@@ -413,7 +414,7 @@ lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const
   LF_TRY(make_map_f16_3d_ext(ctx, &mv, v, 128, Q, batch, row, plane, 64, FA_TILE));
   FlashParams p{};
   p.batch = batch; p.Q = Q; p.qtiles = (Q + FA_TILE - 1) / FA_TILE; p.qpairs = (p.qtiles + 1) / 2; p.ktiles = p.qtiles;
-  p.transpose = transpose; p.mask_mode = mask_mode; p.clamp = clamp; p.mask = mask; p.bias = bias; p.ldb = ldb;
+  p.transpose = transpose; p.mask_mode = mask_mode; p.clamp = clamp; p.mask = mask; p.bias = bias; p.ldb = ldb; p.bias_rows = bias_rows;
   p.gate = g; p.out = out; p.status = (Status*)ctx->tc_status;
   const int64_t items = (int64_t)batch * p.qpairs * 2;
   const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);

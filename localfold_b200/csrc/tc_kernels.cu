@@ -180,7 +180,8 @@ constexpr int CT_THREADS = 192;
 template <int MAJOR>
 __global__ void __launch_bounds__(CT_THREADS, 1)
 contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                op16* __restrict__ x, int n, int ld, int c, float scale, Status* status) {
+                op16* __restrict__ x, int m_rows, int n_rows, int k_len, int ldx, int64_t x_plane, int col0, int c,
+                float scale, Status* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CT_STAGES * CT_STAGE_BYTES);
@@ -192,10 +193,11 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (n + CT_BM - 1) / CT_BM, tiles_n = (n + CT_BN - 1) / CT_BN;
+  // x[h][i][col0 + j] for i < m_rows, j < n_rows; the contraction index runs over k_len
+  const int tiles_m = (m_rows + CT_BM - 1) / CT_BM, tiles_n = (n_rows + CT_BN - 1) / CT_BN;
   const int tiles_per_h = tiles_m * tiles_n;
   const int total = c * tiles_per_h;
-  const int kblocks = (n + CT_BK - 1) / CT_BK;
+  const int kblocks = (k_len + CT_BK - 1) / CT_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < CT_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -281,18 +283,19 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_flag, status, 4)) break;
       tc_fence_after();
       const int gi = mi * CT_BM + row;
-      op16* dst_row = x + ((int64_t)h * n + gi) * ld;
+      op16* dst_row = x + (int64_t)h * x_plane + (int64_t)gi * ldx + col0;
+      const int col_limit = (n_rows + 15) / 16 * 16 < ldx - col0 ? (n_rows + 15) / 16 * 16 : ldx - col0;
 #pragma unroll 1
       for (int cc = 0; cc < CT_BN / 32; ++cc) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * CT_BN + cc * 32, r);
         tmem_ld_wait();
-        const int gj0 = nj * CT_BN + cc * 32;
-        if (gi < n) {
+        const int gj0 = nj * CT_BN + cc * 32;   // column inside the window
+        if (gi < m_rows) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int gj = gj0 + v * 8;
-            if (gj < ld) {
+            if (gj < col_limit) {
               uint4 pk;
               pk.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
               pk.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
@@ -335,30 +338,36 @@ void configure_once() {
 
 bool contract_supported(int n, int c) { return n >= 1 && c >= 1 && g_encode != nullptr; }
 
-lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int n, int ld, int c,
-                   int incoming, float scale) {
+lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
+                        int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale) {
   if (cur.dry) return LF_OK;
-  if (ld % 8 != 0 || ld < n) return lf_fail(ctx, LF_ERR_ARGUMENT, "contraction row stride %d must be a multiple of 8 and at least %d", ld, n);
+  if (ld_ab % 8 != 0 || ld_ab < k_len || ldx % 8 != 0 || col0 % 8 != 0)
+    return lf_fail(ctx, LF_ERR_ARGUMENT, "contraction strides must be multiples of 8 and cover the row");
   CUtensorMap mapA, mapB;
-  const uint64_t row_bytes = (uint64_t)ld * 2, plane_bytes = (uint64_t)n * ld * 2;
+  const uint64_t row_bytes = (uint64_t)ld_ab * 2;
   if (!incoming) {
-    LF_TRY(make_map_f16_3d(ctx, &mapA, a, n, n, c, row_bytes, plane_bytes, CT_BK, CT_BM));
-    LF_TRY(make_map_f16_3d(ctx, &mapB, b, n, n, c, row_bytes, plane_bytes, CT_BK, CT_BN));
+    LF_TRY(make_map_f16_3d(ctx, &mapA, a, k_len, m_rows, c, row_bytes, (uint64_t)m_rows * row_bytes, CT_BK, CT_BM));
+    LF_TRY(make_map_f16_3d(ctx, &mapB, b, k_len, n_rows, c, row_bytes, (uint64_t)n_rows * row_bytes, CT_BK, CT_BN));
   } else {
-    // A(i,k) = b[h][k][i], B(j,k) = a[h][k][j]: boxes of 64 (i or j) x 64 (k)
-    LF_TRY(make_map_f16_3d(ctx, &mapA, b, n, n, c, row_bytes, plane_bytes, 64, CT_BK));
-    LF_TRY(make_map_f16_3d(ctx, &mapB, a, n, n, c, row_bytes, plane_bytes, 64, CT_BK));
+    // square form only: A(i,k) = b[h][k][i], B(j,k) = a[h][k][j]: boxes of 64 (i or j) x 64 (k)
+    LF_TRY(make_map_f16_3d(ctx, &mapA, b, m_rows, k_len, c, row_bytes, (uint64_t)k_len * row_bytes, 64, CT_BK));
+    LF_TRY(make_map_f16_3d(ctx, &mapB, a, n_rows, k_len, c, row_bytes, (uint64_t)k_len * row_bytes, 64, CT_BK));
   }
-  const int tiles = c * ((n + CT_BM - 1) / CT_BM) * ((n + CT_BN - 1) / CT_BN);
+  const int tiles = c * ((m_rows + CT_BM - 1) / CT_BM) * ((n_rows + CT_BN - 1) / CT_BN);
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_CONTRACT);
   if (!incoming)
-    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
+    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status);
   else
-    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, n, ld, c, scale, (Status*)ctx->tc_status);
+    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
+}
+
+lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int n, int ld, int c,
+                   int incoming, float scale) {
+  return contract_rect(ctx, cur, a, b, x, n, n, n, ld, ld, (int64_t)n * ld, 0, c, incoming, scale);
 }
 
 }  // namespace tc

@@ -19,6 +19,10 @@ lf_status check_status(lf_context* ctx);
 bool contract_supported(int n, int c);
 lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int n, int ld, int c,
                    int incoming, float scale);
+// Rectangular form for row shards: x[h][i][col0 + j] = scale * sum_k a[h][i][k] b[h][j][k], i < m_rows, j < n_rows,
+// k < k_len; a, b have row stride ld_ab and dense planes, x has row stride ldx and plane stride x_plane.
+lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
+                        int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale);
 
 // LayerNorm + projection kernels for 128-channel activations (weights repacked by
 // prepare_weights into lf_weights::h).
@@ -27,8 +31,9 @@ void configure_ln_gemm();
 void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0,
                        float scale);
 // a, b [c][n][ld] fp16 = mask * (LN(z) Wp + bp) * sigmoid(LN(z) Wg + bg)
-lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
-                           int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
+// `rows` pair rows of length n (rows = n for the whole pair, fewer for a row shard)
+lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
+                           int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 [batch*Q][128] in logical row order and the
 // pair bias fp16 tiled [heads][ldb/16][Q][16] (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
@@ -36,13 +41,16 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
 lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,
                            const lf_weights* w, const void* resid, void* out, int act_dtype);
-lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int n, int ld, float x_eps, const void* z,
-                          int act_dtype, int variance, float eps, const lf_weights* w, const void* resid, void* out);
+lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int rows, int n, int ld, float x_eps,
+                          const void* z, int act_dtype, int variance, float eps, const lf_weights* w, const void* resid,
+                          void* out);
 // out[b*Q+i][128] = (softmax_j(q_i.k_j + bias[h][i][j] + mask term_j) v_j) * gate, 4 heads x 32
 void configure_attention();
+// `bias_rows`: queries per bias block - Q for a whole pair; for a row shard the bias of every rank's
+// rows, gathered as [rank][head][16-key group][bias_rows][16]
 lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,
-                         const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose, int mask_mode,
-                         int clamp, op16* out);
+                         const op16* bias, int ldb, int bias_rows, const float* mask, int batch, int Q, int transpose,
+                         int mask_mode, int clamp, op16* out);
 
 // Fused AF2 pair transition (128 channels, 512 hidden): out = resid + relu(LN(x) W1 + b1) W2 + b2
 void configure_transition();

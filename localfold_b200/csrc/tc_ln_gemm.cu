@@ -48,7 +48,8 @@ struct LnGemmParams {
   const float* mask;        // [rows]
   op16* out_a;              // [c][n][ld]
   op16* out_b;
-  int n, ld;
+  int n, ld;                // pair row length and operand row stride
+  int plane_rows;           // pair rows held (n for a whole pair, fewer for a row shard)
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
   op16* out_bias;           // fp16, tiled for the attention core: [heads][ldb/16][Q][16] (head, 16-key group, query, key)
@@ -116,7 +117,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles = p.tile_per_row ? (int64_t)p.n * p.tile_per_row : (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int64_t tiles = p.tile_per_row ? (int64_t)p.plane_rows * p.tile_per_row : (p.rows + LG_ROWS - 1) / LG_ROWS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -380,7 +381,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           // gate at 128..255).  Each thread owns one channel and writes runs of consecutive k.
           const int h = row;
           const float bias_p = sBias[j * 256 + h], bias_g = sBias[j * 256 + 128 + h];
-          op16* plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.n * p.ld;
+          op16* plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.plane_rows * p.ld;
           const bool vec = (p.n & 15) == 0;
           const uint32_t un = (uint32_t)p.n;
           // rows of this warp's quarter: r0 .. r0+31, as (i, k) with 32-bit arithmetic
@@ -542,8 +543,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
               const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q;
               const int64_t qi = ur / uq, ki = ur % uq;
               const int64_t bq = p.bias_swap ? ki : qi, bk = p.bias_swap ? qi : ki;   // bias[h][bq][bk]
-              const int64_t dst = ((bk >> 4) * p.Q + bq) * 16 + (bk & 15);
-              const int64_t qq = (int64_t)p.Q * p.ldb;
+              // the bias block of these rows: [head][16-key group][batch rows][16]
+              const int64_t dst = ((bk >> 4) * p.batch + bq) * 16 + (bk & 15);
+              const int64_t qq = (int64_t)p.batch * p.ldb;
 #pragma unroll
               for (int h = 0; h < 16; ++h)
                 if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]));
@@ -593,11 +595,12 @@ void configure_ln_gemm() {
   cudaGetLastError();
 }
 
-lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int n,
-                           int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b) {
+lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
+                           int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b) {
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
-  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)n * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.plane_rows = rows;
   p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
   p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
@@ -660,20 +663,22 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
 }
 
 // out = resid + (LN_c(x) Wz + bz) * sigmoid(LN(z) Wg + bg); x is [128][n][ld] fp16 stored scaled by xscale
-lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int n, int ld, float x_eps, const void* z,
-                          int act_dtype, int variance, float eps, const lf_weights* w, const void* resid, void* out) {
+lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int rows, int n, int ld, float x_eps,
+                          const void* z, int act_dtype, int variance, float eps, const lf_weights* w, const void* resid,
+                          void* out) {
   if (cur.dry) return LF_OK;
   CUtensorMap mapX;
-  LF_TRY(make_map_f16_3d_box(ctx, &mapX, x, n, n, 128, (uint64_t)ld * 2, (uint64_t)n * ld * 2, 64, 1, 128));
+  LF_TRY(make_map_f16_3d_box(ctx, &mapX, x, n, rows, 128, (uint64_t)ld * 2, (uint64_t)rows * ld * 2, 64, 1, 128));
   LnGemmParams p{};
-  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)n * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.plane_rows = rows;
   p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 256; p.bias = (const float*)w->h[3]; p.n_bias = 384;
   p.n_chunks = 1; p.chunk_n[0] = 256; p.chunk_row0[0] = 0;
   p.n = n; p.ld = ld; p.tile_per_row = (n + LG_ROWS - 1) / LG_ROWS; p.x_eps = x_eps;
   p.resid = resid; p.out = out; p.out_bf16 = act_dtype == LF_DTYPE_BF16;
   p.status = (Status*)ctx->tc_status;
-  const int64_t tiles = (int64_t)n * p.tile_per_row;
+  const int64_t tiles = (int64_t)rows * p.tile_per_row;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_OUTPUT);
   ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, true), ctx->stream>>>(mapX, p);
