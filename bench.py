@@ -154,7 +154,9 @@ def workload_config(args, n_gpus):
     return {"workload": f"AF2 Evoformer pair-stack block, N={args.length}, c_z=128, tri-mult c=128, "
                         f"tri-attention 4x32, transition 4x, seed 4, mask ones (BASELINE config 4 shape)",
             "length": args.length, "precision": args.precision, "pair_dtype": "f32",
-            "parallelism": "single GPU" if n_gpus == 1 else f"{n_gpus} independent replicas",
+            "parallelism": "single GPU" if n_gpus == 1 else
+            f"pair rows sharded over {n_gpus} GPUs (all-gather of the triangle operand b and of the pair bias, "
+            f"4 all-to-all transposes per block, NCCL)",
             "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * 4 / 2 ** 20)}
 
 
@@ -194,14 +196,32 @@ def main():
     dev = lf.Device(local_rank, stream=stream.cuda_stream)
 
     n = args.length
-    pair_h, mask_h, weights = syn.af2_pair_block(4 + rank, n, blocks=2)
-    stack = lf.PairStackGpu(dev).prepare(weights, C_Z, C_HIDDEN)
     opts = {"precision": args.precision, "variance": "two-pass"}
-    pair_d = torch.from_numpy(pair_h).cuda()
-    mask_d = torch.from_numpy(mask_h).cuda()
+    if world == 1:
+        pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
+        stack = lf.PairStackGpu(dev).prepare(weights, C_Z, C_HIDDEN)
+        pair_d = torch.from_numpy(pair_h).cuda()
+        mask_d = torch.from_numpy(mask_h).cuda()
 
-    def step(i):
-        stack.run(pair_d, mask_d, opts, first_block=i % 2, n_blocks=1)
+        def step(i):
+            stack.run(pair_d, mask_d, opts, first_block=i % 2, n_blocks=1)
+    else:
+        # strong scaling: the same block, pair rows sharded over the ranks
+        from localfold_b200.sharded import GpuShardOps, ShardedPairStack, TorchComm, prepared_block_weights, shard_rows
+        if n % (16 * world):
+            raise SystemExit(f"--length {n} must be a multiple of 16 x {world} ranks")
+        pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
+        prepared = [lf.PreparedPairBlock(dev, w, C_Z, C_HIDDEN) for w in weights]
+        block_w = [prepared_block_weights(b) for b in prepared]
+        shard = {"z": torch.from_numpy(np.ascontiguousarray(shard_rows(pair_h, rank, world))).cuda()}
+        pair_h = np.ascontiguousarray(shard_rows(pair_h, rank, world))
+        m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(mask_h, rank, world))).cuda()
+        m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(mask_h.T), rank, world))).cuda()
+        sharded = ShardedPairStack(TorchComm(), GpuShardOps(dev, n // world, n, world))
+        stack = None
+
+        def step(i):
+            shard["z"] = sharded.block(shard["z"], m_rows, m_t_rows, block_w[i % 2])
 
     def barrier():
         torch.cuda.synchronize()
@@ -235,30 +255,43 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_per_block = total_ms / args.steps
-    finite = bool(torch.isfinite(pair_d).all().item())
+    finite = bool(torch.isfinite(pair_d if world == 1 else shard["z"]).all().item())
 
     # end to end through the host-buffer API: pinned host pair in, pair out, every step
     e2e = None
     if not args.no_e2e:
-        pinned = torch.empty((n, n, C_Z), dtype=torch.float32, pin_memory=True)
-        pinned.copy_(torch.from_numpy(pair_h))
-        mask_p = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
-        mask_p.copy_(torch.from_numpy(mask_h))
-        host_pair, host_mask = pinned.numpy(), mask_p.numpy()
+        rows_local = n // world
+        pinned = torch.empty((rows_local, n, C_Z), dtype=torch.float32, pin_memory=True)
+        pinned.copy_(torch.from_numpy(pair_h).reshape(rows_local, n, C_Z))
         reps = max(2, min(args.steps, 3))
-        stack.run(host_pair, host_mask, opts, first_block=0, n_blocks=1, inplace=True)   # warm the staging arena
+        if world == 1:
+            mask_p = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
+            mask_p.copy_(torch.from_numpy(mask_h))
+            host_pair, host_mask = pinned.numpy(), mask_p.numpy()
+
+            def e2e_step(i):   # the public host-buffer call: pair in, block, pair out
+                stack.run(host_pair, host_mask, opts, first_block=i % 2, n_blocks=1, inplace=True)
+            h2d = int(pinned.numel() * 4 + mask_p.numel() * 4)
+        else:
+            def e2e_step(i):   # each rank: its pinned shard in, the sharded block, its shard out
+                shard["z"].copy_(pinned, non_blocking=True)
+                step(i)
+                pinned.copy_(shard["z"], non_blocking=True)
+                torch.cuda.synchronize()
+            h2d = int(pinned.numel() * 4) * world
+        e2e_step(0)   # warm the staging arena
         barrier()
         t0 = time.perf_counter()
         for i in range(reps):
-            stack.run(host_pair, host_mask, opts, first_block=i % 2, n_blocks=1, inplace=True)
+            e2e_step(i)
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) * 1e3 / reps
         if world > 1:
             t = torch.tensor([wall], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             wall = float(t.item())
-        e2e = {"value": wall, "unit": "ms/block", "h2d_bytes_per_step": int(pinned.numel() * 4 + mask_p.numel() * 4),
-               "d2h_bytes_per_step": int(pinned.numel() * 4)}
+        e2e = {"value": wall, "unit": "ms/block", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": int(pinned.numel() * 4) * world}
 
     if rank == 0:
         peaks = measured_peaks()
@@ -266,19 +299,21 @@ def main():
         roofline = None
         if ct_launches:
             per_launch_ms = ct_ms / ct_launches
-            achieved = contraction_flops(n) / (per_launch_ms * 1e-3) / 1e12
+            # one launch: all of x on one GPU, or one gathered chunk (rows x rows x N per channel) when sharded
+            launch_flops = contraction_flops(n) if world == 1 else 256.0 * (n // world) ** 2 * n
+            achieved = launch_flops / (per_launch_ms * 1e-3) / 1e12
             roofline = {"kernel": "triangle contraction (tcgen05, 128 batched NxNxN GEMMs)", "bound": "tensor",
                         "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                         "frac": achieved / peaks["tflops_sustained"], "traffic": None,
                         "peak_source": peaks["source"] + " (sustained cuBLAS bf16; the kernel runs inside a long step)",
-                        "launch_ms": per_launch_ms, "flops_per_launch": contraction_flops(n)}
+                        "launch_ms": per_launch_ms, "flops_per_launch": launch_flops}
         cpu = None
         if not args.no_cpu:
             cpu = cpu_sample(args.cpu_sample, n)
         line = {
             "metric": "pair_stack_block_ms", "value": ms_per_block, "unit": "ms/block", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_block, "higher_is_better": False,
-            "scaling": "weak" if world > 1 else "strong", "vs_baseline": None,
+            "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 operands / f32 accumulate (pair stream f32)" if args.precision == "bf16" else "f32",
             "data": "synthetic", "config": workload_config(args, world),
             "tflops_block": block_flops(n) / (ms_per_block * 1e-3) / 1e12,
@@ -287,8 +322,10 @@ def main():
             "clocks": clocks, "finite": finite,
         }
         print(json.dumps(line))
-    stack.close()
+    if stack is not None:
+        stack.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -685,7 +685,7 @@ void trn_f32(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
 }
 
 lf_status trn_dispatch(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a, int precision) {
-  if (precision == LF_PRECISION_BF16 && !a.swiglu && tc::transition_supported(a.w))
+  if (precision == LF_PRECISION_BF16 && tc::transition_supported(a.w))
     return tc::transition_run(ctx, cur, a.act, a.act_dtype, a.rows, a.variance, a.eps, a.w, a.residual ? a.act : nullptr, a.out);
   if (a.act_dtype == LF_DTYPE_BF16) trn_f32<bf16>(ctx, cur, a); else trn_f32<float>(ctx, cur, a);
   return LF_OK;
@@ -1000,7 +1000,7 @@ lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_re
   if (att && !(w->kind == LF_WEIGHTS_ATTENTION_AF2 && tc::ln_gemm_supported(w) && w->dims.heads == 4 && w->has_pair_proj && !w->has_pair_norm))
     return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs AF2 attention weights: 128 channels, 4 heads, normalized-input pair bias");
   if (d->op == LF_SHARD_TRANSITION && !tc::transition_supported(w))
-    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs AF2 transition weights 128 -> 512 -> 128");
+    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "shard step needs transition weights 128 -> 512 -> 128");
   if ((tri || d->op == LF_SHARD_ATTENTION_PROJECT) && d->variance != LF_VARIANCE_TWO_PASS && d->variance != LF_VARIANCE_FAST)
     return lf_fail(ctx, LF_ERR_ARGUMENT, "variance has no default: pass LF_VARIANCE_TWO_PASS or LF_VARIANCE_FAST");
   cudaSetDevice(ctx->device);

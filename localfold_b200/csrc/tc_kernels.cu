@@ -156,6 +156,21 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->h.assign(1, nullptr);
     w->h[0] = img;
   }
+  if (w->kind == LF_WEIGHTS_TRANSITION_AF3 && w->dims.channels == 128 && w->dims.hidden == 512) {
+    // per 64-wide hidden chunk: W1 slice image of 128 rows (64 gate columns, then the matching 64 value
+    // columns; K = 128 inputs: 32 KiB), then W2 slice image (rows = 128 outputs, K = 64 hidden: 16 KiB)
+    op16* img = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img, 8 * 49152));
+    w->owned.push_back(img);
+    for (int cidx = 0; cidx < 8; ++cidx) {
+      op16* base = img + (size_t)cidx * 24576;
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, cidx * 64, 1024, base, 0, 1.0f);
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, 512 + cidx * 64, 1024, base, 64, 1.0f);
+      pack_weight_image(ctx, w->f[TRN_W2] + (size_t)cidx * 64 * 128, 64, 128, 128, 0, 128, base + 16384, 0, 1.0f);
+    }
+    w->h.assign(1, nullptr);
+    w->h[0] = img;
+  }
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return LF_OK;
 }

@@ -1,5 +1,7 @@
-// Fused pair transition on tcgen05 for 128-channel activations, 512 hidden (AF2 form):
-//   out = resid + relu(LN(x) W1 + b1) W2 + b2
+// Fused pair transition on tcgen05 for 128-channel activations, 512 hidden:
+//   AF2 form:  out = resid + relu(LN(x) W1 + b1) W2 + b2              (hidden chunks of 128)
+//   AF3 form:  out = resid + (swish(u_gate) * u_value) W2, u = LN(x) W1, W1 = (gate half | value half)
+//              (hidden chunks of 64: each first-GEMM chunk is 64 gate + 64 value columns)
 // The 4x-wide hidden never leaves the SM: it is produced 128 columns at a time into TMEM,
 // passed through bias + ReLU into a swizzled fp16 shared-memory tile, and consumed at once by
 // the second GEMM, whose float32 accumulator stays in TMEM across the four chunks.  The weights
@@ -20,9 +22,8 @@ using namespace tc05;
 constexpr int TR_THREADS = 26 * 32;
 constexpr int TR_ROWS = 128;
 constexpr int TR_TILE_BYTES = TR_ROWS * 128 * 2;   // 32 KiB: 128 rows x 128 fp16, two k-atoms
-constexpr int TR_W_STAGE = 2 * TR_TILE_BYTES;      // W1 slice + W2 slice
-constexpr int TR_CHUNKS = 4;
-constexpr int TR_SMEM = 2 * TR_W_STAGE + 2 * TR_TILE_BYTES + (512 + 128 + 256) * 4 + 256 + 1024;
+constexpr int TR_W_STAGE = 2 * TR_TILE_BYTES;      // AF2: W1 slice (32 KiB) + W2 slice (32 KiB); AF3: 32 KiB + 16 KiB
+constexpr int TR_SMEM = 2 * TR_W_STAGE + 2 * TR_TILE_BYTES + (1024 + 128 + 256) * 4 + 256 + 1024;
 
 struct TransitionParams {
   const void* act;
@@ -30,13 +31,19 @@ struct TransitionParams {
   int64_t rows;
   const float* gamma; const float* beta;
   float eps; int variance;
-  const uint8_t* wimg;      // [4 chunks][W1 slice image 32 KiB | W2 slice image 32 KiB]
-  const float* b1;          // [512]
+  const uint8_t* wimg;      // per chunk: W1 slice image, then W2 slice image
+  const float* b1;          // [512] (AF2) or [1024] = gate half | value half (AF3)
   const float* b2;          // [128]
   const void* resid;
   void* out;
   Status* status;
 };
+
+__device__ __forceinline__ float sigmoid_tanh(float v) {   // one MUFU: 0.5 + 0.5 tanh(v/2)
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * v));
+  return fmaf(0.5f, t, 0.5f);
+}
 
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
@@ -44,14 +51,18 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
+template <bool SWIGLU>
 __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const TransitionParams p) {
+  constexpr int TR_CHUNKS = SWIGLU ? 8 : 4;                 // hidden chunks per tile
+  constexpr int HK = SWIGLU ? 64 : 128;                     // hidden channels per chunk = K of the second GEMM
+  constexpr uint32_t W_BYTES = SWIGLU ? 3 * TR_TILE_BYTES / 2 : 2 * TR_TILE_BYTES;   // bytes streamed per chunk
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sW = smem;                              // [2 stages][W1 slice | W2 slice]
   uint8_t* sA = sW + 2 * TR_W_STAGE;               // normalised activations (A of GEMM 1)
   uint8_t* sH = sA + TR_TILE_BYTES;                // hidden chunk (A of GEMM 2)
   float* sB1 = reinterpret_cast<float*>(sH + TR_TILE_BYTES);   // [512]
-  float* sB2 = sB1 + 512;                          // [128]
+  float* sB2 = sB1 + 1024;                         // [128]
   float* sGamma = sB2 + 128;                       // [128]
   float* sBeta = sGamma + 128;                     // [128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sBeta + 128);
@@ -78,7 +89,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
     *abort_flag = 0;
     fence_barrier_init();
   }
-  for (int i = threadIdx.x; i < 512; i += TR_THREADS) sB1[i] = p.b1[i];
+  for (int i = threadIdx.x; i < (SWIGLU ? 1024 : 512); i += TR_THREADS) sB1[i] = p.b1[i];
   if (threadIdx.x < 128) { sB2[threadIdx.x] = p.b2[threadIdx.x]; sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
   if (warp == 24) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -96,8 +107,8 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
         for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
           const int s = g & 1;
           if (!mbar_wait(&w_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 50)) { ok = false; break; }
-          mbar_expect_tx(&w_full[s], TR_W_STAGE);
-          bulk_load(sW + s * TR_W_STAGE, p.wimg + (size_t)c * TR_W_STAGE, TR_W_STAGE, &w_full[s]);
+          mbar_expect_tx(&w_full[s], W_BYTES);
+          bulk_load(sW + s * TR_W_STAGE, p.wimg + (size_t)c * W_BYTES, W_BYTES, &w_full[s]);
         }
       }
     }
@@ -196,7 +207,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
       auto gemm2 = [&](uint32_t gc, int c) {   // out += hidden chunk x W2 slice of chunk counter gc
         const uint32_t w2 = smem_u32(sW + (gc & 1) * TR_W_STAGE + TR_TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < HK / 16; ++kk) {
           const uint64_t adesc = make_smem_desc(h_addr + (kk >> 2) * (TR_ROWS * 128) + (kk & 3) * 32, 16, 1024);
           const uint64_t bdesc = make_smem_desc(w2 + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
           umma_f16(tmem_base + 256, adesc, bdesc, idesc, (c | kk) != 0 ? 1u : 0u);
@@ -255,28 +266,52 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
         if (!mbar_wait(&hacc_full[s], (g >> 1) & 1, abort_flag, p.status, 58)) { ok = false; break; }
         tc_fence_after();
         uint32_t pk[16];
-#pragma unroll
-        for (int half16 = 0; half16 < 2; ++half16) {
-          uint32_t v[16];
-          tmem_ld16(tmem_base + lane_addr + s * 128 + part * 32 + half16 * 16, v);
+        if (SWIGLU) {
+          // hidden channels part*16 .. +15 of the chunk: gate at column j, value at column 64 + j
+          uint32_t gt[16], vl[16];
+          tmem_ld16(tmem_base + lane_addr + s * 128 + part * 16, gt);
+          tmem_ld16(tmem_base + lane_addr + s * 128 + 64 + part * 16, vl);
           tmem_ld_wait();
-          const float* b1 = sB1 + c * 128 + part * 32 + half16 * 16;
+          const float* bg = sB1 + c * 64 + part * 16;
+          const float* bv = sB1 + 512 + c * 64 + part * 16;
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            pk[half16 * 8 + e] = pack_half2(fmaxf(__uint_as_float(v[2 * e]) + b1[2 * e], 0.f),
-                                            fmaxf(__uint_as_float(v[2 * e + 1]) + b1[2 * e + 1], 0.f));
+          for (int e = 0; e < 8; ++e) {
+            const float g0 = __uint_as_float(gt[2 * e]) + bg[2 * e], g1 = __uint_as_float(gt[2 * e + 1]) + bg[2 * e + 1];
+            const float v0 = __uint_as_float(vl[2 * e]) + bv[2 * e], v1 = __uint_as_float(vl[2 * e + 1]) + bv[2 * e + 1];
+            pk[e] = pack_half2(g0 * sigmoid_tanh(g0) * v0, g1 * sigmoid_tanh(g1) * v1);
+          }
+        } else {
+#pragma unroll
+          for (int half16 = 0; half16 < 2; ++half16) {
+            uint32_t v[16];
+            tmem_ld16(tmem_base + lane_addr + s * 128 + part * 32 + half16 * 16, v);
+            tmem_ld_wait();
+            const float* b1 = sB1 + c * 128 + part * 32 + half16 * 16;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              pk[half16 * 8 + e] = pack_half2(fmaxf(__uint_as_float(v[2 * e]) + b1[2 * e], 0.f),
+                                              fmaxf(__uint_as_float(v[2 * e + 1]) + b1[2 * e + 1], 0.f));
+          }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&hacc_empty[s]);
         // the hidden tile is single-buffered: the previous chunk's second GEMM must have read it
         if (!mbar_wait(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
-        // hidden columns part*32 .. +31 of this row: k-atom part/2, chunks 4*(part%2) .. +3
-        uint8_t* hb = sH + (uint32_t)(part >> 1) * (TR_ROWS * 128);
+        if (SWIGLU) {
+          // 16 hidden channels = chunks 2*part, 2*part+1 of the row's single 64-wide k-atom
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(hb + swizzle128_offset((uint32_t)row, (uint32_t)((part & 1) * 4 + ch))) =
-              make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+          for (int ch = 0; ch < 2; ++ch)
+            *reinterpret_cast<uint4*>(sH + swizzle128_offset((uint32_t)row, (uint32_t)(part * 2 + ch))) =
+                make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        } else {
+          // hidden columns part*32 .. +31 of this row: k-atom part/2, chunks 4*(part%2) .. +3
+          uint8_t* hb = sH + (uint32_t)(part >> 1) * (TR_ROWS * 128);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+            *reinterpret_cast<uint4*>(hb + swizzle128_offset((uint32_t)row, (uint32_t)((part & 1) * 4 + ch))) =
+                make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        }
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(h_full);
@@ -347,7 +382,8 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
 }
 
 void configure_transition() {
-  cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
+  cudaFuncSetAttribute(transition_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
+  cudaFuncSetAttribute(transition_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
   cudaGetLastError();
 }
 
@@ -364,7 +400,10 @@ lf_status transition_run(lf_context* ctx, ArenaCursor& cur, const void* act, int
   const int64_t tiles = (rows + TR_ROWS - 1) / TR_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_TRANSITION);
-  transition_kernel<<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
+  if (w->kind == LF_WEIGHTS_TRANSITION_AF3)
+    transition_kernel<true><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
+  else
+    transition_kernel<false><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;

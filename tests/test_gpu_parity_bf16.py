@@ -149,3 +149,32 @@ def test_triangle_attention_bf16_peaked_logits(dev):
     want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], False, pb)
     assert np.isfinite(got).all()
     assert oracle.relative_l2(got, want) <= OP_TOL
+
+
+@pytest.mark.parametrize("rows", [128, 5000])
+def test_transition_af3_bf16(dev, rows):
+    import localfold_b200 as lf
+    d = syn.draw(850 + rows)
+    act = d.normal(rows, 128)
+    w = syn.af3_transition_weights(d, 128, 4)
+    w["inputLayerNormScale"] = 1 + d.normal(128, std=0.1)
+    w["inputLayerNormOffset"] = d.normal(128, std=0.1)
+    got = lf.Af3TransitionGpu(dev).run(act, {"rows": rows, "channels": 128, "factor": 4}, w, {"precision": "bf16"})
+    want = oracle.transition_af3(act, w, 4)
+    assert oracle.relative_l2(got["output"], want) <= OP_TOL
+    assert got["launches"] == 1
+
+
+def test_af3_pairformer_block_bf16_int5_weights(dev):
+    """BASELINE config 2 shape at reduced N: AF3 pairformer blocks whose linear weights went through the
+    int5 bundle format (quantised and decoded identically for the oracle and the GPU)."""
+    import localfold_b200 as lf
+    from localfold_b200 import bundle
+    n = 96
+    pair, single, pair_mask, seq_mask, blocks = syn.af3_pairformer(2, n, 128, 384, blocks=1)
+    blocks = [bundle.quantise_weights_like_bundle(b) for b in blocks]
+    wp, ws = oracle.af3_pairformer_block(pair, single, pair_mask, seq_mask, blocks[0], True)
+    got = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
+                                             "tokens": n}, blocks, {"swapTransposedBias": True}, {"precision": "bf16"})
+    assert oracle.relative_l2(got["pair"], wp) <= BLOCK_TOL
+    assert oracle.relative_l2(got["single"], ws) <= BLOCK_TOL
