@@ -6,10 +6,11 @@
 // Per key tile and stream: S = Q K^T on the tensor core into the stream's 128 TMEM columns;
 // the stream's four softmax warps (one thread per query row, so every row reduction is
 // thread-local) read S once in 16-column pieces, add the pair bias and the key mask,
-// exponentiate against a reference maximum known in advance (falling back to two passes in the
-// rare tile where a logit outruns it) and write P as fp16 into the stream's swizzled
-// shared-memory tile; then P V runs on the tensor core into the TMEM columns S just vacated and
-// is folded into the row's register accumulator.  Sixteen softmax warps (four per scheduler)
+// exponentiate against a reference maximum known in advance (raised, with an in-place rescale of
+// what was written, in the rare tile where a logit outruns it) and write P as packed fp16 back
+// into the TMEM columns of S already consumed; P V then runs on the tensor core with P as the A
+// operand straight from tensor memory, into TMEM columns S has vacated, and is folded into the
+// row's register accumulator.  P never touches shared memory.  Sixteen softmax warps (four per scheduler)
 // hide each other's memory and MMA latency at under 100 registers per thread.  The N x N x N
 // logits never exist in memory.
 //
@@ -28,8 +29,7 @@ constexpr int FA_THREADS = 18 * 32;
 constexpr int FA_TILE = 128;
 constexpr int FA_Q_BYTES = FA_TILE * 128;          // per query tile: 128 rows x (2 heads x 32 x 2 B)
 constexpr int FA_KV_BYTES = FA_TILE * 128;
-constexpr int FA_P_BYTES = FA_TILE * FA_TILE * 2;  // per stream: two 16 KiB k-atoms
-constexpr int FA_SMEM = 2 * FA_Q_BYTES + 2 * 2 * FA_KV_BYTES + 4 * FA_P_BYTES + 2 * FA_TILE * 4 + 256 + 1024;
+constexpr int FA_SMEM = 2 * FA_Q_BYTES + 2 * 2 * FA_KV_BYTES + 2 * FA_TILE * 4 + 256 + 1024;
 
 struct FlashParams {
   int batch, Q, qtiles, qpairs, ktiles;
@@ -56,8 +56,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   uint8_t* sQ = smem;                            // [2 query tiles]
   uint8_t* sK = sQ + 2 * FA_Q_BYTES;             // [2 stages]
   uint8_t* sV = sK + 2 * FA_KV_BYTES;            // [2 stages]
-  uint8_t* sP = sV + 2 * FA_KV_BYTES;            // [4 streams]
-  float* sMask = reinterpret_cast<float*>(sP + 4 * FA_P_BYTES);   // [2 stages][128] additive terms
+  float* sMask = reinterpret_cast<float*>(sV + 2 * FA_KV_BYTES);   // [2 stages][128] additive terms
   uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 2 * FA_TILE);
   uint64_t* q_full = bars;           // 1
   uint64_t* q_empty = bars + 1;      // 1
@@ -166,13 +165,13 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
             if (mbar_test(&p_full[sidx], u & 1)) {
               tc_fence_after();
               const int st = u & 1;
-              const uint32_t p_addr = smem_u32(sP + sidx * FA_P_BYTES);
+              // P is the A operand straight from tensor memory: 16 keys per step = 8 packed columns;
+              // the product lands in columns 64..95 of the stream's region (S there is dead by now)
               const uint32_t v_addr = smem_u32(sV + st * FA_KV_BYTES);
 #pragma unroll
               for (int kk = 0; kk < FA_TILE / 16; ++kk) {
-                const uint64_t adesc = make_smem_desc(p_addr + (kk >> 2) * (FA_TILE * 128) + (kk & 3) * 32, 16, 1024);
                 const uint64_t bdesc = make_smem_desc(v_addr + h * 64 + kk * 2048, 8192, 1024);
-                umma_f16(d, adesc, bdesc, idesc_pv, kk != 0 ? 1u : 0u);
+                umma_f16_ts(d + 64, d + kk * 8, bdesc, idesc_pv, kk != 0 ? 1u : 0u);
               }
               umma_commit(&o_full[sidx]);
               if (++pv_cnt[st] == 4) { pv_cnt[st] = 0; umma_commit(&kv_empty[st]); }
@@ -220,7 +219,6 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
     const int g = sidx >> 1, h = sidx & 1;
     const int row = q * 32 + lane;
     const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + sidx * FA_TILE;
-    uint8_t* pt = sP + sidx * FA_P_BYTES;
     const float L2E = 1.4426950408889634f;
     uint32_t n_kv = 0, n_tile = 0;
     bool ok = true;
@@ -247,12 +245,13 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tc_fence_after();
         const bool masked = mask_flag[st] != 0;
         const int k0 = t * FA_TILE;
-        // One pass in the common case: exponentials are taken against a reference that is known before
-        // the tile is read - the running reference, raised to the maximum of the tile's first 16 logits.
-        // A logit may exceed the reference by up to kSlack (e^8 < 3000 fits fp16 and float32 sums easily);
-        // if any row of the warp exceeds it, the warp redoes the tile in two passes against the true maximum.
+        // One pass: exponentials are taken against a reference known before the tile is read - the
+        // running reference, raised to the maximum of the tile's first 16 logits - and P (fp16, two keys
+        // per 32-bit column) overwrites the S columns already consumed.  A logit may exceed the reference
+        // by up to kSlack (e^8 < 3000 fits fp16 and float32 sums easily); when a later piece outruns it,
+        // the reference is raised and the P columns already written are rescaled in place.
         constexpr float kSlack = 8.0f;
-        float m_ref = m_run, neg = 0.f, sum = 0.f, mx = -INFINITY;
+        float m_ref = m_run, neg = 0.f, sum = 0.f;
 #pragma unroll 1
         for (int c = 0; c < FA_TILE / 16; ++c) {
           uint32_t su[16];
@@ -292,8 +291,29 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           float cm = sv[0];
 #pragma unroll
           for (int e = 1; e < 16; ++e) cm = fmaxf(cm, sv[e]);
-          mx = fmaxf(mx, cm);
-          if (c == 0) { m_ref = fmaxf(m_run, cm); neg = -m_ref * L2E; }
+          if (c == 0) {
+            m_ref = fmaxf(m_run, cm);
+            neg = -m_ref * L2E;
+          } else if (__any_sync(0xffffffffu, cm - m_ref > kSlack)) {
+            // raise the reference of the rows that need it and rescale what they have written so far
+            const float m_up = cm - m_ref > kSlack ? cm : m_ref;
+            const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
+            tmem_st_wait();
+            for (int cc = 0; cc < c; ++cc) {
+              uint32_t w[8];
+              tmem_ld8(acc + cc * 8, w);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float2 pv = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                w[e] = pack_half2(pv.x * f, pv.y * f);
+              }
+              tmem_st8(acc + cc * 8, w);
+            }
+            sum *= f;
+            m_ref = m_up;
+            neg = -m_ref * L2E;
+          }
           uint32_t w8[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -302,63 +322,21 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
             sum += p0 + p1;
             w8[e] = pack_half2(p0, p1);
           }
-          // keys c*16 .. +15 of row `row`: k-atom c/4, 16-byte chunks 2*(c%4) and 2*(c%4)+1
-          uint8_t* base = pt + (c >> 2) * (FA_TILE * 128);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((c & 3) * 2))) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((c & 3) * 2 + 1))) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+          tmem_st8(acc + c * 8, w8);      // keys c*16 .. +15 -> columns c*8 .. +7 (below the S columns still unread)
         }
-        if (__any_sync(0xffffffffu, mx - m_ref > kSlack)) {
-          // rare: two passes against the true row maximum (S is still intact in TMEM)
-          m_ref = fmaxf(m_run, mx);
-          neg = -m_ref * L2E;
-          sum = 0.f;
-#pragma unroll 1
-          for (int c = 0; c < FA_TILE / 16; ++c) {
-            uint32_t su[16];
-            tmem_ld16(acc + c * 16, su);
-            tmem_ld_wait();
-            float sv[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) sv[e] = __uint_as_float(su[e]);
-            if (masked) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) sv[e] += sMask[st * FA_TILE + c * 16 + e];
-            }
-            if (bias_row) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e)
-                if (k0 + c * 16 < p.ldb) sv[e] += __half2float(bias_row[(int64_t)((k0 >> 4) + c) * bias_step + e]);
-            }
-            if (masked && p.clamp) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) sv[e] = sv[e] == -INFINITY ? sv[e] : fminf(fmaxf(sv[e], -1e8f), 1e8f);
-            }
-            uint32_t w8[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float p0 = ex2f(fmaf(sv[2 * e], L2E, neg));
-              const float p1 = ex2f(fmaf(sv[2 * e + 1], L2E, neg));
-              sum += p0 + p1;
-              w8[e] = pack_half2(p0, p1);
-            }
-            uint8_t* base = pt + (c >> 2) * (FA_TILE * 128);
-            *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((c & 3) * 2))) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-            *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((c & 3) * 2 + 1))) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
-          }
-        }
+        tmem_st_wait();
         const float corr = ex2f((m_run - m_ref) * L2E);
         m_run = m_ref;
         l_run = l_run * corr + sum;
         tc_fence_before();
-        fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[sidx]);
-        // P V of this tile lands in the stream's first 32 columns
+        // P V of this tile lands in columns 64..95 of the stream's region
         if (!mbar_wait(&o_full[sidx], n_tile & 1, abort_flag, p.status, 42)) { ok = false; break; }
         tc_fence_after();
         {
           uint32_t o[32];
-          tmem_ld32(acc, o);
+          tmem_ld32(acc + 64, o);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) O[e] = fmaf(O[e], corr, __uint_as_float(o[e]));
