@@ -334,8 +334,9 @@ LF_API lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d,
  *                      x[:, :, chunk*rows : (chunk+1)*rows]    (outgoing form; rows % 16 == 0)
  *   TRIANGLE_OUTPUT    buf2 = x; pair += output(x, pair)
  *   ATTENTION_PROJECT  buf0..3 = q, k, v, gate [rows*length][128]; buf4 = this shard's pair bias
- *                      [4][ld/16][rows][16]
- *   ATTENTION_CORE     buf0..3; buf4 = every rank's bias [ranks][4][ld/16][rows][16]; buf5 = o
+ *                      [4][rows][ld] (head, query row of the shard, key)
+ *   ATTENTION_CORE     buf0..3; buf4 = the bias of all query rows [4][length][ld], the shards'
+ *                      rows in rank order under each head; buf5 = o
  *   ATTENTION_OUTPUT   buf5 = o; pair += o Wo + bo
  *   TRANSITION         pair += transition(pair)
  * The incoming triangle update and the ending-node attention run as the outgoing / starting forms

@@ -640,7 +640,7 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
   LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
                                a.bias_swap, a.w, q, k, v, g, bias, ldb));
-  LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.Q, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
+  LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));
   LF_TRY(tc::attention_output(ctx, cur, o16, a.batch, a.Q, a.transpose, a.w, a.residual ? a.act : nullptr, a.out, a.act_dtype));
   (void)f; (void)c;
   return LF_OK;
@@ -1030,7 +1030,7 @@ lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_re
       break;
     case LF_SHARD_ATTENTION_CORE:
       if (!d->mask || !b[0] || !b[1] || !b[2] || !b[3] || !b[4] || !b[5]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention core: null buffer");
-      s = tc::attention_core(ctx, cur, b[0], b[1], b[2], b[3], b[4], ld, R, d->mask, R, n, 0, 0, 1, b[5]);
+      s = tc::attention_core(ctx, cur, b[0], b[1], b[2], b[3], b[4], ld, d->mask, R, n, 0, 0, 1, b[5]);
       break;
     case LF_SHARD_ATTENTION_OUTPUT:
       if (!d->pair || !b[5]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention output: null buffer");

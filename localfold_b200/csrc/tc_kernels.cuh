@@ -46,10 +46,9 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
                           void* out);
 // out[b*Q+i][128] = (softmax_j(q_i.k_j + bias[h][i][j] + mask term_j) v_j) * gate, 4 heads x 32
 void configure_attention();
-// `bias_rows`: queries per bias block - Q for a whole pair; for a row shard the bias of every rank's
-// rows, gathered as [rank][head][16-key group][bias_rows][16]
+// `bias`: fp16 [4][Q][ldb] (head, query, key; ldb a multiple of 16) or null
 lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,
-                         const op16* bias, int ldb, int bias_rows, const float* mask, int batch, int Q, int transpose,
+                         const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose,
                          int mask_mode, int clamp, op16* out);
 
 // Fused AF2 pair transition (128 channels, 512 hidden): out = resid + relu(LN(x) W1 + b1) W2 + b2

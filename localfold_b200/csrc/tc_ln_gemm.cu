@@ -52,7 +52,7 @@ struct LnGemmParams {
   int plane_rows;           // pair rows held (n for a whole pair, fewer for a row shard)
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
-  op16* out_bias;           // fp16, tiled for the attention core: [heads][ldb/16][Q][16] (head, 16-key group, query, key)
+  op16* out_bias;           // fp16 [heads][batch rows][ldb] (head, query, key)
   int ldb;
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
@@ -543,8 +543,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
               const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q;
               const int64_t qi = ur / uq, ki = ur % uq;
               const int64_t bq = p.bias_swap ? ki : qi, bk = p.bias_swap ? qi : ki;   // bias[h][bq][bk]
-              // the bias block of these rows: [head][16-key group][batch rows][16]
-              const int64_t dst = ((bk >> 4) * p.batch + bq) * 16 + (bk & 15);
+              // row-major per head: [head][batch rows][ldb]
+              const int64_t dst = bq * p.ldb + bk;
               const int64_t qq = (int64_t)p.batch * p.ldb;
 #pragma unroll
               for (int h = 0; h < 16; ++h)

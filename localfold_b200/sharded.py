@@ -160,7 +160,7 @@ class GpuShardOps:
         self.x = torch.empty((128, R, ld), **f16)
         self.qkvg = [torch.empty((R * N, 128), **f16) for _ in range(4)]
         self.o = torch.empty((R * N, 128), **f16)
-        self.bias = torch.zeros((4, ld // 16, R, 16), **f16)
+        self.bias = torch.zeros((4, R, ld), **f16)
 
     def _step(self, op, w, pair=None, mask=None, bufs=(), chunk=0):
         d = nat.ShardStepDesc()
@@ -193,6 +193,8 @@ class GpuShardOps:
         return q, k, v, g, self.bias
 
     def attention_core(self, q, k, v, g, bias_all, mask, w):
+        # gathered [rank][head][rows][ld] -> [head][all rows][ld]
+        bias_all = bias_all.permute(1, 0, 2, 3).reshape(4, self.N, self.ld).contiguous()
         self._step(nat.SHARD_ATTENTION_CORE, w, None, mask, (q, k, v, g, bias_all, self.o))
         return self.o
 
