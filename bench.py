@@ -48,6 +48,58 @@ def contraction_flops(n: int) -> float:
     return 256.0 * n ** 3
 
 
+# Algorithmic work of one launch of each kernel family on a shard of `rows` pair rows of length n
+# (c_z = c_hidden = 128, 4 heads x 32): tensor-core FLOPs for the two contraction-shaped kernels,
+# bytes that must cross HBM for the fused LayerNorm/projection kernels (pair stream f32, operands f16).
+#   triangle_contract  128 channels x (rows x rows_b x n) GEMM            256 rows rows_b n FLOP
+#   attention          Q K^T and P V over 4 heads x 32                    512 rows n n FLOP
+#   ln_gemm            triangle projection: z in, a and b out             1024 B / position
+#                      attention projection: z in, q k v gate + bias out  1544 B / position
+#                      attention output: o and z in, z out                1280 B / position
+#   triangle_output    x and z in, z out                                  1280 B / position
+#   transition         z in, z out                                        1024 B / position
+FAMILY_WORK = {
+    "triangle_contract": ("tensor", lambda rows, n, world: 256.0 * rows * rows * n),
+    "attention": ("tensor", lambda rows, n, world: 512.0 * rows * n * n),
+    "ln_gemm": ("hbm", lambda rows, n, world: (2 * 1024 + 2 * 1544 + 2 * 1280) / 6.0 * rows * n),
+    "triangle_output": ("hbm", lambda rows, n, world: 1280.0 * rows * n),
+    "transition": ("hbm", lambda rows, n, world: 1024.0 * rows * n),
+}
+FAMILY_NAME = {
+    "triangle_contract": "triangle contraction (tcgen05, 128 batched GEMMs)",
+    "attention": "attention core (tcgen05 Q K^T and P V, softmax between them in tensor memory)",
+    "ln_gemm": "LayerNorm + projection kernels (average of the six launches)",
+    "triangle_output": "triangle output (LayerNorm of x folded into the GEMM, gate, residual)",
+    "transition": "pair transition (LayerNorm + two GEMMs, weights streamed)",
+}
+
+
+def roofline_table(families, n, world, peaks):
+    """Per kernel family: algorithmic work per launch / its measured launch time against the
+    measured peak.  Returns (the entry of the family with the largest share of the step, all entries)."""
+    rows = n // world
+    total = sum(v[0] for v in families.values()) or 1.0
+    out = []
+    for fam, (bound, work) in FAMILY_WORK.items():
+        ms, launches = families.get(fam, (0.0, 0))
+        if not launches:
+            continue
+        per_launch_ms = ms / launches
+        w = work(rows, n, world)
+        if bound == "tensor":
+            achieved, peak, unit = w / (per_launch_ms * 1e-3) / 1e12, peaks["tflops_sustained"], "TFLOP/s"
+            src = peaks["source"] + " (sustained cuBLAS bf16: the kernel runs inside a long step)"
+        else:
+            achieved, peak, unit = w / (per_launch_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+            src = peaks["source"] + " (copy bandwidth)"
+        out.append({"kernel": FAMILY_NAME[fam], "family": fam, "bound": bound, "achieved": achieved, "peak": peak,
+                    "unit": unit, "frac": achieved / peak, "traffic": None, "peak_source": src,
+                    "launch_ms": per_launch_ms, "launches": launches, "share_of_step": ms / total,
+                    "work_per_launch": w})
+    out.sort(key=lambda e: -e["share_of_step"])
+    return (out[0] if out else None), out
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -295,18 +347,7 @@ def main():
 
     if rank == 0:
         peaks = measured_peaks()
-        ct_ms, ct_launches = families["triangle_contract"]
-        roofline = None
-        if ct_launches:
-            per_launch_ms = ct_ms / ct_launches
-            # one launch: all of x on one GPU, or one gathered chunk (rows x rows x N per channel) when sharded
-            launch_flops = contraction_flops(n) if world == 1 else 256.0 * (n // world) ** 2 * n
-            achieved = launch_flops / (per_launch_ms * 1e-3) / 1e12
-            roofline = {"kernel": "triangle contraction (tcgen05, 128 batched NxNxN GEMMs)", "bound": "tensor",
-                        "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                        "frac": achieved / peaks["tflops_sustained"], "traffic": None,
-                        "peak_source": peaks["source"] + " (sustained cuBLAS bf16; the kernel runs inside a long step)",
-                        "launch_ms": per_launch_ms, "flops_per_launch": launch_flops}
+        roofline, roofline_kernels = roofline_table(families, n, world, peaks)
         cpu = None
         if not args.no_cpu:
             cpu = cpu_sample(args.cpu_sample, n)
@@ -317,7 +358,7 @@ def main():
             "dtype": "f16 operands / f32 accumulate (pair stream f32)" if args.precision == "bf16" else "f32",
             "data": "synthetic", "config": workload_config(args, world),
             "tflops_block": block_flops(n) / (ms_per_block * 1e-3) / 1e12,
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "roofline": roofline, "roofline_kernels": roofline_kernels, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "kernel_ms_per_step": {k: v[0] / args.steps for k, v in families.items() if v[1]},
             "clocks": clocks, "finite": finite,
         }
