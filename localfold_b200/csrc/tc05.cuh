@@ -54,6 +54,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `ns` per try, which
+// keeps a waiting producer off the issue port; the wake-up can lag the phase flip by about a
+// microsecond, so consumers on a critical path use the plain form.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Non-blocking test of a phase (for threads that poll several barriers).
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
@@ -80,6 +94,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 2047u) == 0) {
+      if (*abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (start == 0) start = now;
+      else if (now - start > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status && atomicCAS(&status->code, 0u, 1u) == 0u) { status->where = where; status->block = blockIdx.x; }
+        return false;
+      }
+    }
+  }
+}
+
+// For producers that run a ring ahead: parks between tries (see mbar_try_wait_parked).
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* status,
+                                          unsigned int where) {
+  if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
+  uint64_t start = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
+    if ((it & 63u) == 0) {
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (start == 0) start = now;
