@@ -11,8 +11,8 @@
 // every row reduction is thread-local) read S in 16-column pieces, add the key-mask terms,
 // exponentiate against a per-row reference and write P as packed fp16 over the S columns already
 // consumed; O += P V then runs with P as the A operand straight from tensor memory.  The row
-// reference is the maximum of the row's first 16 logits and is only raised when a later logit
-// exceeds it by more than e^8 (P stays well inside fp16); raising it rescales, in place, the P
+// reference is the maximum of the row's first 16 logits and is only raised when the exponentials
+// of a later piece sum to more than 2^15 (so P stays inside fp16); raising it rescales, in place, the P
 // columns of the current tile, the O columns and the running sum.  So in the common case a softmax
 // warp hands P over and goes straight on to the next tile, whose S already waits in the other
 // buffer: the only hand-off per tile is "P of tile u written" -> the issuer queues O += P V and,
@@ -322,8 +322,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
     const int row = q * 32 + lane;
     const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + sidx * FA_TILE;
     const float L2E = 1.4426950408889634f;
-    // A logit may exceed the row reference by up to kSlack (e^8 < 3000 fits fp16 and float32 sums easily)
-    constexpr float kSlack = 8.0f;
+    constexpr float kBig = 32768.0f;    // a piece whose 16 exponentials sum to at most this has every P < 2^15
     uint32_t n_tile = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
@@ -368,18 +367,37 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
               }
             }
           }
-          float mx[8];
+          auto piece_max = [&]() {
+            float mx[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) mx[e] = fmaxf(__uint_as_float(su[e]), __uint_as_float(su[e + 8]));
-          const float cm = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+            for (int e = 0; e < 8; ++e) mx[e] = fmaxf(__uint_as_float(su[e]), __uint_as_float(su[e + 8]));
+            return fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+          };
           if (t == 0 && c == 0) {
-            m_ref = cm;                     // key 0 exists, so this is finite
+            m_ref = piece_max();            // key 0 exists, so this is finite
             neg = -m_ref * L2E;
-          } else if (__any_sync(0xffffffffu, cm - m_ref > kSlack)) {
-            // Rare: raise the reference of the rows that need it; rescale what those rows have
-            // written of this tile's P, their O columns (once the P V steps so far have landed)
-            // and their running sum.
-            const float m_up = cm - m_ref > kSlack ? cm : m_ref;
+          }
+          uint32_t w8[8];
+          float piece_sum;
+          auto exponentials = [&]() {
+            float ps[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float p0 = ex2f(fmaf(__uint_as_float(su[2 * e]), L2E, neg));
+              const float p1 = ex2f(fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg));
+              ps[e] = p0 + p1;
+              w8[e] = pack_half2(p0, p1);
+            }
+            piece_sum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+          };
+          exponentials();
+          // The sum of the 16 exponentials bounds each of them: while it stays below kBig every P is
+          // far inside fp16 and the row reference is left alone (no maximum is searched at all).
+          if (__any_sync(0xffffffffu, !(piece_sum <= kBig))) {
+            // Rare: raise the reference of the rows that need it to their maximum so far; rescale what
+            // those rows have written of this tile's P, their O columns (once the P V steps so far
+            // have landed) and their running sum; then redo this piece.
+            const float m_up = !(piece_sum <= kBig) ? fmaxf(m_ref, piece_max()) : m_ref;
             const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
             tmem_st_wait();
             for (int cc = 0; cc < c; ++cc) {
@@ -411,17 +429,9 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
             l_run *= f;
             m_ref = m_up;
             neg = -m_ref * L2E;
+            exponentials();
           }
-          uint32_t w8[8];
-          float ps[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float p0 = ex2f(fmaf(__uint_as_float(su[2 * e]), L2E, neg));
-            const float p1 = ex2f(fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg));
-            ps[e] = p0 + p1;
-            w8[e] = pack_half2(p0, p1);
-          }
-          l_run += ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+          l_run += piece_sum;
           tmem_st8(sbuf + c * 8, w8);     // keys c*16 .. +15 -> columns c*8 .. +7
         };
         tmem_ld16(sbuf + 32, s2);
