@@ -148,8 +148,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
 
   if (warp >= LG_EPI_WARPS && warp < LG_MMA_WARP) {
     // ---------------- LayerNorm producers ----------------
-    // Eight lanes share a row (16 channels each), so one warp instruction covers four rows and a
-    // row statistic needs three shuffle steps.  Each warp owns 16 rows of the tile, handled as two
+    // Eight lanes share a row, so one warp instruction covers four rows and a row statistic needs
+    // three shuffle steps.  A lane's 16 channels are interleaved with its neighbours' so that every
+    // load instruction reads 128 contiguous bytes per row: float input, element e is channel
+    // 32 (e / 4) + 4 j + e % 4; 16-bit input, channel 64 (e / 8) + 8 j + e % 8.  Each warp owns 16 rows of the tile, handled as two
     // groups of two row-quads; the loads of a group are all issued before any is consumed.
     const int pw = warp - LG_EPI_WARPS;
     const int sub = lane >> 3, j = lane & 7;
@@ -179,10 +181,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             int64_t src = r;
             if (p.transpose && !p.a_is_op16) { const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q; src = (int64_t)(ur % uq) * p.batch + ur / uq; }
             if (p.a_is_op16) {
-              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const op16*>(p.act) + src * LG_K + 16 * j);
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const op16*>(p.act) + src * LG_K + 8 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 2; ++w4) {
-                const uint4 raw = g[w4];
+                const uint4 raw = g[w4 * 8];
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -192,10 +194,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
                 }
               }
             } else if (p.act_bf16) {
-              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K + 16 * j);
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + src * LG_K + 8 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 2; ++w4) {
-                const uint4 raw = g[w4];
+                const uint4 raw = g[w4 * 8];
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -205,10 +207,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
                 }
               }
             } else {
-              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + src * LG_K + 16 * j);
+              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + src * LG_K + 4 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 4; ++w4) {
-                const float4 f = g[w4];
+                const float4 f = g[w4 * 8];
                 v[u][w4 * 4] = f.x; v[u][w4 * 4 + 1] = f.y; v[u][w4 * 4 + 2] = f.z; v[u][w4 * 4 + 3] = f.w;
               }
             }
@@ -247,19 +249,29 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           const float var = p.variance == 2 ? sq * (1.0f / LG_K) - mean * mean : sq * (1.0f / LG_K);
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
+          // element e sits at channel ch(e): 16-bit input 64 (e / 8) + 8 j + e % 8, else 32 (e / 4) + 4 j + e % 4
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float2 gm = *reinterpret_cast<const float2*>(sGamma + 16 * j + 2 * e);
-            const float2 bt = *reinterpret_cast<const float2*>(sBeta + 16 * j + 2 * e);
+            const int ch = p.act_bf16 ? 64 * (e >> 2) + 8 * j + 2 * (e & 3) : 32 * (e >> 1) + 4 * j + 2 * (e & 1);
+            const float2 gm = *reinterpret_cast<const float2*>(sGamma + ch);
+            const float2 bt = *reinterpret_cast<const float2*>(sBeta + ch);
             packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
           }
           }
-          // channels 16j .. 16j+15: k-atom j/4, 16-byte chunks 2*(j%4) and 2*(j%4)+1 of the row
-          uint8_t* base = tile + (uint32_t)(j >> 2) * (LG_ROWS * 128);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2))) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2 + 1))) =
-              make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          if (p.a_is_op16 || p.act_bf16) {
+            // channels 64 w + 8 j .. + 7: k-atom w, 16-byte chunk j of the row
+#pragma unroll
+            for (int w2 = 0; w2 < 2; ++w2)
+              *reinterpret_cast<uint4*>(tile + (uint32_t)w2 * (LG_ROWS * 128) + swizzle128_offset((uint32_t)row, (uint32_t)j)) =
+                  make_uint4(packed[w2 * 4], packed[w2 * 4 + 1], packed[w2 * 4 + 2], packed[w2 * 4 + 3]);
+          } else {
+            // channels 32 w + 4 j .. + 3: k-atom w / 2, 16-byte chunk 4 (w % 2) + j / 2, its half j % 2
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4)
+              *reinterpret_cast<uint2*>(tile + (uint32_t)(w4 >> 1) * (LG_ROWS * 128) +
+                                        swizzle128_offset((uint32_t)row, (uint32_t)((w4 & 1) * 4 + (j >> 1))) + (j & 1) * 8) =
+                  make_uint2(packed[w4 * 2], packed[w4 * 2 + 1]);
+          }
         }
       }
       fence_async_smem();
