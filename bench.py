@@ -65,6 +65,11 @@ FAMILY_WORK = {
     "triangle_output": ("hbm", lambda rows, n, world: 1280.0 * rows * n),
     "transition": ("hbm", lambda rows, n, world: 1024.0 * rows * n),
 }
+# DRAM bytes per pair position and launch, from one ncu capture of the N = 1024 block
+# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/kernels_af2_pair_block_n1024.md).  The traffic of
+# every kernel grows with the number of pair positions, so a launch on `rows x n` positions is scaled from it.
+TRAFFIC_PER_POSITION = {"triangle_contract": 736.0, "attention": 1336.0, "ln_gemm": 1237.0,
+                        "triangle_output": 1233.0, "transition": 975.0}
 FAMILY_NAME = {
     "triangle_contract": "triangle contraction (tcgen05, 128 batched GEMMs)",
     "attention": "attention core (tcgen05 Q K^T and P V, softmax between them in tensor memory)",
@@ -93,7 +98,8 @@ def roofline_table(families, n, world, peaks):
             achieved, peak, unit = w / (per_launch_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
             src = peaks["source"] + " (copy bandwidth)"
         out.append({"kernel": FAMILY_NAME[fam], "family": fam, "bound": bound, "achieved": achieved, "peak": peak,
-                    "unit": unit, "frac": achieved / peak, "traffic": None, "peak_source": src,
+                    "unit": unit, "frac": achieved / peak, "traffic": TRAFFIC_PER_POSITION[fam] * rows * n,
+                    "traffic_source": "ncu capture at N=1024 scaled by pair positions", "peak_source": src,
                     "launch_ms": per_launch_ms, "launches": launches, "share_of_step": ms / total,
                     "work_per_launch": w})
     out.sort(key=lambda e: -e["share_of_step"])
