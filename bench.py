@@ -213,8 +213,9 @@ def workload_config(args, n_gpus):
                         f"tri-attention 4x32, transition 4x, seed 4, mask ones (BASELINE config 4 shape)",
             "length": args.length, "precision": args.precision, "pair_dtype": "f32",
             "parallelism": "single GPU" if n_gpus == 1 else
-            f"pair rows sharded over {n_gpus} GPUs (all-gather of the triangle operand b and of the pair bias, "
-            f"4 all-to-all transposes per block, NCCL)",
+            f"pair rows sharded over {n_gpus} GPUs (NCCL all-gather of the triangle operand b and of the pair bias; "
+            f"4 transposes per block by " + ("one peer-store kernel each over NVLink" if args.transpose == "peer"
+                                            else "NCCL all-to-all") + ")",
             "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * 4 / 2 ** 20)}
 
 
@@ -229,6 +230,8 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=384, help="N of the CPU oracle's bounded sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--transpose", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: transposes of the sharded pair by peer stores (one kernel) or by NCCL all-to-all")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -265,17 +268,24 @@ def main():
             stack.run(pair_d, mask_d, opts, first_block=i % 2, n_blocks=1)
     else:
         # strong scaling: the same block, pair rows sharded over the ranks
-        from localfold_b200.sharded import GpuShardOps, ShardedPairStack, TorchComm, prepared_block_weights, shard_rows
+        from localfold_b200.sharded import (GpuShardOps, PeerTranspose, ShardedPairStack, TorchComm, prepared_block_weights,
+                                            shard_rows)
         if n % (16 * world):
             raise SystemExit(f"--length {n} must be a multiple of 16 x {world} ranks")
         pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
         prepared = [lf.PreparedPairBlock(dev, w, C_Z, C_HIDDEN) for w in weights]
         block_w = [prepared_block_weights(b) for b in prepared]
-        shard = {"z": torch.from_numpy(np.ascontiguousarray(shard_rows(pair_h, rank, world))).cuda()}
         pair_h = np.ascontiguousarray(shard_rows(pair_h, rank, world))
+        transposer = None
+        if args.transpose == "peer":   # the shard lives in buffers the ranks share; transposes are peer stores
+            transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
+            transposer.shard().copy_(torch.from_numpy(pair_h))
+            shard = {"z": transposer.shard()}
+        else:
+            shard = {"z": torch.from_numpy(pair_h).cuda()}
         m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(mask_h, rank, world))).cuda()
         m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(mask_h.T), rank, world))).cuda()
-        sharded = ShardedPairStack(TorchComm(), GpuShardOps(dev, n // world, n, world))
+        sharded = ShardedPairStack(TorchComm(), GpuShardOps(dev, n // world, n, world), transposer)
         stack = None
 
         def step(i):

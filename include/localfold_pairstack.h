@@ -360,6 +360,26 @@ typedef struct lf_shard_step_desc {
 } lf_shard_step_desc;
 LF_API lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_result* r);
 
+/* ------------------------------------------------------------------------------------------
+ * Transpose of the row-sharded pair across the GPUs of one box, written directly into the
+ * peers' memory.  The reference is single-device: no counterpart there.
+ *
+ * lf_peer_buffer_create allocates a device buffer and returns its 64-byte CUDA IPC handle; the
+ * ranks (one process per GPU) exchange handles by their own means and map each other's buffers
+ * with lf_peer_buffer_open.  lf_pair_transpose_scatter then moves this rank's shard
+ * src [rows][length][vector_bytes] so that dst[d] (rank d's buffer, as mapped in this process;
+ * dst[rank] is the local one) receives zT[m][rank*rows + r] = z[r][d*rows + m]: after every rank
+ * has run it and a barrier of the caller's (e.g. an NCCL collective on the same stream) has
+ * passed, each buffer holds that rank's rows of the transposed pair.  vector_bytes = 512 (128
+ * float32 channels) or 256 (128 bf16 channels).  The kernel uses plain peer stores over NVLink.
+ * ------------------------------------------------------------------------------------------ */
+LF_API lf_status lf_peer_buffer_create(lf_context* ctx, size_t bytes, void** ptr, unsigned char handle[64]);
+LF_API lf_status lf_peer_buffer_open(lf_context* ctx, const unsigned char handle[64], void** ptr);
+LF_API lf_status lf_peer_buffer_close(lf_context* ctx, void* ptr);
+LF_API lf_status lf_peer_buffer_destroy(lf_context* ctx, void* ptr);
+LF_API lf_status lf_pair_transpose_scatter(lf_context* ctx, const void* src, int32_t rows, int32_t length,
+                                           int32_t vector_bytes, int32_t ranks, int32_t rank, void* const* dst);
+
 #ifdef __cplusplus
 }
 #endif

@@ -472,17 +472,13 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
               if (p.out_bf16) {
                 bf16* op = reinterpret_cast<bf16*>(p.out) + dst * 128 + c0;
                 if (p.resid) {
-                  const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.resid) + dst * 128 + c0);
+                  uint32_t words[8];
+                  ld_global_v8(reinterpret_cast<const bf16*>(p.resid) + dst * 128 + c0, words);
 #pragma unroll
-                  for (int w4 = 0; w4 < 2; ++w4) {
-                    const uint4 raw = rp[w4];
-                    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
-                      o[w4 * 8 + e * 2] += __low2float(h2);
-                      o[w4 * 8 + e * 2 + 1] += __high2float(h2);
-                    }
+                  for (int e = 0; e < 8; ++e) {
+                    const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                    o[e * 2] += __low2float(h2);
+                    o[e * 2 + 1] += __high2float(h2);
                   }
                 }
                 uint32_t pk[8];
@@ -494,12 +490,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
                 st_global_v8(op, pk);
               } else {
                 float* op = reinterpret_cast<float*>(p.out) + dst * 128 + c0;
-                if (p.resid) {
-                  const float4* rp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.resid) + dst * 128 + c0);
+                if (p.resid) {   // 32 bytes per load: half the L1 wavefronts of 16-byte loads for a row-per-thread access
+                  const float* rp = reinterpret_cast<const float*>(p.resid) + dst * 128 + c0;
 #pragma unroll
-                  for (int w4 = 0; w4 < 4; ++w4) {
-                    const float4 f = rp[w4];
-                    o[w4 * 4] += f.x; o[w4 * 4 + 1] += f.y; o[w4 * 4 + 2] += f.z; o[w4 * 4 + 3] += f.w;
+                  for (int w8 = 0; w8 < 2; ++w8) {
+                    uint32_t f[8];
+                    ld_global_v8(rp + w8 * 8, f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[w8 * 8 + e] += __uint_as_float(f[e]);
                   }
                 }
                 uint32_t pk[8];

@@ -128,10 +128,12 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
           const int64_t r = t * TR_ROWS + row;
           if (r < p.rows) {
             if (p.act_bf16) {
-              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + r * 128 + 16 * j);
+              // a lane's channels interleave with its neighbours' so that a load reads 128 contiguous bytes
+              // per row: 16-bit input, element e is channel 64 (e / 8) + 8 j + e % 8; float, 32 (e / 4) + 4 j + e % 4
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.act) + r * 128 + 8 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 2; ++w4) {
-                const uint4 raw = g[w4];
+                const uint4 raw = g[w4 * 8];
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -141,10 +143,10 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
                 }
               }
             } else {
-              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + r * 128 + 16 * j);
+              const float4* g = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.act) + r * 128 + 4 * j);
 #pragma unroll
               for (int w4 = 0; w4 < 4; ++w4) {
-                const float4 f = g[w4];
+                const float4 f = g[w4 * 8];
                 v[u][w4 * 4] = f.x; v[u][w4 * 4 + 1] = f.y; v[u][w4 * 4 + 2] = f.z; v[u][w4 * 4 + 3] = f.w;
               }
             }
@@ -181,15 +183,25 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
           uint32_t packed[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float2 gm = *reinterpret_cast<const float2*>(sGamma + 16 * j + 2 * e);
-            const float2 bt = *reinterpret_cast<const float2*>(sBeta + 16 * j + 2 * e);
+            const int ch = p.act_bf16 ? 64 * (e >> 2) + 8 * j + 2 * (e & 3) : 32 * (e >> 1) + 4 * j + 2 * (e & 1);
+            const float2 gm = *reinterpret_cast<const float2*>(sGamma + ch);
+            const float2 bt = *reinterpret_cast<const float2*>(sBeta + ch);
             packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
           }
-          uint8_t* base = sA + (uint32_t)(j >> 2) * (TR_ROWS * 128);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2))) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(base + swizzle128_offset((uint32_t)row, (uint32_t)((j & 3) * 2 + 1))) =
-              make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          if (p.act_bf16) {
+            // channels 64 w + 8 j .. + 7: k-atom w, 16-byte chunk j of the row
+#pragma unroll
+            for (int w2 = 0; w2 < 2; ++w2)
+              *reinterpret_cast<uint4*>(sA + (uint32_t)w2 * (TR_ROWS * 128) + swizzle128_offset((uint32_t)row, (uint32_t)j)) =
+                  make_uint4(packed[w2 * 4], packed[w2 * 4 + 1], packed[w2 * 4 + 2], packed[w2 * 4 + 3]);
+          } else {
+            // channels 32 w + 4 j .. + 3: k-atom w / 2, 16-byte chunk 4 (w % 2) + j / 2, its half j % 2
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4)
+              *reinterpret_cast<uint2*>(sA + (uint32_t)(w4 >> 1) * (TR_ROWS * 128) +
+                                        swizzle128_offset((uint32_t)row, (uint32_t)((w4 & 1) * 4 + (j >> 1))) + (j & 1) * 8) =
+                  make_uint2(packed[w4 * 2], packed[w4 * 2 + 1]);
+          }
         }
       }
       fence_async_smem();
@@ -330,17 +342,13 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
           for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v[e]) + sB2[c0 + e];
           if (out_bf16) {
             if (p.resid) {
-              const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.resid) + r * 128 + c0);
+              uint32_t words[8];
+              ld_global_v8(reinterpret_cast<const bf16*>(p.resid) + r * 128 + c0, words);
 #pragma unroll
-              for (int w4 = 0; w4 < 2; ++w4) {
-                const uint4 raw = rp[w4];
-                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
-                  o[w4 * 8 + e * 2] += __low2float(h2);
-                  o[w4 * 8 + e * 2 + 1] += __high2float(h2);
-                }
+              for (int e = 0; e < 8; ++e) {
+                const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&words[e]);
+                o[e * 2] += __low2float(h2);
+                o[e * 2 + 1] += __high2float(h2);
               }
             }
             uint32_t ob[8];
@@ -351,12 +359,14 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
             }
             st_global_v8(reinterpret_cast<bf16*>(p.out) + r * 128 + c0, ob);
           } else {
-            if (p.resid) {
-              const float4* rp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.resid) + r * 128 + c0);
+            if (p.resid) {   // 32 bytes per load: half the L1 wavefronts of 16-byte loads for a row-per-thread access
+              const float* rp = reinterpret_cast<const float*>(p.resid) + r * 128 + c0;
 #pragma unroll
-              for (int w4 = 0; w4 < 4; ++w4) {
-                const float4 f = rp[w4];
-                o[w4 * 4] += f.x; o[w4 * 4 + 1] += f.y; o[w4 * 4 + 2] += f.z; o[w4 * 4 + 3] += f.w;
+              for (int w8 = 0; w8 < 2; ++w8) {
+                uint32_t f[8];
+                ld_global_v8(rp + w8 * 8, f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[w8 * 8 + e] += __uint_as_float(f[e]);
               }
             }
             uint32_t ob[8];

@@ -98,12 +98,107 @@ def transpose_shard(comm, z):
     return recv.permute(2, 0, 1, 3).reshape(R, N, C).contiguous()          # [my col][src*R + row][C]
 
 
-class ShardedPairStack:
-    """Runs AF2 pair blocks on a row shard.  `ops` does the arithmetic, `comm` the exchanges."""
+class _DeviceArray:
+    """A raw device allocation seen through ``__cuda_array_interface__`` (for ``torch.as_tensor``)."""
 
-    def __init__(self, comm, ops):
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+class PeerTranspose:
+    """Transposes of the row-sharded pair with one kernel per rank that stores into the peers' memory
+    (``lf_pair_transpose_scatter``), instead of pack -> all-to-all -> unpack.
+
+    Each rank holds two shard-sized buffers allocated by the library and shared with the other ranks'
+    processes as CUDA IPC handles; the pair shard lives in one of them, and a transpose writes every
+    rank's other buffer.  An all-reduce of one element on the same stream follows the kernel: when it
+    has passed, every peer's stores into this rank's buffer have landed.  A buffer is written again
+    only two transposes later, after its owner's own reading kernel and a barrier, so one barrier per
+    transpose is enough.  GPUs of one box only.
+    """
+
+    def __init__(self, device, group, rows, length, dtype):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.group, self.dev = torch, dist, group, device
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.R, self.N = int(rows), int(length)
+        if self.R * self.world != self.N:
+            raise ValueError("shard rows times ranks must equal the row length")
+        self.dtype = dtype
+        self.vector_bytes = 128 * (4 if dtype == torch.float32 else 2)
+        nbytes = self.R * self.N * self.vector_bytes
+        lib = device.lib
+        self.local, handles = [], []
+        for _ in range(2):
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            device.check(lib.lf_peer_buffer_create(device.handle, nbytes, ctypes.byref(ptr), handle))
+            self.local.append(ptr.value)
+            handles.append(handle.raw)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self.mapped = []        # [buffer][rank] -> device pointer valid in this process
+        self.opened = []
+        for b in range(2):
+            row = []
+            for g in range(self.world):
+                if g == self.rank:
+                    row.append(self.local[b])
+                    continue
+                ptr = ctypes.c_void_p()
+                device.check(lib.lf_peer_buffer_open(device.handle, gathered[g][b], ctypes.byref(ptr)))
+                row.append(ptr.value)
+                self.opened.append(ptr.value)
+            self.mapped.append(row)
+        typestr = "<f4" if dtype == torch.float32 else "<u2"
+        views = [torch.as_tensor(_DeviceArray(p, (self.R, self.N, 128), typestr), device=f"cuda:{device.ordinal}") for p in self.local]
+        self.views = [v if dtype == torch.float32 else v.view(torch.bfloat16) for v in views]
+        self.flag = torch.zeros(1, device=f"cuda:{device.ordinal}")
+        self.current = 0
+        dist.barrier(group=group)
+
+    def shard(self):
+        """The tensor the pair shard lives in right now ([rows][length][128])."""
+        return self.views[self.current]
+
+    def transpose(self, z):
+        """z must be `shard()`.  Returns the other buffer, holding this rank's rows of the transposed pair."""
+        if z.data_ptr() != self.local[self.current]:
+            raise ValueError("the pair shard must live in the buffer shard() returned")
+        other = 1 - self.current
+        dst = (ctypes.c_void_p * self.world)(*self.mapped[other])
+        self.dev.check(self.dev.lib.lf_pair_transpose_scatter(self.dev.handle, self.local[self.current], self.R, self.N,
+                                                              self.vector_bytes, self.world, self.rank, dst))
+        self.dist.all_reduce(self.flag, group=self.group)     # stream-ordered barrier: all stores have landed
+        self.current = other
+        return self.views[other]
+
+    def close(self):
+        lib = self.dev.lib
+        self.dev.synchronize()
+        self.dist.barrier(group=self.group)
+        for p in self.opened:
+            lib.lf_peer_buffer_close(self.dev.handle, p)
+        self.dist.barrier(group=self.group)
+        for p in self.local:
+            lib.lf_peer_buffer_destroy(self.dev.handle, p)
+        self.opened, self.local = [], []
+
+
+class ShardedPairStack:
+    """Runs AF2 pair blocks on a row shard.  `ops` does the arithmetic, `comm` the exchanges;
+    `transposer` (a ``PeerTranspose``) replaces the all-to-all transposes when given - the shard
+    must then live in ``transposer.shard()``."""
+
+    def __init__(self, comm, ops, transposer=None):
         self.comm = comm
         self.ops = ops
+        self.transposer = transposer
+
+    def _transpose(self, z):
+        return self.transposer.transpose(z) if self.transposer is not None else transpose_shard(self.comm, z)
 
     def _triangle(self, z, mask, w):
         ops, comm = self.ops, self.comm
@@ -125,14 +220,14 @@ class ShardedPairStack:
         """One block on the local shard `z` (updated and returned; it may be a new tensor)."""
         comm = self.comm
         self._triangle(z, mask_rows, w["triangle_outgoing"])
-        z = transpose_shard(comm, z)
+        z = self._transpose(z)
         self._triangle(z, mask_t_rows, w["triangle_incoming"])
-        z = transpose_shard(comm, z)
+        z = self._transpose(z)
         self._attention(z, mask_rows, w["attention_starting"])
-        z = transpose_shard(comm, z)
+        z = self._transpose(z)
         self._attention(z, mask_t_rows, w["attention_ending"])
         self.ops.transition(z, w["transition"])
-        z = transpose_shard(comm, z)
+        z = self._transpose(z)
         return z
 
     def run(self, z, mask_rows, mask_t_rows, blocks):

@@ -1,6 +1,7 @@
 """Row-sharded pair block on the GPU: two ranks (two processes on one device, exchanging through gloo
 with host staging, so no NCCL and no second GPU is needed) run the library's shard steps and must
-match the unsharded CPU oracle within the 16-bit per-block bound."""
+match the unsharded CPU oracle within the 16-bit per-block bound.  One case moves the transposes
+to the peer-store kernel (buffers shared between the two processes as CUDA IPC handles)."""
 import os
 import sys
 
@@ -14,14 +15,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, n, result_path):
+def _worker(rank, world, port, n, result_path, peer):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import localfold_b200 as lf
     from localfold_b200 import synthetic as syn
-    from localfold_b200.sharded import GpuShardOps, ShardedPairStack, TorchComm, prepared_block_weights, shard_rows
+    from localfold_b200.sharded import (GpuShardOps, PeerTranspose, ShardedPairStack, TorchComm, prepared_block_weights,
+                                        shard_rows)
 
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
@@ -32,10 +34,17 @@ def _worker(rank, world, port, n, result_path):
     z = torch.from_numpy(np.ascontiguousarray(shard_rows(pair, rank, world))).cuda()
     m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(mask, rank, world))).cuda()
     m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(mask.T), rank, world))).cuda()
-    stack = ShardedPairStack(TorchComm(via_host=True), GpuShardOps(dev, n // world, n, world))
+    transposer = None
+    if peer:   # transposes by peer stores between the two processes' buffers (CUDA IPC), barrier through gloo
+        transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
+        transposer.shard().copy_(z)
+        z = transposer.shard()
+    stack = ShardedPairStack(TorchComm(via_host=True), GpuShardOps(dev, n // world, n, world), transposer)
     z = stack.run(z, m_rows, m_t_rows, [prepared_block_weights(b) for b in blocks])
     dev.synchronize()
     host = z.cpu()
+    if transposer is not None:
+        transposer.close()
     gathered = [torch.empty_like(host) for _ in range(world)]
     dist.all_gather(gathered, host)
     if rank == 0:
@@ -46,14 +55,14 @@ def _worker(rank, world, port, n, result_path):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n", [64, 160])
-def test_sharded_gpu_block_matches_oracle(tmp_path, n):
+@pytest.mark.parametrize("n,peer", [(64, False), (160, False), (160, True)])
+def test_sharded_gpu_block_matches_oracle(tmp_path, n, peer):
     sys.path.insert(0, ROOT)
     from localfold_b200 import synthetic as syn
     from oracle import oracle
     port = 29800 + os.getpid() % 150
     result = str(tmp_path / "pair.npy")
-    mp.spawn(_worker, args=(2, port, n, result), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, n, result, peer), nprocs=2, join=True)
     got = np.load(result)
     pair, mask, weights = syn.af2_pair_block(21, n, blocks=2, masked_tail=0.1)
     want = pair
