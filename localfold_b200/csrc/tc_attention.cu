@@ -55,6 +55,19 @@ struct FlashParams {
   Status* status;
 };
 
+// Two exponentials per MUFU operation: 2^x for a packed pair of fp16 arguments, fp16 results
+// (relative error about 2^-10, the same order as the fp16 rounding P gets anyway).
+__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
+  uint32_t y;
+  asm("add.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
+  return y;
+}
+
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -380,15 +393,15 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           uint32_t w8[8];
           float piece_sum;
           auto exponentials = [&]() {
-            float ps[8];
+            // arguments in float32, rounded to a packed fp16 pair, exponentiated two at a time; the
+            // piece sum adds the same fp16 values that go into P V (pairwise in fp16, then float32)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float p0 = ex2f(fmaf(__uint_as_float(su[2 * e]), L2E, neg));
-              const float p1 = ex2f(fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg));
-              ps[e] = p0 + p1;
-              w8[e] = pack_half2(p0, p1);
-            }
-            piece_sum = ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
+            for (int e = 0; e < 8; ++e)
+              w8[e] = ex2_h2(pack_half2(fmaf(__uint_as_float(su[2 * e]), L2E, neg), fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg)));
+            const uint32_t t4 = hadd2_u(hadd2_u(hadd2_u(w8[0], w8[1]), hadd2_u(w8[2], w8[3])),
+                                        hadd2_u(hadd2_u(w8[4], w8[5]), hadd2_u(w8[6], w8[7])));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&t4));
+            piece_sum = f2.x + f2.y;
           };
           exponentials();
           // The sum of the 16 exponentials bounds each of them: while it stays below kBig every P is
