@@ -355,114 +355,112 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tc_fence_after();
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 0);
         const bool masked = mask_flag[st] != 0;
-        // the tile's 48 S columns go to registers in three pieces, each requested before the piece
-        // ahead of it is worked on; P overwrites columns whose S is already in registers
+        // The tile's 48 S columns go to registers; the three 16-key pieces are then independent chains
+        // (mask terms, exponentials, sums) that the scheduler interleaves, and one vote per tile decides
+        // whether the row reference has to be raised.  P is stored only after that, so the rare slow
+        // path can read S again.
         uint32_t s0[16], s1[16], s2[16];
-        tmem_ld16(sbuf, s0);
-        tmem_ld16(sbuf + 16, s1);
-        tmem_ld_wait();
-        auto piece = [&](uint32_t (&su)[16], const int c) {
+        auto load_s = [&]() {
+          tmem_ld16(sbuf, s0);
+          tmem_ld16(sbuf + 16, s1);
+          tmem_ld16(sbuf + 32, s2);
+          tmem_ld_wait();
           if (masked) {
-            const float4* mt = reinterpret_cast<const float4*>(sMask + st * FA_KT + c * 16);
+            auto add_terms = [&](uint32_t (&su)[16], const int c) {
+              const float4* mt = reinterpret_cast<const float4*>(sMask + st * FA_KT + c * 16);
 #pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4) {
-              const float4 m = mt[j4];
-              su[j4 * 4] = __float_as_uint(__uint_as_float(su[j4 * 4]) + m.x);
-              su[j4 * 4 + 1] = __float_as_uint(__uint_as_float(su[j4 * 4 + 1]) + m.y);
-              su[j4 * 4 + 2] = __float_as_uint(__uint_as_float(su[j4 * 4 + 2]) + m.z);
-              su[j4 * 4 + 3] = __float_as_uint(__uint_as_float(su[j4 * 4 + 3]) + m.w);
-            }
-            if (p.clamp) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) {   // keys past the end stay at -inf: they are not keys at all
-                const float v = __uint_as_float(su[e]);
-                su[e] = __float_as_uint(v == -INFINITY ? v : fminf(fmaxf(v, -1e8f), 1e8f));
+              for (int j4 = 0; j4 < 4; ++j4) {
+                const float4 m = mt[j4];
+                su[j4 * 4] = __float_as_uint(__uint_as_float(su[j4 * 4]) + m.x);
+                su[j4 * 4 + 1] = __float_as_uint(__uint_as_float(su[j4 * 4 + 1]) + m.y);
+                su[j4 * 4 + 2] = __float_as_uint(__uint_as_float(su[j4 * 4 + 2]) + m.z);
+                su[j4 * 4 + 3] = __float_as_uint(__uint_as_float(su[j4 * 4 + 3]) + m.w);
               }
-            }
-          }
-          auto piece_max = [&]() {
-            float mx[8];
+              if (p.clamp) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) mx[e] = fmaxf(__uint_as_float(su[e]), __uint_as_float(su[e + 8]));
-            return fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-          };
-          if (t == 0 && c == 0) {
-            m_ref = piece_max();            // key 0 exists, so this is finite
-            neg = -m_ref * L2E;
-          }
-          uint32_t w8[8];
-          float piece_sum;
-          auto exponentials = [&]() {
-            // arguments in float32, rounded to a packed fp16 pair, exponentiated two at a time; the
-            // piece sum adds the same fp16 values that go into P V (pairwise in fp16, then float32)
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              w8[e] = ex2_h2(pack_half2(fmaf(__uint_as_float(su[2 * e]), L2E, neg), fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg)));
-            const uint32_t t4 = hadd2_u(hadd2_u(hadd2_u(w8[0], w8[1]), hadd2_u(w8[2], w8[3])),
-                                        hadd2_u(hadd2_u(w8[4], w8[5]), hadd2_u(w8[6], w8[7])));
-            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&t4));
-            piece_sum = f2.x + f2.y;
-          };
-          exponentials();
-          // The sum of the 16 exponentials bounds each of them: while it stays below kBig every P is
-          // far inside fp16 and the row reference is left alone (no maximum is searched at all).
-          if (__any_sync(0xffffffffu, !(piece_sum <= kBig))) {
-            // Rare: raise the reference of the rows that need it to their maximum so far; rescale what
-            // those rows have written of this tile's P, their O columns (once the P V steps so far
-            // have landed) and their running sum; then redo this piece.
-            const float m_up = !(piece_sum <= kBig) ? fmaxf(m_ref, piece_max()) : m_ref;
-            const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
-            tmem_st_wait();
-            for (int cc = 0; cc < c; ++cc) {
-              uint32_t w[8];
-              tmem_ld8(sbuf + cc * 8, w);
-              tmem_ld_wait();
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float2 pv = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
-                w[e] = pack_half2(pv.x * f, pv.y * f);
-              }
-              tmem_st8(sbuf + cc * 8, w);
-            }
-            if (t > 0) {
-              if (!mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 43)) ok = false;
-              tc_fence_after();
-              if (ok) {
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                  uint32_t o[16];
-                  tmem_ld16(acc + FA_O_COL + half * 16, o);
-                  tmem_ld_wait();
-#pragma unroll
-                  for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-                  tmem_st16(acc + FA_O_COL + half * 16, o);
+                for (int e = 0; e < 16; ++e) {   // keys past the end stay at -inf: they are not keys at all
+                  const float v = __uint_as_float(su[e]);
+                  su[e] = __float_as_uint(v == -INFINITY ? v : fminf(fmaxf(v, -1e8f), 1e8f));
                 }
               }
-            }
-            l_run *= f;
-            m_ref = m_up;
-            neg = -m_ref * L2E;
-            exponentials();
+            };
+            add_terms(s0, 0);
+            add_terms(s1, 1);
+            add_terms(s2, 2);
           }
-          l_run += piece_sum;
-          tmem_st8(sbuf + c * 8, w8);     // keys c*16 .. +15 -> columns c*8 .. +7
         };
-        tmem_ld16(sbuf + 32, s2);
-        piece(s0, 0);
-        piece(s1, 1);
-        tmem_ld_wait();
-        piece(s2, 2);
+        auto piece_max = [&](const uint32_t (&su)[16]) {
+          float mx[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mx[e] = fmaxf(__uint_as_float(su[e]), __uint_as_float(su[e + 8]));
+          return fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        };
+        // arguments in float32, rounded to a packed fp16 pair, exponentiated two at a time; the piece sum
+        // adds the same fp16 values that go into P V (pairwise in fp16, then float32)
+        auto exponentials = [&](const uint32_t (&su)[16], uint32_t (&w)[8]) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            w[e] = ex2_h2(pack_half2(fmaf(__uint_as_float(su[2 * e]), L2E, neg), fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg)));
+          const uint32_t t4 = hadd2_u(hadd2_u(hadd2_u(w[0], w[1]), hadd2_u(w[2], w[3])), hadd2_u(hadd2_u(w[4], w[5]), hadd2_u(w[6], w[7])));
+          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&t4));
+          return f2.x + f2.y;
+        };
+        load_s();
+        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 2);
+        if (t == 0) {
+          m_ref = fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)));   // key 0 exists, so this is finite
+          neg = -m_ref * L2E;
+        }
+        uint32_t w0[8], w1[8], w2[8];
+        float a0 = exponentials(s0, w0), a1 = exponentials(s1, w1), a2 = exponentials(s2, w2);
+        // The sum of a piece's 16 exponentials bounds each of them: while it stays below kBig every P is
+        // far inside fp16 and the row reference is left alone (no maximum is searched at all).
+        const bool over = !(a0 <= kBig) || !(a1 <= kBig) || !(a2 <= kBig);
+        if (__any_sync(0xffffffffu, over)) {
+          // Rare: raise the reference of the rows that need it to their maximum so far; rescale their O
+          // columns (once the P V steps so far have landed) and their running sum; then redo the tile.
+          load_s();
+          const float m_up = over ? fmaxf(m_ref, fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)))) : m_ref;
+          const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
+          if (t > 0) {
+            if (!mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 43)) ok = false;
+            tc_fence_after();
+            if (ok) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                uint32_t o[16];
+                tmem_ld16(acc + FA_O_COL + half * 16, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+                tmem_st16(acc + FA_O_COL + half * 16, o);
+              }
+            }
+          }
+          l_run *= f;
+          m_ref = m_up;
+          neg = -m_ref * L2E;
+          a0 = exponentials(s0, w0);
+          a1 = exponentials(s1, w1);
+          a2 = exponentials(s2, w2);
+        }
+        l_run += (a0 + a1) + a2;
+        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 3);
+        tmem_st8(sbuf, w0);          // keys c*16 .. +15 -> columns c*8 .. +7
+        tmem_st8(sbuf + 8, w1);
+        tmem_st8(sbuf + 16, w2);
         if (!ok) break;
         tmem_st_wait();
+        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 7);
         // Stay within one phase of the "P V landed" barrier (a parity test cannot tell phases two apart).
         // This comes before the arrive below: once this warp has arrived, P V of this tile may land at
         // any time.  P V of the previous tile was queued a whole tile ago, so this rarely waits.
         if (n_tile > 0 && !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 44)) { ok = false; break; }
+        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 8);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[g * 2 + (n_tile & 1)]);
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 1);
-        if (q == 1 && lane == 0) FA_TRACE(sidx, n_tile, 8);
         if (q == 3 && lane == 0) FA_TRACE(sidx, n_tile, 9);
 
       }
