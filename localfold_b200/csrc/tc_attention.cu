@@ -2,7 +2,7 @@
 //
 // Work item = (batch row b, pair of 128-query tiles, pair of heads): four independent streams
 // (query tile g, head h) that share the K and V tiles of the head pair, which stream through a
-// four-stage TMA ring of 48-key tiles (both heads of the pair share a 128-byte swizzled row).
+// five-stage TMA ring of 48-key tiles (both heads of the pair share a 128-byte swizzled row).
 //
 // Per stream, tensor memory holds two S / P buffers (48 columns each) and the output accumulator O
 // (32 columns): 128 columns per stream, 512 in all.
@@ -35,7 +35,7 @@ using namespace tc05;
 constexpr int FA_THREADS = 20 * 32;
 constexpr int FA_TILE = 128;                        // query rows per stream
 constexpr int FA_KT = 48;                           // keys per tile
-constexpr int FA_STAGES = 4;                        // K/V ring
+constexpr int FA_STAGES = 5;                        // K/V ring
 constexpr int FA_Q_BYTES = FA_TILE * 128;           // per query tile: 128 rows x (2 heads x 32 x 2 B)
 constexpr int FA_KV_BYTES = FA_KT * 128;            // K or V of one tile, both heads
 constexpr int FA_BIAS_BYTES = FA_TILE * 64 * 2;     // one stream's bias tile: 128 queries x 64 keys fetched (48 used), fp16
@@ -54,19 +54,6 @@ struct FlashParams {
   op16* out;               // [batch*Q][128]
   Status* status;
 };
-
-// Two exponentials per MUFU operation: 2^x for a packed pair of fp16 arguments, fp16 results
-// (relative error about 2^-10, the same order as the fp16 rounding P gets anyway).
-__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
-  uint32_t y;
-  asm("add.f16x2 %0, %1, %2;" : "=r"(y) : "r"(a), "r"(b));
-  return y;
-}
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
@@ -98,13 +85,13 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   uint64_t* q_full = bars;           // 1
   uint64_t* q_empty = bars + 1;      // count 2: one commit per issuer
   uint64_t* kv_full = bars + 2;      // [stage] count 2: TMA bytes + mask terms
-  uint64_t* kv_empty = bars + 6;     // [stage] count 2: one commit per issuer
-  uint64_t* s_full = bars + 10;      // [issuer][buffer]: S of both its streams is there
-  uint64_t* p_full = bars + 14;      // [issuer][buffer] count 8: the eight softmax warps of its two streams
-  uint64_t* o_full = bars + 18;      // [issuer] one phase per key tile: P V of both streams has landed
-  uint64_t* b_full = bars + 20;      // [issuer][slot]
-  uint64_t* b_empty = bars + 24;     // [issuer][slot]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
+  uint64_t* kv_empty = kv_full + FA_STAGES;     // [stage] count 2: one commit per issuer
+  uint64_t* s_full = kv_empty + FA_STAGES;      // [issuer][buffer]: S of both its streams is there
+  uint64_t* p_full = s_full + 4;     // [issuer][buffer] count 8: the eight softmax warps of its two streams
+  uint64_t* o_full = p_full + 4;     // [issuer] one phase per key tile: P V of both streams has landed
+  uint64_t* b_full = o_full + 2;     // [issuer][slot]
+  uint64_t* b_empty = b_full + 2 * FA_BIAS_SLOTS;     // [issuer][slot]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_empty + 2 * FA_BIAS_SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* mask_flag = abort_flag + 1;      // [stage]: the stage has a non-zero term
 
@@ -156,7 +143,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
       for (int t = 0; t < T && ok; ++t, ++n_kv) {
         const int st = n_kv % FA_STAGES;
         if (lane == 0) {
-          if (!mbar_wait_parked(&kv_empty[st], ((n_kv / FA_STAGES) & 1) ^ 1, abort_flag, p.status, 21)) ok = false;
+          if (!mbar_wait(&kv_empty[st], ((n_kv / FA_STAGES) & 1) ^ 1, abort_flag, p.status, 21)) ok = false;   // not parked: the ring is only a few tiles deep
           else {
             mbar_expect_tx(&kv_full[st], 2 * FA_KV_BYTES);
             tma_load_3d(sK + st * FA_KV_BYTES, &mapK, &kv_full[st], hp * 64, t * FA_KT, b);
@@ -395,15 +382,19 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           for (int e = 0; e < 8; ++e) mx[e] = fmaxf(__uint_as_float(su[e]), __uint_as_float(su[e + 8]));
           return fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         };
-        // arguments in float32, rounded to a packed fp16 pair, exponentiated two at a time; the piece sum
-        // adds the same fp16 values that go into P V (pairwise in fp16, then float32)
+        // float32 exponentials: the packed fp16 form (ex2.approx.f16x2) measured slower per element, and
+        // handing the exponent unit from warp to warp in turn (to keep the four warps of a scheduler out
+        // of step) measured no gain - the wake-up costs what the stagger saves
         auto exponentials = [&](const uint32_t (&su)[16], uint32_t (&w)[8]) {
+          float ps[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            w[e] = ex2_h2(pack_half2(fmaf(__uint_as_float(su[2 * e]), L2E, neg), fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg)));
-          const uint32_t t4 = hadd2_u(hadd2_u(hadd2_u(w[0], w[1]), hadd2_u(w[2], w[3])), hadd2_u(hadd2_u(w[4], w[5]), hadd2_u(w[6], w[7])));
-          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&t4));
-          return f2.x + f2.y;
+          for (int e = 0; e < 8; ++e) {
+            const float p0 = ex2f(fmaf(__uint_as_float(su[2 * e]), L2E, neg));
+            const float p1 = ex2f(fmaf(__uint_as_float(su[2 * e + 1]), L2E, neg));
+            ps[e] = p0 + p1;
+            w[e] = pack_half2(p0, p1);
+          }
+          return ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         };
         load_s();
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 2);
