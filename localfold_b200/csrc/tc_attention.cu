@@ -333,35 +333,24 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
       const int qi = (2 * qp + g) * FA_TILE + row;
       const bool qvalid = qi < p.Q;
       float m_ref = 0.f, neg = 0.f, l_run = 0.f;
-      // S of a tile in registers.  Within an item the next tile's S is requested as soon as this tile's
-      // P is on its way to tensor memory, so its latency and barrier waits hide behind the hand-off.
-      uint32_t s0[16], s1[16], s2[16];
-      auto request_s = [&](uint32_t buf) {
-        tmem_ld16(buf, s0);
-        tmem_ld16(buf + 16, s1);
-        tmem_ld16(buf + 32, s2);
-      };
-      // waits for S of tile `nt` (and for the key terms of its stage, published through kv_full), then requests it
-      auto await_and_request = [&](uint32_t nt) -> bool {
-        if (!mbar_wait(&s_full[g * 2 + (nt & 1)], (nt >> 1) & 1, abort_flag, p.status, 40)) return false;
-        if (!mbar_wait(&kv_full[nt % FA_STAGES], (nt / FA_STAGES) & 1, abort_flag, p.status, 41)) return false;
-        tc_fence_after();
-        request_s(acc + (nt & 1) * FA_KT);
-        return true;
-      };
-      bool requested = false;
       for (int t = 0; t < T && ok; ++t, ++n_tile) {
         const int st = n_tile % FA_STAGES;
         const uint32_t sbuf = acc + (n_tile & 1) * FA_KT;
-        if (!requested && !await_and_request(n_tile)) { ok = false; break; }
-        requested = false;
+        if (!mbar_wait(&s_full[g * 2 + (n_tile & 1)], (n_tile >> 1) & 1, abort_flag, p.status, 40)) { ok = false; break; }
+        // key terms of this stage were published through kv_full
+        if (!mbar_wait(&kv_full[st], (n_tile / FA_STAGES) & 1, abort_flag, p.status, 41)) { ok = false; break; }
+        tc_fence_after();
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 0);
         const bool masked = mask_flag[st] != 0;
         // The tile's 48 S columns go to registers; the three 16-key pieces are then independent chains
         // (mask terms, exponentials, sums) that the scheduler interleaves, and one vote per tile decides
         // whether the row reference has to be raised.  P is stored only after that, so the rare slow
         // path can read S again.
-        auto finish_s = [&]() {
+        uint32_t s0[16], s1[16], s2[16];
+        auto load_s = [&]() {
+          tmem_ld16(sbuf, s0);
+          tmem_ld16(sbuf + 16, s1);
+          tmem_ld16(sbuf + 32, s2);
           tmem_ld_wait();
           if (masked) {
             auto add_terms = [&](uint32_t (&su)[16], const int c) {
@@ -407,7 +396,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           }
           return ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         };
-        finish_s();
+        load_s();
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 2);
         if (t == 0) {
           m_ref = fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)));   // key 0 exists, so this is finite
@@ -421,8 +410,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         if (__any_sync(0xffffffffu, over)) {
           // Rare: raise the reference of the rows that need it to their maximum so far; rescale their O
           // columns (once the P V steps so far have landed) and their running sum; then redo the tile.
-          request_s(sbuf);
-          finish_s();
+          load_s();
           const float m_up = over ? fmaxf(m_ref, fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)))) : m_ref;
           const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
           if (t > 0) {
@@ -453,10 +441,6 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tmem_st8(sbuf + 8, w1);
         tmem_st8(sbuf + 16, w2);
         if (!ok) break;
-        if (t + 1 < T) {     // the next tile's S, while the stores drain and the hand-off below runs
-          if (!await_and_request(n_tile + 1)) { ok = false; break; }
-          requested = true;
-        }
         tmem_st_wait();
         if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 7);
         // Stay within one phase of the "P V landed" barrier (a parity test cannot tell phases two apart).
