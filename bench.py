@@ -278,7 +278,18 @@ def main():
         pair_h = np.ascontiguousarray(shard_rows(pair_h, rank, world))
         transposer = None
         if args.transpose == "peer":   # the shard lives in buffers the ranks share; transposes are peer stores
-            transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
+            try:
+                transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
+                mapped = 1
+            except Exception as exc:   # e.g. no peer access between two of the GPUs: every rank falls back together
+                print(f"rank {rank}: peer mapping failed ({exc}); using NCCL all-to-all transposes", file=sys.stderr)
+                mapped = 0
+            flag = torch.tensor([mapped], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                transposer = None
+                args.transpose = "nccl"
+        if transposer is not None:
             transposer.shard().copy_(torch.from_numpy(pair_h))
             shard = {"z": transposer.shard()}
         else:

@@ -130,28 +130,43 @@ class PeerTranspose:
         self.vector_bytes = 128 * (4 if dtype == torch.float32 else 2)
         nbytes = self.R * self.N * self.vector_bytes
         lib = device.lib
-        self.local, handles = [], []
-        for _ in range(2):
-            ptr = ctypes.c_void_p()
-            handle = ctypes.create_string_buffer(64)
-            device.check(lib.lf_peer_buffer_create(device.handle, nbytes, ctypes.byref(ptr), handle))
-            self.local.append(ptr.value)
-            handles.append(handle.raw)
+        self.local, self.opened, self.mapped = [], [], []
+        handles, error = [], None
+        try:
+            for _ in range(2):
+                ptr = ctypes.c_void_p()
+                handle = ctypes.create_string_buffer(64)
+                device.check(lib.lf_peer_buffer_create(device.handle, nbytes, ctypes.byref(ptr), handle))
+                self.local.append(ptr.value)
+                handles.append(handle.raw)
+        except Exception as exc:      # keep going: every rank must reach the collectives below
+            error = exc
+            handles = [b"", b""]
         gathered = [None] * self.world
         dist.all_gather_object(gathered, handles, group=group)
-        self.mapped = []        # [buffer][rank] -> device pointer valid in this process
-        self.opened = []
-        for b in range(2):
-            row = []
-            for g in range(self.world):
-                if g == self.rank:
-                    row.append(self.local[b])
-                    continue
-                ptr = ctypes.c_void_p()
-                device.check(lib.lf_peer_buffer_open(device.handle, gathered[g][b], ctypes.byref(ptr)))
-                row.append(ptr.value)
-                self.opened.append(ptr.value)
-            self.mapped.append(row)
+        if error is None and all(len(h[0]) == 64 for h in gathered):
+            try:
+                for b in range(2):       # [buffer][rank] -> device pointer valid in this process
+                    row = []
+                    for g in range(self.world):
+                        if g == self.rank:
+                            row.append(self.local[b])
+                            continue
+                        ptr = ctypes.c_void_p()
+                        device.check(lib.lf_peer_buffer_open(device.handle, gathered[g][b], ctypes.byref(ptr)))
+                        row.append(ptr.value)
+                        self.opened.append(ptr.value)
+                    self.mapped.append(row)
+            except Exception as exc:
+                error = exc
+        elif error is None:
+            error = RuntimeError("another rank could not allocate its peer buffers")
+        # all ranks agree on the outcome before anyone relies on the mapping
+        verdicts = [None] * self.world
+        dist.all_gather_object(verdicts, error is None, group=group)
+        if not all(verdicts):
+            self._release()
+            raise error if error is not None else RuntimeError("another rank could not map the peer buffers")
         typestr = "<f4" if dtype == torch.float32 else "<u2"
         views = [torch.as_tensor(_DeviceArray(p, (self.R, self.N, 128), typestr), device=f"cuda:{device.ordinal}") for p in self.local]
         self.views = [v if dtype == torch.float32 else v.view(torch.bfloat16) for v in views]
@@ -175,16 +190,19 @@ class PeerTranspose:
         self.current = other
         return self.views[other]
 
-    def close(self):
+    def _release(self):
         lib = self.dev.lib
-        self.dev.synchronize()
-        self.dist.barrier(group=self.group)
         for p in self.opened:
             lib.lf_peer_buffer_close(self.dev.handle, p)
-        self.dist.barrier(group=self.group)
+        self.dist.barrier(group=self.group)      # nobody frees a buffer a peer still has mapped
         for p in self.local:
             lib.lf_peer_buffer_destroy(self.dev.handle, p)
         self.opened, self.local = [], []
+
+    def close(self):
+        self.dev.synchronize()
+        self.dist.barrier(group=self.group)
+        self._release()
 
 
 class ShardedPairStack:
