@@ -54,6 +54,17 @@ class TorchComm:
             out = flat.view((self.world,) + tuple(src.shape))
         return out.to(t.device) if self.via_host else out
 
+    def all_gather_async(self, t):
+        """Starts the gather; returns (gathered [world, ...], work).  `work.wait()` orders the current
+        stream after the transfer; work is None when the gather already completed (host-staged backends)."""
+        import torch
+        if self.via_host or self.dist.get_backend(self.group) == "gloo":
+            return self.all_gather(t), None
+        src = t.contiguous()
+        flat = torch.empty((self.world * src.shape[0],) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
+        work = self.dist.all_gather_into_tensor(flat, src, group=self.group, async_op=True)
+        return flat.view((self.world,) + tuple(src.shape)), work
+
     def all_to_all(self, t):
         """t: [world, ...]; block g goes to rank g; returns the blocks received, by source rank."""
         import torch
@@ -221,10 +232,14 @@ class ShardedPairStack:
     def _triangle(self, z, mask, w):
         ops, comm = self.ops, self.comm
         a, b = ops.triangle_project(z, mask, w)
-        b_all = comm.all_gather(b)
+        b_all, work = comm.all_gather_async(b)
         x = ops.new_product()
+        ops.triangle_contract(a, b, x, comm.rank, w)      # the local chunk runs while the others travel
+        if work is not None:
+            work.wait()
         for g in range(comm.world):
-            ops.triangle_contract(a, b_all[g], x, g, w)
+            if g != comm.rank:
+                ops.triangle_contract(a, b_all[g], x, g, w)
         ops.triangle_output(x, z, w)
 
     def _attention(self, z, mask, w):
