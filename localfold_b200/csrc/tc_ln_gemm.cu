@@ -304,7 +304,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
     }
   } else if (warp == LG_MMA_WARP) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop (uniform control flow and operand values, so the operands of the
+    // MMA instructions stay in uniform registers); one elected lane issues.
+    {
       int it = 0;
       uint32_t g = 0;
       for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
@@ -317,6 +319,12 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           const int b = g & 1;
           if (!mbar_wait(&acc_empty[b], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
           tc_fence_after();
+          if (EPI == LG_EPI_TRI_OUT) {
+            if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 15) ||
+                !mbar_wait(&stat_full[s], (it >> 1) & 1, abort_flag, p.status, 16)) { ok = false; break; }
+            tc_fence_after();
+          }
+          if (elect_one()) {
           if (EPI == LG_EPI_TRIANGLE) {
             // D[channel][pair row]: weights are the A operand (128 projection rows, then 128 gate
             // rows of operand j), the normalised tile is the B operand (N = 128 pair rows)
@@ -334,9 +342,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           } else if (EPI == LG_EPI_TRI_OUT) {
             // columns 0..127: x tile (MN-major A, raw) times the gain-folded output projection;
             // columns 128..255: normalised pair tile (K-major A) times the output gate weights
-            if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 15) ||
-                !mbar_wait(&stat_full[s], (it >> 1) & 1, abort_flag, p.status, 16)) { ok = false; break; }
-            tc_fence_after();
             const uint32_t x_addr = smem_u32(sX + s * LG_A_BYTES);
             const uint32_t w_addr = smem_u32(sW);
             const uint32_t idesc_x = make_idesc_f16(LG_ROWS, 128, 1, 0);
@@ -364,9 +369,11 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             }
           }
           umma_commit(&acc_full[b]);
+          if (j == p.n_chunks - 1) umma_commit(&a_empty[s]);
+          }
+          __syncwarp();
         }
         if (!ok) break;
-        umma_commit(&a_empty[s]);
       }
     }
   } else {

@@ -210,13 +210,15 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
     }
   } else if (warp == 24) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop (uniform control flow and operand values, so the operands of the
+    // MMA instructions stay in uniform registers); one elected lane issues.
+    {
       constexpr uint32_t idesc = make_idesc_f16(TR_ROWS, 128, 0, 0);
       const uint32_t a_addr = smem_u32(sA), h_addr = smem_u32(sH);
       uint32_t g = 0;      // chunk counter across tiles
       int it = 0;
       bool ok = true;
-      auto gemm2 = [&](uint32_t gc, int c) {   // out += hidden chunk x W2 slice of chunk counter gc
+      auto gemm2 = [&](uint32_t gc, int c) {   // out += hidden chunk x W2 slice of chunk counter gc (elected lane)
         const uint32_t w2 = smem_u32(sW + (gc & 1) * TR_W_STAGE + TR_TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HK / 16; ++kk) {
@@ -235,30 +237,39 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
               !mbar_wait(&hacc_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 55)) { ok = false; break; }
           tc_fence_after();
           const uint32_t w1 = smem_u32(sW + s * TR_W_STAGE);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (TR_ROWS * 128) + (kk & 3) * 32, 16, 1024);
-            const uint64_t bdesc = make_smem_desc(w1 + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-            umma_f16(tmem_base + s * 128, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t adesc = make_smem_desc(a_addr + (kk >> 2) * (TR_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+              const uint64_t bdesc = make_smem_desc(w1 + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+              umma_f16(tmem_base + s * 128, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
+            }
+            umma_commit(&hacc_full[s]);
+            if (c == TR_CHUNKS - 1) umma_commit(a_empty);
           }
-          umma_commit(&hacc_full[s]);
-          if (c == TR_CHUNKS - 1) umma_commit(a_empty);
+          __syncwarp();
           if (c >= 1) {
             // second GEMM of the previous chunk, once its hidden tile is in shared memory
             if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 56)) { ok = false; break; }
             tc_fence_after();
-            gemm2(g - 1, c - 1);
-            umma_commit(h_empty);
-            umma_commit(&w_empty[(g - 1) & 1]);
+            if (elect_one()) {
+              gemm2(g - 1, c - 1);
+              umma_commit(h_empty);
+              umma_commit(&w_empty[(g - 1) & 1]);
+            }
+            __syncwarp();
           }
         }
         if (!ok) break;
         if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 57)) break;
         tc_fence_after();
-        gemm2(g - 1, TR_CHUNKS - 1);
-        umma_commit(h_empty);
-        umma_commit(&w_empty[(g - 1) & 1]);
-        umma_commit(out_full);
+        if (elect_one()) {
+          gemm2(g - 1, TR_CHUNKS - 1);
+          umma_commit(h_empty);
+          umma_commit(&w_empty[(g - 1) & 1]);
+          umma_commit(out_full);
+        }
+        __syncwarp();
       }
     }
   } else {
