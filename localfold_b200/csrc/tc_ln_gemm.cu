@@ -229,6 +229,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             for (int e = 0; e < 16; ++e) v[u][e] = 0.f;
           }
         }
+#ifdef LF_LG_TRACE
+        // the first value of the group has arrived
+        if (pw == 0 && lane == 0 && v[0][0] != 12345.678f) LG_TRACE(it, 12 + grp * 2);
+#endif
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
@@ -283,6 +287,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
                   make_uint2(packed[w4 * 2], packed[w4 * 2 + 1]);
           }
         }
+        if (pw == 0 && lane == 0) LG_TRACE(it, 13 + grp * 2);
       }
       fence_async_smem();
       __syncwarp();
@@ -587,7 +592,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[b]);
         if (warp == 0 && lane == 0) LG_TRACE(it, 9 + j);
-        if (warp == 15 && lane == 0) LG_TRACE(it, 12 + j);
       }
     }
   }
