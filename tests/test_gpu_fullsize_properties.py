@@ -127,3 +127,19 @@ def test_transition_rows_against_oracle_fullsize(dev, pair):
     want = oracle.transition_af2(sample, w, 512)
     assert np.isfinite(got).all()
     assert oracle.relative_l2(got, want) <= 8e-3
+
+
+def test_pair_block_relabelling_fullsize(dev, pair):
+    """The whole AF2 pair block (13 launches) commutes with a relabelling of the residues."""
+    import localfold_b200 as lf
+    z, mask, perm = pair
+    _, _, weights = syn.af2_pair_block(4, 16, blocks=1)      # the weights do not depend on the length
+    stack = lf.PairStackGpu(dev).prepare(weights, 128, 128)
+    base = z.clone()
+    stack.run(base, mask, OPTS, first_block=0, n_blocks=1)
+    moved = relabel(z, perm)
+    stack.run(moved, relabel(mask, perm), OPTS, first_block=0, n_blocks=1)
+    dev.synchronize()
+    stack.close()
+    assert bool(torch.isfinite(base).all())
+    assert rel_l2(moved, relabel(base, perm)) <= 2e-3
