@@ -333,7 +333,8 @@ LF_API lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d,
  *   TRIANGLE_CONTRACT  buf0 = a, buf1 = b of rank `chunk`, buf2 = x [128][rows][ld]: fills
  *                      x[:, :, chunk*rows : (chunk+1)*rows]    (outgoing form; rows % 16 == 0)
  *   TRIANGLE_OUTPUT    buf2 = x; pair += output(x, pair)
- *   ATTENTION_PROJECT  buf0..3 = q, k, v, gate [rows*length][128]; buf4 = this shard's pair bias
+ *   ATTENTION_PROJECT  buf0..3 = q, k, v, gate: rows*length*128 fp16 each, in the library's own piece order
+ *                      (scratch between the attention steps, not meant to be read); buf4 = this shard's pair bias
  *                      [4][rows][ld] (head, query row of the shard, key)
  *   ATTENTION_CORE     buf0..3; buf4 = the bias of all query rows [4][length][ld], the shards'
  *                      rows in rank order under each head; buf5 = o

@@ -627,17 +627,22 @@ void att_f32(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
 // 16-bit path: tensor-core LayerNorm + q/k/v/gate/bias projection, then the attention core.
 template <typename T>
 lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
-  const int64_t R = (int64_t)a.batch * a.Q;
   const int HD = a.heads * a.d, c = a.ch;
   const auto& f = a.w->f;
-  op16* q = cur.take<op16>(R * HD);
-  op16* k = cur.take<op16>(R * HD);
-  op16* v = cur.take<op16>(R * HD);
-  op16* g = cur.take<op16>(R * HD);
-  const int ldb = (a.Q + 15) / 16 * 16;   // keys padded to whole groups of 16 (the tiled bias layout)
+  const int ldb = (a.Q + 15) / 16 * 16;        // rows and keys padded to whole groups of 16
+  const int64_t RP = (int64_t)a.batch * ldb;   // q, k, v, gate and o are stored in 8 x 8 pieces: rows padded per batch row
+  op16* q = cur.take<op16>(RP * HD);
+  op16* k = cur.take<op16>(RP * HD);
+  op16* v = cur.take<op16>(RP * HD);
+  op16* g = cur.take<op16>(RP * HD);
   op16* bias = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
-  op16* o16 = cur.take<op16>(R * HD);
-  if (bias && ldb != a.Q && !cur.dry) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
+  op16* o16 = cur.take<op16>(RP * HD);
+  if (ldb != a.Q && !cur.dry) {
+    // the padding rows and columns are read (as keys past the end, masked out): they must hold finite values
+    if (bias) cudaMemsetAsync(bias, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
+    cudaMemsetAsync(k, 0, (size_t)RP * HD * sizeof(op16), ctx->stream);
+    cudaMemsetAsync(v, 0, (size_t)RP * HD * sizeof(op16), ctx->stream);
+  }
   LF_TRY(tc::attention_project(ctx, cur, a.act, a.act_dtype, a.batch, a.Q, a.transpose, a.variance, a.eps, a.heads, a.d,
                                a.bias_swap, a.w, q, k, v, g, bias, ldb));
   LF_TRY(tc::attention_core(ctx, cur, q, k, v, g, bias, ldb, a.mask, a.batch, a.Q, a.transpose, a.mask_mode, a.clamp, o16));

@@ -50,8 +50,9 @@ struct FlashParams {
   int transpose, mask_mode, clamp;
   const float* mask;       // b*Q + j, or j*batch + b when transpose
   int has_bias, ldb;       // the bias [4][Q][ldb] fp16 arrives through its tensor map
-  const op16* gate;        // [batch*Q][128] sigmoid(gate)
-  op16* out;               // [batch*Q][128]
+  int ldq;                 // rows per batch row of q, k, v, gate, out (Q rounded up to 16)
+  const op16* gate;        // sigmoid(gate), in 8 x 8 pieces like q: element (b, q, c) at b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8
+  op16* out;               // same layout
   Status* status;
 };
 
@@ -135,8 +136,9 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         if (!mbar_wait_parked(q_empty, (n_item & 1) ^ 1, abort_flag, p.status, 20)) ok = false;
         else {
           mbar_expect_tx(q_full, 2 * FA_Q_BYTES);
-          tma_load_3d(sQ, &mapQ, q_full, hp * 64, (2 * qp) * FA_TILE, b);
-          tma_load_3d(sQ + FA_Q_BYTES, &mapQ, q_full, hp * 64, (2 * qp + 1) * FA_TILE, b);
+          // coordinates: channel and row inside a piece, piece along channels (8 per head pair), piece along rows, batch row
+          tma_load_5d(sQ, &mapQ, q_full, 0, 0, hp * 8, (2 * qp) * (FA_TILE / 8), b);
+          tma_load_5d(sQ + FA_Q_BYTES, &mapQ, q_full, 0, 0, hp * 8, (2 * qp + 1) * (FA_TILE / 8), b);
         }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -146,8 +148,8 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           if (!mbar_wait(&kv_empty[st], ((n_kv / FA_STAGES) & 1) ^ 1, abort_flag, p.status, 21)) ok = false;   // not parked: the ring is only a few tiles deep
           else {
             mbar_expect_tx(&kv_full[st], 2 * FA_KV_BYTES);
-            tma_load_3d(sK + st * FA_KV_BYTES, &mapK, &kv_full[st], hp * 64, t * FA_KT, b);
-            tma_load_3d(sV + st * FA_KV_BYTES, &mapV, &kv_full[st], hp * 64, t * FA_KT, b);
+            tma_load_5d(sK + st * FA_KV_BYTES, &mapK, &kv_full[st], 0, 0, hp * 8, t * (FA_KT / 8), b);
+            tma_load_5d(sV + st * FA_KV_BYTES, &mapV, &kv_full[st], 0, 0, hp * 8, t * (FA_KT / 8), b);
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -243,8 +245,9 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           const uint32_t d = d0 + h * FA_TILE + (u & 1) * FA_KT;
 #pragma unroll
           for (int kk = 0; kk < 2; ++kk) {
-            const uint64_t adesc = make_smem_desc(q_addr + h * 64 + kk * 32, 16, 1024);
-            const uint64_t bdesc = make_smem_desc(k_addr + h * 64 + kk * 32, 16, 1024);
+            // unswizzled K-major tiles [rows / 8][8 pieces][8 rows][16 B]: a head is 4 pieces (512 B), a k-step 2 pieces
+            const uint64_t adesc = make_smem_desc_plain(q_addr + h * 512 + kk * 256, 128, 1024);
+            const uint64_t bdesc = make_smem_desc_plain(k_addr + h * 512 + kk * 256, 128, 1024);
             umma_f16(d, adesc, bdesc, idesc_qk, kk);
           }
           if (has_bias) {
@@ -301,7 +304,8 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
             const uint32_t pbuf = d + (u & 1) * FA_KT;
 #pragma unroll
             for (int kk = 0; kk < FA_KT / 16; ++kk) {
-              const uint64_t bdesc = make_smem_desc(v_addr + h * 64 + kk * 2048, 8192, 1024);
+              // V as the MN-major operand: a piece is 8 keys x 8 channels; 16 keys per step = two row groups (2048 B)
+              const uint64_t bdesc = make_smem_desc_plain(v_addr + h * 512 + kk * 2048, 1024, 128);
               umma_f16_ts(d + FA_O_COL, pbuf + kk * 8, bdesc, idesc_pv, (pv_t != 0 || kk != 0) ? 1u : 0u);
             }
           }
@@ -464,21 +468,23 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tmem_ld32(acc + FA_O_COL, o);
         tmem_ld_wait();
         if (qvalid) {
-          const int64_t r = (int64_t)b * p.Q + qi;
+          // the head's 32 channels are four 8-channel pieces of this row, 64 elements apart
+          const int64_t r = (int64_t)b * p.ldq * 128 + (int64_t)(qi >> 3) * 1024 + head * 256 + (qi & 7) * 8;
           const float inv = 1.0f / l_run;
-          const uint4* g4 = reinterpret_cast<const uint4*>(p.gate + r * 128 + head * 32);
-          op16* dst = p.out + r * 128 + head * 32;
+          const op16* gsrc = p.gate + r;
+          op16* dst = p.out + r;
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             uint32_t pk[8];
-            const uint4 ga = g4[c * 2], gb = g4[c * 2 + 1];
+            const uint4 ga = *reinterpret_cast<const uint4*>(gsrc + c * 128), gb = *reinterpret_cast<const uint4*>(gsrc + c * 128 + 64);
             const uint32_t gw[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&gw[e]));
               pk[e] = pack_half2(__uint_as_float(o[c * 16 + e * 2]) * inv * gf.x, __uint_as_float(o[c * 16 + e * 2 + 1]) * inv * gf.y);
             }
-            st_global_v8(dst + c * 16, pk);
+            *reinterpret_cast<uint4*>(dst + c * 128) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(dst + c * 128 + 64) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           }
         }
       }
@@ -499,22 +505,23 @@ void configure_attention() {
 
 lf_status make_map_f16_3d_ext(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                               uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1);
+lf_status make_map_tiled_act(lf_context* ctx, CUtensorMap* map, const void* base, int ldq, int batch, int rows);
 
 lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const op16* k, const op16* v, const op16* g,
                          const op16* bias, int ldb, const float* mask, int batch, int Q, int transpose,
                          int mask_mode, int clamp, op16* out) {
   if (cur.dry) return LF_OK;
   CUtensorMap mq, mk, mv, mb;
-  const uint64_t row = 256, plane = (uint64_t)Q * 256;
-  LF_TRY(make_map_f16_3d_ext(ctx, &mq, q, 128, Q, batch, row, plane, 64, FA_TILE));
-  LF_TRY(make_map_f16_3d_ext(ctx, &mk, k, 128, Q, batch, row, plane, 64, FA_KT));
-  LF_TRY(make_map_f16_3d_ext(ctx, &mv, v, 128, Q, batch, row, plane, 64, FA_KT));
+  const int ldq = (Q + 15) / 16 * 16;
+  LF_TRY(make_map_tiled_act(ctx, &mq, q, ldq, batch, FA_TILE));
+  LF_TRY(make_map_tiled_act(ctx, &mk, k, ldq, batch, FA_KT));
+  LF_TRY(make_map_tiled_act(ctx, &mv, v, ldq, batch, FA_KT));
   // bias [4][Q][ldb]: boxes of 64 keys x 128 queries; without a bias the map is a stand-in that is never used
   if (bias) LF_TRY(make_map_f16_3d_ext(ctx, &mb, bias, ldb, Q, 4, (uint64_t)ldb * 2, (uint64_t)Q * ldb * 2, 64, FA_TILE));
   else mb = mq;
   FlashParams p{};
   p.batch = batch; p.Q = Q; p.qtiles = (Q + FA_TILE - 1) / FA_TILE; p.qpairs = (p.qtiles + 1) / 2; p.ktiles = (Q + FA_KT - 1) / FA_KT;
-  p.transpose = transpose; p.mask_mode = mask_mode; p.clamp = clamp; p.mask = mask; p.has_bias = bias ? 1 : 0; p.ldb = ldb;
+  p.transpose = transpose; p.mask_mode = mask_mode; p.clamp = clamp; p.mask = mask; p.has_bias = bias ? 1 : 0; p.ldb = ldb; p.ldq = ldq;
   p.gate = g; p.out = out; p.status = (Status*)ctx->tc_status;
   const int64_t items = (int64_t)batch * p.qpairs * 2;
   const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);

@@ -49,6 +49,25 @@ lf_status make_map_f16_3d_ext(lf_context* ctx, CUtensorMap* map, const void* bas
   return make_map_f16_3d(ctx, map, base, d0, d1, d2, stride1_bytes, stride2_bytes, b0, b1);
 }
 
+// Attention activations q, k, v, gate, o: fp16 [batch][ldq][128] stored as 8-row x 8-channel pieces of 128
+// contiguous bytes (element (b, q, c) at b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8).  A warp whose
+// threads own consecutive rows then writes whole 128-byte lines with 16-byte stores, and a piece is exactly
+// one core matrix of the tensor core's unswizzled operand format.  The map's dimensions are (channel in
+// piece, row in piece, piece along channels, piece along rows, batch row) - strides increasing - and a
+// box of `rows` rows x 64 channels lands in shared memory as [rows/8][8 pieces][8 rows][16 B].
+lf_status make_map_tiled_act(lf_context* ctx, CUtensorMap* map, const void* base, int ldq, int batch, int rows) {
+  if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[5] = {8, 8, 16, (cuuint64_t)(ldq / 8), (cuuint64_t)batch};
+  cuuint64_t strides[4] = {16, 128, 2048, (cuuint64_t)ldq * 256};
+  cuuint32_t box[5] = {8, 8, 8, (cuuint32_t)(rows / 8), 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled (5-d) failed with code %d", (int)r);
+  return LF_OK;
+}
+
 lf_status check_status(lf_context* ctx) {
   if (!ctx->tc_status) return LF_OK;
   Status st;

@@ -54,6 +54,8 @@ struct LnGemmParams {
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
   op16* out_bias;           // fp16 [heads][batch rows][ldb] (head, query, key)
   int ldb;
+  int ldq;                  // attention activations (q, k, v, gate, o) are stored in 8-row x 8-channel pieces: element (b, q, c)
+                            // of a [batch][Q][128] tensor sits at b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ldq = Q rounded up to 16
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
   // output epilogues (attention output projection, triangle output): out = resid + f(acc)
@@ -191,10 +193,13 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             int64_t src = r;
             if (p.transpose && !p.a_is_op16) { const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q; src = (int64_t)(ur % uq) * p.batch + ur / uq; }
             if (p.a_is_op16) {
-              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const op16*>(p.act) + src * LG_K + 8 * j);
+              // rows in 8 x 8 pieces: channels 8 j .. + 7 are piece j of the row, channels 64 + 8 j .. piece 8 + j
+              const uint32_t ur = (uint32_t)r, uq = (uint32_t)p.Q, rb = ur / uq, rq = ur % uq;
+              const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const op16*>(p.act) + (int64_t)rb * p.ldq * 128 +
+                                                              (int64_t)(rq >> 3) * 1024 + j * 64 + (rq & 7) * 8);
 #pragma unroll
               for (int w4 = 0; w4 < 2; ++w4) {
-                const uint4 raw = g[w4 * 8];
+                const uint4 raw = g[w4 * 64];
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -544,6 +549,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             const float4* bias4 = reinterpret_cast<const float4*>(sBias + j * 256 + second * 128 + col0);
             const bool gate = (j == 1 && second == 1);
             const bool has_bias = (p.bias_flags >> (j * 2 + second)) & 1;
+            // destination of this row in the 8 x 8-piece layout: pieces along channels are 64 elements apart
+            const uint32_t ur = (uint32_t)(valid ? r : 0), uq = (uint32_t)p.Q, rb = ur / uq, rq = ur % uq;
+            op16* out_row = out + (int64_t)rb * p.ldq * 128 + (int64_t)(rq >> 3) * 1024 + (rq & 7) * 8;
 #pragma unroll 1
             for (int c0 = 0; c0 < 64; c0 += 16) {
               uint32_t v[16];
@@ -567,7 +575,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
                 uint32_t pk[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) pk[u] = pack_half2(f[2 * u], f[2 * u + 1]);
-                st_global_v8(out + r * 128 + col0 + c0, pk);
+                // two 16-byte pieces: 32 consecutive rows of a warp fill four whole 128-byte lines per store
+                op16* dst = out_row + ((col0 + c0) >> 3) * 64;
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(dst + 64) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
               }
             }
           } else if (part == 0) {
@@ -663,6 +674,7 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
   p.chunk_row0[0] = 0; p.chunk_row0[1] = 256; p.chunk_row0[2] = 512;
   p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.ldb = ldb; p.heads = heads; p.bias_swap = bias_swap;
+  p.ldq = (Q + 15) / 16 * 16;
   p.bias_flags = w->bias_flags;
   (void)head_dim;
   p.status = (Status*)ctx->tc_status;
@@ -684,6 +696,7 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
   p.act = o; p.a_is_op16 = 1; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
+  p.ldq = (Q + 15) / 16 * 16;
   p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = 1e-5f; p.variance = 1;
   p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 128; p.bias = w->f[ATT_BO]; p.n_bias = 128;
   p.n_chunks = 1; p.chunk_n[0] = 128; p.chunk_row0[0] = 0;
