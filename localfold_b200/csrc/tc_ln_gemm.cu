@@ -63,6 +63,8 @@ struct LnGemmParams {
   const void* resid;        // pair rows (memory order) to add, or null
   void* out;                // pair rows written in the same memory order
   int out_bf16;
+  int tma_out;              // attention output only: the residual tile comes in and the result goes out through the tensor map
+                            // (one map for both: the residual is the output tensor or absent), per warp 32 rows x 32 channels
   // triangle output: tiles follow pair rows (i, 128 k's); x is fetched by TMA as an MN-major operand
   int tile_per_row;         // tiles per pair row i (0 = rows are tiled linearly)
   float x_eps;              // epsilon of the centre LayerNorm in the units x is stored in
@@ -113,7 +115,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
   uint8_t* sW = smem;
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
   uint8_t* sX = sA + 2 * LG_A_BYTES;                  // triangle output only: 2 stages of the raw x tile
-  float* sBias = reinterpret_cast<float*>(sX + (EPI == LG_EPI_TRI_OUT ? 2 * LG_A_BYTES : 0));
+  uint8_t* sStage = sX;                               // attention output only: per epilogue warp 32 rows x 128 B of the pair
+  float* sBias = reinterpret_cast<float*>(sX + (EPI == LG_EPI_TRI_OUT ? 2 * LG_A_BYTES : (EPI == LG_EPI_OUTPUT ? LG_EPI_WARPS * 4096 : 0)));
   float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
   float* sGamma = sBias + 544;      // [128]
   float* sBeta = sGamma + 128;      // [128]
@@ -124,7 +127,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
   uint64_t* acc_empty = bars + 6;   // [2]
   uint64_t* x_full = bars + 8;      // [2] TMA bytes of the x tile
   uint64_t* stat_full = bars + 10;  // [2] row statistics of the x tile written
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* stage_bar = bars + 12;  // [epilogue warp] TMA bytes of the warp's residual tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + LG_EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,6 +143,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], LG_EPI_WARPS);
     }
+    for (int i = 0; i < LG_EPI_WARPS; ++i) mbar_init(&stage_bar[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -413,6 +418,23 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
       tile_rows(p, t, row_base, row_count);
       const int64_t r = row_base + row;
       const bool valid = row < row_count;
+      // attention output through the tensor map: this warp's 32 rows x 32 channels of the pair
+      const bool tma_tile = EPI == LG_EPI_OUTPUT && p.tma_out && q * 32 < row_count;
+      int tx = 0, ty = 0, tz = 0;
+      if (tma_tile) {
+        const int64_t r0 = row_base + q * 32;
+        tx = part * 32;
+        if (p.transpose) { const uint32_t u0 = (uint32_t)r0, uq = (uint32_t)p.Q; ty = (int)(u0 / uq); tz = (int)(u0 % uq); }
+        else ty = (int)r0;
+        if (lane == 0) {
+          bulk_wait_read();      // the previous tile's store has finished reading the staging rows
+          if (p.resid) {
+            mbar_expect_tx(&stage_bar[warp], 4096);
+            tma_load_3d(sStage + warp * 4096, &mapX, &stage_bar[warp], tx, ty, tz);
+          }
+        }
+        __syncwarp();
+      }
       for (int j = 0; j < p.n_chunks; ++j, ++g) {
         const int b = g & 1;
         if (!mbar_wait(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
@@ -467,6 +489,32 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             }
             kk0 += 16;
             if (kk0 >= un) { kk0 -= un; ++ii; }
+          }
+        } else if (EPI == LG_EPI_OUTPUT && p.tma_out) {
+          // thread = pair row; the warp's 32 rows x 32 channels are finished in its staging rows (128 B each,
+          // 16-byte pieces swizzled by row so that the row-per-thread accesses spread over the banks) and leave
+          // as one TMA store: no global load or store instruction touches the pair here
+          if (tma_tile) {
+            uint8_t* stage = sStage + warp * 4096 + lane * 128;
+            if (p.resid && !mbar_wait(&stage_bar[warp], it & 1, abort_flag, p.status, 18)) { ok = false; break; }
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v1[16];
+              tmem_ld16(acc + part * 32 + half * 16, v1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) {
+                float4* cell = reinterpret_cast<float4*>(stage + ((uint32_t)((half * 4 + k4) ^ (lane & 7)) << 4));
+                const float* bias = sBias + part * 32 + half * 16 + k4 * 4;
+                float4 o = make_float4(__uint_as_float(v1[k4 * 4]) + bias[0], __uint_as_float(v1[k4 * 4 + 1]) + bias[1],
+                                       __uint_as_float(v1[k4 * 4 + 2]) + bias[2], __uint_as_float(v1[k4 * 4 + 3]) + bias[3]);
+                if (p.resid) { const float4 rr = *cell; o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
+                *cell = o;
+              }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) { tma_store_3d(&mapX, sStage + warp * 4096, tx, ty, tz); bulk_commit(); }
           }
         } else if (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) {
           // thread = pair row; this warp's quarter = 32 output channels, two runs of 16
@@ -607,6 +655,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
     }
   }
 
+  if (EPI == LG_EPI_OUTPUT && p.tma_out && warp < LG_EPI_WARPS && lane == 0) bulk_wait_all();   // this thread's stores have landed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) drain_after_abort();
@@ -631,14 +680,17 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
   pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0, scale);
 }
 
-static int ln_gemm_smem(int n_pad, bool tri_out = false) {
-  return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (544 + 256 + 512) * 4 + 256 + 1024;
+lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                            uint64_t stride2_bytes, uint32_t b1, uint32_t b2);
+
+static int ln_gemm_smem(int n_pad, bool tri_out = false, bool staged_out = false) {
+  return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (staged_out ? LG_EPI_WARPS * 4096 : 0) + (544 + 256 + 512) * 4 + 512 + 1024;
 }
 
 void configure_ln_gemm() {
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_ATTENTION>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(528));
-  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128, false, true));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, true));
   cudaGetLastError();
 }
@@ -702,11 +754,20 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   p.n_chunks = 1; p.chunk_n[0] = 128; p.chunk_row0[0] = 0;
   p.resid = resid; p.out = out; p.out_bf16 = act_dtype == LF_DTYPE_BF16;
   p.status = (Status*)ctx->tc_status;
+  // float32 pair, updated in place (or no residual): the residual tile and the result travel by TMA.  Logical
+  // rows (b, q) sit at pair row b*Q + q, or q*batch + b for the transposed orientation, where a warp's 32
+  // consecutive q must share b.
+  CUtensorMap mo{};
+  p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out) && (!transpose || Q % 32 == 0)) ? 1 : 0;
+  if (p.tma_out) {
+    if (transpose) LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)batch, (uint64_t)Q, 512, (uint64_t)batch * 512, 1, 32));
+    else LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)p.rows, 1, 512, (uint64_t)p.rows * 512, 32, 1));
+  }
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  // the fp16 rows are in logical order; the transposed scatter happens in the epilogue
-  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128), ctx->stream>>>(CUtensorMap{}, p);
+  // the fp16 rows are in logical order; the transposed scatter happens in the epilogue (or in the tensor map)
+  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128, false, true), ctx->stream>>>(mo, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
