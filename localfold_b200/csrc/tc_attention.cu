@@ -2,7 +2,10 @@
 //
 // Work item = (batch row b, pair of 128-query tiles, pair of heads): four independent streams
 // (query tile g, head h) that share the K and V tiles of the head pair, which stream through a
-// five-stage TMA ring of 48-key tiles (both heads of the pair share a 128-byte swizzled row).
+// five-stage TMA ring of 48-key tiles.  Q, K, V (and the gate and the output) live in memory as
+// 8-row x 8-channel pieces of 128 bytes; 5-d tensor maps bring a tile's pieces in as
+// [rows / 8][8 pieces of the head pair][8 rows][16 B], which is the tensor core's unswizzled
+// operand format (K-major for Q and K, MN-major for V).
 //
 // Per stream, tensor memory holds two S / P buffers (48 columns each) and the output accumulator O
 // (32 columns): 128 columns per stream, 512 in all.

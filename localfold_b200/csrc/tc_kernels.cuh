@@ -34,7 +34,8 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 // `rows` pair rows of length n (rows = n for the whole pair, fewer for a row shard)
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
                            int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
-// q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 [batch*Q][128] in logical row order and the
+// q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 logical rows [batch][ld][128] stored in 8-row x
+// 8-channel pieces (element (b, q, c) at b*ld*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ld = Q rounded up to 16) and the
 // pair bias fp16 tiled [heads][ldb/16][Q][16] (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,

@@ -51,7 +51,7 @@ struct LnGemmParams {
   int n, ld;                // pair row length and operand row stride
   int plane_rows;           // pair rows held (n for a whole pair, fewer for a row shard)
   // attention projection epilogue
-  op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // [rows][128] logical order
+  op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // logical rows, stored in 8 x 8 pieces (see ldq)
   op16* out_bias;           // fp16 [heads][batch rows][ldb] (head, query, key)
   int ldb;
   int ldq;                  // attention activations (q, k, v, gate, o) are stored in 8-row x 8-channel pieces: element (b, q, c)
@@ -59,7 +59,7 @@ struct LnGemmParams {
   int heads, bias_swap;
   int bias_flags;           // bit (2*chunk + half): that 128-column group has a non-zero bias
   // output epilogues (attention output projection, triangle output): out = resid + f(acc)
-  int a_is_op16;            // the A operand is an fp16 [rows][128] tensor copied as is (no LayerNorm)
+  int a_is_op16;            // the A operand is an fp16 tensor of logical rows in 8 x 8 pieces (see ldq), copied as is (no LayerNorm)
   const void* resid;        // pair rows (memory order) to add, or null
   void* out;                // pair rows written in the same memory order
   int out_bf16;
