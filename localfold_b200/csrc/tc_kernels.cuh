@@ -36,7 +36,7 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
                            int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 logical rows [batch][ld][128] stored in 8-row x
 // 8-channel pieces (element (b, q, c) at b*ld*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ld = Q rounded up to 16) and the
-// pair bias fp16 tiled [heads][ldb/16][Q][16] (null = none) from the normalised input
+// pair bias fp16 [heads][batch rows][ldb] (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
