@@ -108,15 +108,18 @@ __device__ long long lf_lg_trace[24 * 16];
 
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1)
-ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
+ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const LnGemmParams p) {
+  // operand stages: the triangle output keeps one (its shared memory goes to the staging rows of the pair tile instead);
+  // the producers of tile t+1 then start when the MMAs of tile t have completed, i.e. beside the epilogue of tile t
+  constexpr int NS = EPI == LG_EPI_TRI_OUT ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int w_bytes = p.n_pad * 256;
   uint8_t* sW = smem;
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
-  uint8_t* sX = sA + 2 * LG_A_BYTES;                  // triangle output only: 2 stages of the raw x tile
-  uint8_t* sStage = sX;                               // attention output only: per epilogue warp 32 rows x 128 B of the pair
-  float* sBias = reinterpret_cast<float*>(sX + (EPI == LG_EPI_TRI_OUT ? 2 * LG_A_BYTES : (EPI == LG_EPI_OUTPUT ? LG_EPI_WARPS * 4096 : 0)));
+  uint8_t* sX = sA + NS * LG_A_BYTES;                 // triangle output only: the raw x tile
+  uint8_t* sStage = sX + (EPI == LG_EPI_TRI_OUT ? LG_A_BYTES : 0);   // output kernels: per epilogue warp 32 rows x 128 B of the pair
+  float* sBias = reinterpret_cast<float*>(sStage + ((EPI == LG_EPI_TRI_OUT || EPI == LG_EPI_OUTPUT) ? LG_EPI_WARPS * 4096 : 0));
   float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
   float* sGamma = sBias + 544;      // [128]
   float* sBeta = sGamma + 128;      // [128]
@@ -173,8 +176,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
     const int sub = lane >> 3, j = lane & 7;
     int it = 0;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
-      const int s = it & 1;
-      if (!mbar_wait(&a_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 10)) break;
+      const int s = it % NS;
+      const uint32_t ph = (uint32_t)(it / NS) & 1u;
+      if (!mbar_wait(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
       if (pw == 0 && lane == 0) LG_TRACE(it, 0);
       uint8_t* tile = sA + s * LG_A_BYTES;
       int64_t row_base;
@@ -306,7 +310,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
       if (EPI == LG_EPI_TRI_OUT && pw < 4) {
         // statistics of the centre LayerNorm: one thread per pair reads its 128 channels from the
         // raw x tile (row h of the tile = 128 bytes of 64 pairs, 128-byte swizzled)
-        if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 14)) break;
+        if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, 14)) break;
         const int pr = pw * 32 + lane;
         const uint8_t* xt = sX + s * LG_A_BYTES + (pr >> 6) * (LG_A_BYTES / 2);
         const uint32_t chunk = (uint32_t)((pr & 63) >> 3), within = (uint32_t)(pr & 7) * 2u;
@@ -322,8 +326,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
         if (p.variance != 2) var = fmaxf(var, 0.f);
         float inv = rsqrtf(var + p.x_eps);
         inv = inv * (1.5f - 0.5f * (var + p.x_eps) * inv * inv);
-        sStat[s * 256 + pr] = inv;
-        sStat[s * 256 + 128 + pr] = inv * mean;
+        sStat[(it & 1) * 256 + pr] = inv;            // two sets: the epilogue of the previous tile may still read its own
+        sStat[(it & 1) * 256 + 128 + pr] = inv * mean;
         __syncwarp();
         if (lane == 0) mbar_arrive(&stat_full[s]);
       }
@@ -336,8 +340,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
       int it = 0;
       uint32_t g = 0;
       for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(&a_full[s], (it >> 1) & 1, abort_flag, p.status, 11)) break;
+        const int s = it % NS;
+        const uint32_t ph = (uint32_t)(it / NS) & 1u;
+        if (!mbar_wait(&a_full[s], ph, abort_flag, p.status, 11)) break;
         tc_fence_after();
         if (lane == 0) LG_TRACE(it, 2);
         const uint32_t a_addr = smem_u32(sA + s * LG_A_BYTES);
@@ -347,8 +352,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           if (!mbar_wait(&acc_empty[b], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
           tc_fence_after();
           if (EPI == LG_EPI_TRI_OUT) {
-            if (!mbar_wait(&x_full[s], (it >> 1) & 1, abort_flag, p.status, 15) ||
-                !mbar_wait(&stat_full[s], (it >> 1) & 1, abort_flag, p.status, 16)) { ok = false; break; }
+            if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, 15) ||
+                !mbar_wait(&stat_full[s], ph, abort_flag, p.status, 16)) { ok = false; break; }
             tc_fence_after();
           }
           if (elect_one()) {
@@ -409,7 +414,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
     const int q = warp & 3, part = warp >> 2;   // part: which quarter of the chunk's columns
     const int row = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    uint32_t g = 0;
+    uint32_t g = 0, staged = 0;
     bool ok = true;
     int it = 0;
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
@@ -419,18 +424,25 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
       const int64_t r = row_base + row;
       const bool valid = row < row_count;
       // attention output through the tensor map: this warp's 32 rows x 32 channels of the pair
-      const bool tma_tile = EPI == LG_EPI_OUTPUT && p.tma_out && q * 32 < row_count;
+      const bool tma_tile = (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out && q * 32 < row_count;
       int tx = 0, ty = 0, tz = 0;
+      uint32_t stage_phase = 0;
       if (tma_tile) {
+        stage_phase = staged & 1u;       // a warp skips tiles of which it owns no row, so it counts its own residual loads
+        if (p.resid) ++staged;
         const int64_t r0 = row_base + q * 32;
         tx = part * 32;
-        if (p.transpose) { const uint32_t u0 = (uint32_t)r0, uq = (uint32_t)p.Q; ty = (int)(u0 / uq); tz = (int)(u0 % uq); }
+        if (EPI == LG_EPI_TRI_OUT) {
+          // tiles lie inside one pair row i: the map is (channel, k, i), so a ragged last tile of a row is clipped at k = n
+          tz = (int)(t / p.tile_per_row);
+          ty = (int)(t % p.tile_per_row) * LG_ROWS + q * 32;
+        } else if (p.transpose) { const uint32_t u0 = (uint32_t)r0, uq = (uint32_t)p.Q; ty = (int)(u0 / uq); tz = (int)(u0 % uq); }
         else ty = (int)r0;
         if (lane == 0) {
           bulk_wait_read();      // the previous tile's store has finished reading the staging rows
           if (p.resid) {
             mbar_expect_tx(&stage_bar[warp], 4096);
-            tma_load_3d(sStage + warp * 4096, &mapX, &stage_bar[warp], tx, ty, tz);
+            tma_load_3d(sStage + warp * 4096, &mapO, &stage_bar[warp], tx, ty, tz);
           }
         }
         __syncwarp();
@@ -490,31 +502,49 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
             kk0 += 16;
             if (kk0 >= un) { kk0 -= un; ++ii; }
           }
-        } else if (EPI == LG_EPI_OUTPUT && p.tma_out) {
+        } else if ((EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out) {
           // thread = pair row; the warp's 32 rows x 32 channels are finished in its staging rows (128 B each,
           // 16-byte pieces swizzled by row so that the row-per-thread accesses spread over the banks) and leave
           // as one TMA store: no global load or store instruction touches the pair here
           if (tma_tile) {
             uint8_t* stage = sStage + warp * 4096 + lane * 128;
-            if (p.resid && !mbar_wait(&stage_bar[warp], it & 1, abort_flag, p.status, 18)) { ok = false; break; }
+            if (p.resid && !mbar_wait(&stage_bar[warp], stage_phase, abort_flag, p.status, 18)) { ok = false; break; }
+            float rs = 0.f, rm = 0.f;
+            if (EPI == LG_EPI_TRI_OUT) {
+              if (!mbar_wait(&stat_full[it % NS], (uint32_t)(it / NS) & 1u, abort_flag, p.status, 17)) { ok = false; break; }
+              rs = sStat[(it & 1) * 256 + row];
+              rm = sStat[(it & 1) * 256 + 128 + row];
+            }
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
-              uint32_t v1[16];
-              tmem_ld16(acc + part * 32 + half * 16, v1);
+              const int c0 = part * 32 + half * 16;
+              uint32_t v1[16], v2[16];
+              tmem_ld16(acc + c0, v1);
+              if (EPI == LG_EPI_TRI_OUT) tmem_ld16(acc + 128 + c0, v2);
               tmem_ld_wait();
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
                 float4* cell = reinterpret_cast<float4*>(stage + ((uint32_t)((half * 4 + k4) ^ (lane & 7)) << 4));
-                const float* bias = sBias + part * 32 + half * 16 + k4 * 4;
-                float4 o = make_float4(__uint_as_float(v1[k4 * 4]) + bias[0], __uint_as_float(v1[k4 * 4 + 1]) + bias[1],
-                                       __uint_as_float(v1[k4 * 4 + 2]) + bias[2], __uint_as_float(v1[k4 * 4 + 3]) + bias[3]);
+                const float* bias = sBias + c0 + k4 * 4;
+                float e4[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (EPI == LG_EPI_TRI_OUT) {
+                    // (x - mean) * inv folded: inv * acc - inv*mean * s1[c] + t[c], gated
+                    const float lin = fmaf(rs, __uint_as_float(v1[k4 * 4 + e]), fmaf(-rm, bias[e], bias[128 + e]));
+                    e4[e] = lin * sigmoid_fast(__uint_as_float(v2[k4 * 4 + e]) + bias[256 + e]);
+                  } else {
+                    e4[e] = __uint_as_float(v1[k4 * 4 + e]) + bias[e];
+                  }
+                }
+                float4 o = make_float4(e4[0], e4[1], e4[2], e4[3]);
                 if (p.resid) { const float4 rr = *cell; o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
                 *cell = o;
               }
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) { tma_store_3d(&mapX, sStage + warp * 4096, tx, ty, tz); bulk_commit(); }
+            if (lane == 0) { tma_store_3d(&mapO, sStage + warp * 4096, tx, ty, tz); bulk_commit(); }
           }
         } else if (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) {
           // thread = pair row; this warp's quarter = 32 output channels, two runs of 16
@@ -525,7 +555,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
           }
           float rs = 0.f, rm = 0.f;
           if (EPI == LG_EPI_TRI_OUT) {
-            if (!mbar_wait(&stat_full[it & 1], (it >> 1) & 1, abort_flag, p.status, 17)) { ok = false; break; }
+            if (!mbar_wait(&stat_full[it % NS], (uint32_t)(it / NS) & 1u, abort_flag, p.status, 17)) { ok = false; break; }
             rs = sStat[(it & 1) * 256 + row];
             rm = sStat[(it & 1) * 256 + 128 + row];
           }
@@ -655,7 +685,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const LnGemmParams p) {
     }
   }
 
-  if (EPI == LG_EPI_OUTPUT && p.tma_out && warp < LG_EPI_WARPS && lane == 0) bulk_wait_all();   // this thread's stores have landed
+  if ((EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out && warp < LG_EPI_WARPS && lane == 0) bulk_wait_all();   // this thread's stores have landed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) drain_after_abort();
@@ -691,7 +721,7 @@ void configure_ln_gemm() {
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_ATTENTION>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(528));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128, false, true));
-  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, true));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, false, true));
   cudaGetLastError();
 }
 
@@ -708,7 +738,7 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, p);
+  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -733,7 +763,7 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(CUtensorMap{}, p);
+  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -767,7 +797,7 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
   // the fp16 rows are in logical order; the transposed scatter happens in the epilogue (or in the tensor map)
-  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128, false, true), ctx->stream>>>(mo, p);
+  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128, false, true), ctx->stream>>>(CUtensorMap{}, mo, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -791,8 +821,13 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
   p.status = (Status*)ctx->tc_status;
   const int64_t tiles = (int64_t)rows * p.tile_per_row;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  // float32 pair updated in place (or no residual): the residual tile and the result travel by TMA; the map is
+  // (channel, k, i) so that the last tile of a pair row is clipped at k = n
+  CUtensorMap mo{};
+  p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out)) ? 1 : 0;
+  if (p.tma_out) LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)n, (uint64_t)rows, 512, (uint64_t)n * 512, 32, 1));
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_OUTPUT);
-  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, true), ctx->stream>>>(mapX, p);
+  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, false, true), ctx->stream>>>(mapX, mo, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
