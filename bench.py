@@ -69,7 +69,7 @@ FAMILY_WORK = {
 # (dram__bytes_read.sum + dram__bytes_write.sum; profiles/kernels_af2_pair_block_n1024.md).  The traffic of
 # every kernel grows with the number of pair positions, so a launch on `rows x n` positions is scaled from it.
 TRAFFIC_PER_POSITION = {"triangle_contract": 737.0, "attention": 1284.0, "ln_gemm": 1234.0,
-                        "triangle_output": 1233.0, "transition": 975.0}
+                        "triangle_output": 1234.0, "transition": 975.0}
 FAMILY_NAME = {
     "triangle_contract": "triangle contraction (tcgen05, 128 batched GEMMs)",
     "attention": "attention core (tcgen05 Q K^T and P V, softmax between them in tensor memory)",
