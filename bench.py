@@ -10,9 +10,14 @@ of ones), synthetic N(0,1) pair and N(0, 1/fan_in) weights.  Successive steps
 are successive blocks of the stack on the same pair, as in the stack runner.
 
 The JSON line reports ms per block (lower is better) with the pair resident in
-HBM (`value`), the same through the host-buffer API with copies in the timed
-region (`e2e`), the live roofline of the triangle contraction kernel, and the
-CPU oracle timed on this host on a bounded sample (`cpu_baseline`).
+HBM (`value`, timed with per-kernel profiling off), the same through the
+host-buffer API with copies in the timed region (`e2e`), the live roofline of
+every kernel family from a second, profiled pass over the same steps, the
+N = 384 block time the metric also names (`extra.n384_ms_per_block`, L2 flushed
+between blocks because that pair fits in L2), and - at N = 1 - the CPU oracle
+timed on this host on a bounded sample (`cpu_baseline`).  `--pair-dtype bf16`
+stores the pair stream in bf16, as BASELINE config 4 words it; the default is
+float32, the storage that meets the per-block accuracy bound.
 
 `--impl reference` times the reference's CPU implementation of the same block
 (the C restatement under oracle/; the reference itself is JavaScript and no
@@ -53,23 +58,33 @@ def contraction_flops(n: int) -> float:
 # bytes that must cross HBM for the fused LayerNorm/projection kernels (pair stream f32, operands f16).
 #   triangle_contract  128 channels x (rows x rows_b x n) GEMM            256 rows rows_b n FLOP
 #   attention          Q K^T and P V over 4 heads x 32                    512 rows n n FLOP
-#   ln_gemm            triangle projection: z in, a and b out             1024 B / position
-#                      attention projection: z in, q k v gate + bias out  1544 B / position
-#                      attention output: o and z in, z out                1280 B / position
-#   triangle_output    x and z in, z out                                  1280 B / position
-#   transition         z in, z out                                        1024 B / position
+# with w the bytes of a pair element (4 for the float32 stream, 2 for bf16):
+#   ln_gemm            triangle projection: z in, a and b out             128 w + 512 B / position
+#                      attention projection: z in, q k v gate + bias out  128 w + 1032 B / position
+#                      attention output: o and z in, z out                256 w + 256 B / position
+#   triangle_output    x and z in, z out                                  256 w + 256 B / position
+#   transition         z in, z out                                        256 w B / position
 FAMILY_WORK = {
-    "triangle_contract": ("tensor", lambda rows, n, world: 256.0 * rows * rows * n),
-    "attention": ("tensor", lambda rows, n, world: 512.0 * rows * n * n),
-    "ln_gemm": ("hbm", lambda rows, n, world: (2 * 1024 + 2 * 1544 + 2 * 1280) / 6.0 * rows * n),
-    "triangle_output": ("hbm", lambda rows, n, world: 1280.0 * rows * n),
-    "transition": ("hbm", lambda rows, n, world: 1024.0 * rows * n),
+    "triangle_contract": ("tensor", lambda rows, n, world, w: 256.0 * rows * rows * n),
+    "attention": ("tensor", lambda rows, n, world, w: 512.0 * rows * n * n),
+    "ln_gemm": ("hbm", lambda rows, n, world, w: (2 * (128 * w + 512) + 2 * (128 * w + 1032) + 2 * (256 * w + 256)) / 6.0 * rows * n),
+    "triangle_output": ("hbm", lambda rows, n, world, w: (256.0 * w + 256) * rows * n),
+    "transition": ("hbm", lambda rows, n, world, w: 256.0 * w * rows * n),
 }
-# DRAM bytes per pair position and launch, from one ncu capture of the N = 1024 block
-# (dram__bytes_read.sum + dram__bytes_write.sum; profiles/kernels_af2_pair_block_n1024.md).  The traffic of
-# every kernel grows with the number of pair positions, so a launch on `rows x n` positions is scaled from it.
-TRAFFIC_PER_POSITION = {"triangle_contract": 737.0, "attention": 1284.0, "ln_gemm": 1234.0,
-                        "triangle_output": 1234.0, "transition": 975.0}
+
+
+def traffic_per_position():
+    """DRAM bytes per pair position and launch of each kernel family, as written by the profiling step from
+    an ncu capture of this build (dram__bytes_read.sum + dram__bytes_write.sum at a smaller N, divided by
+    the positions of that launch; every kernel's traffic grows with the positions).  None when no capture
+    is on file: `traffic` is then null rather than a stale figure."""
+    path = os.path.join(ROOT, "profiles", "traffic_af2_pair_block.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f)
+
+
 FAMILY_NAME = {
     "triangle_contract": "triangle contraction (tcgen05, 128 batched GEMMs)",
     "attention": "attention core (tcgen05 Q K^T and P V, softmax between them in tensor memory)",
@@ -79,18 +94,19 @@ FAMILY_NAME = {
 }
 
 
-def roofline_table(families, n, world, peaks):
+def roofline_table(families, n, world, peaks, pair_bytes=4):
     """Per kernel family: algorithmic work per launch / its measured launch time against the
     measured peak.  Returns (the entry of the family with the largest share of the step, all entries)."""
     rows = n // world
     total = sum(v[0] for v in families.values()) or 1.0
+    traffic = traffic_per_position()
     out = []
     for fam, (bound, work) in FAMILY_WORK.items():
         ms, launches = families.get(fam, (0.0, 0))
         if not launches:
             continue
         per_launch_ms = ms / launches
-        w = work(rows, n, world)
+        w = work(rows, n, world, pair_bytes)
         if bound == "tensor":
             achieved, peak, unit = w / (per_launch_ms * 1e-3) / 1e12, peaks["tflops_sustained"], "TFLOP/s"
             src = peaks["source"] + " (sustained cuBLAS bf16: the kernel runs inside a long step)"
@@ -98,10 +114,15 @@ def roofline_table(families, n, world, peaks):
             achieved, peak, unit = w / (per_launch_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
             src = peaks["source"] + " (copy bandwidth)"
         out.append({"kernel": FAMILY_NAME[fam], "family": fam, "bound": bound, "achieved": achieved, "peak": peak,
-                    "unit": unit, "frac": achieved / peak, "traffic": TRAFFIC_PER_POSITION[fam] * rows * n,
-                    "traffic_source": "ncu capture at N=1024 scaled by pair positions", "peak_source": src,
+                    "unit": unit, "frac": achieved / peak,
+                    "traffic": traffic["bytes_per_position"][fam] * rows * n if traffic and fam in traffic.get("bytes_per_position", {}) else None,
+                    "traffic_source": traffic.get("source") if traffic else None, "peak_source": src,
                     "launch_ms": per_launch_ms, "launches": launches, "share_of_step": ms / total,
                     "work_per_launch": w})
+        if fam == "transition":      # a GEMM pair at 256-512 flop per byte: reported against both rooflines
+            flops = 262144.0 * rows * n
+            out[-1]["tensor"] = {"achieved": flops / (per_launch_ms * 1e-3) / 1e12, "peak": peaks["tflops_sustained"],
+                                 "unit": "TFLOP/s", "frac": flops / (per_launch_ms * 1e-3) / 1e12 / peaks["tflops_sustained"]}
     out.sort(key=lambda e: -e["share_of_step"])
     return (out[0] if out else None), out
 
@@ -164,13 +185,21 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(sample_n: int, full_n: int, threads: int | None = None):
+def host_threads() -> int:
+    """Cores this process may run on: the CPU legs use exactly these, whatever OMP_NUM_THREADS says
+    (torchrun exports OMP_NUM_THREADS=1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_sample(sample_n: int, full_n: int):
     """Times the CPU oracle on one AF2 pair block at `sample_n` and scales to `full_n` by FLOPs."""
     from localfold_b200 import synthetic as syn
     from oracle import oracle
-    if threads:
-        oracle.set_threads(threads)
-    cores = oracle.max_threads() if not threads else threads
+    cores = host_threads()
+    oracle.set_threads(cores)
     pair, mask, weights = syn.af2_pair_block(4, sample_n)
     t0 = time.perf_counter()
     oracle.af2_pair_block(pair, mask, weights[0], C_HIDDEN)
@@ -183,6 +212,8 @@ def cpu_sample(sample_n: int, full_n: int, threads: int | None = None):
 
 
 def run_reference(args, rank):
+    """The reference arm: the CPU restatement on all host cores.  Rank 0 alone works; under torchrun the
+    other ranks leave at once (no process group is formed, nothing waits on anything)."""
     if rank != 0:
         return
     full_n = args.length
@@ -193,14 +224,14 @@ def run_reference(args, rank):
         res = cpu_sample(sample_n, full_n)
         if i >= args.warmup:
             times.append(res["value"])
-        if sum(times) and (time.perf_counter() - START) > 240:
+        if times and (time.perf_counter() - START) > 150:
             break
     ms = float(np.mean(times))
     line = {
         "impl": "reference", "metric": "pair_stack_block_ms", "value": ms, "unit": "ms/block", "n_gpus": args.gpus,
         "steps": len(times), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate / f32 store", "data": "synthetic",
-        "config": workload_config(args, 1),
+        "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": ms, "unit": "ms/block", "cores": res["cores"], "kind": "port", "sample": res["sample"]},
         "e2e": {"value": ms, "unit": "ms/block", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -211,12 +242,12 @@ def run_reference(args, rank):
 def workload_config(args, n_gpus):
     return {"workload": f"AF2 Evoformer pair-stack block, N={args.length}, c_z=128, tri-mult c=128, "
                         f"tri-attention 4x32, transition 4x, seed 4, mask ones (BASELINE config 4 shape)",
-            "length": args.length, "precision": args.precision, "pair_dtype": "f32",
+            "length": args.length, "precision": args.precision, "pair_dtype": args.pair_dtype,
             "parallelism": "single GPU" if n_gpus == 1 else
             f"pair rows sharded over {n_gpus} GPUs (NCCL all-gather of the triangle operand b and of the pair bias; "
             f"4 transposes per block by " + ("one peer-store kernel each over NVLink" if args.transpose == "peer"
                                             else "NCCL all-to-all") + ")",
-            "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * 4 / 2 ** 20)}
+            "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * (2 if args.pair_dtype == "bf16" else 4) / 2 ** 20)}
 
 
 def main():
@@ -227,9 +258,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--length", type=int, default=2048)
     ap.add_argument("--precision", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--pair-dtype", default="f32", choices=["f32", "bf16"],
+                    help="storage of the pair stream (bf16: BASELINE config 4 as worded; f32 meets the 2e-3 per-block bound)")
     ap.add_argument("--cpu-sample", type=int, default=384, help="N of the CPU oracle's bounded sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-n384", action="store_true", help="skip the N = 384 leg")
     ap.add_argument("--transpose", default="peer", choices=["peer", "nccl"],
                     help="N > 1: transposes of the sharded pair by peer stores (one kernel) or by NCCL all-to-all")
     args = ap.parse_args()
@@ -258,10 +292,13 @@ def main():
 
     n = args.length
     opts = {"precision": args.precision, "variance": "two-pass"}
+    pair_dtype = torch.bfloat16 if args.pair_dtype == "bf16" else torch.float32
+    pair_bytes = 2 if args.pair_dtype == "bf16" else 4
+    sharded_check = None
     if world == 1:
         pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
         stack = lf.PairStackGpu(dev).prepare(weights, C_Z, C_HIDDEN)
-        pair_d = torch.from_numpy(pair_h).cuda()
+        pair_d = torch.from_numpy(pair_h).cuda().to(pair_dtype)
         mask_d = torch.from_numpy(mask_h).cuda()
 
         def step(i):
@@ -275,28 +312,56 @@ def main():
         pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
         prepared = [lf.PreparedPairBlock(dev, w, C_Z, C_HIDDEN) for w in weights]
         block_w = [prepared_block_weights(b) for b in prepared]
-        pair_h = np.ascontiguousarray(shard_rows(pair_h, rank, world))
-        transposer = None
-        if args.transpose == "peer":   # the shard lives in buffers the ranks share; transposes are peer stores
-            try:
-                transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
-                mapped = 1
-            except Exception as exc:   # e.g. no peer access between two of the GPUs: every rank falls back together
-                print(f"rank {rank}: peer mapping failed ({exc}); using NCCL all-to-all transposes", file=sys.stderr)
-                mapped = 0
-            flag = torch.tensor([mapped], device="cuda")
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-            if int(flag.item()) == 0:
-                transposer = None
-                args.transpose = "nccl"
-        if transposer is not None:
-            transposer.shard().copy_(torch.from_numpy(pair_h))
-            shard = {"z": transposer.shard()}
-        else:
-            shard = {"z": torch.from_numpy(pair_h).cuda()}
-        m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(mask_h, rank, world))).cuda()
-        m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(mask_h.T), rank, world))).cuda()
-        sharded = ShardedPairStack(TorchComm(), GpuShardOps(dev, n // world, n, world), transposer)
+
+        def build(length, full_pair, full_mask):
+            """The sharded runner for one length: (shard holder, row masks, runner, transposer)."""
+            rows = length // world
+            local = np.ascontiguousarray(shard_rows(full_pair, rank, world))
+            transposer = None
+            if args.transpose == "peer":   # the shard lives in buffers the ranks share; transposes are peer stores
+                try:
+                    transposer = PeerTranspose(dev, None, rows, length, pair_dtype)
+                    mapped = 1
+                except Exception as exc:   # e.g. no peer access between two of the GPUs: every rank falls back together
+                    print(f"rank {rank}: peer mapping failed ({exc}); using NCCL all-to-all transposes", file=sys.stderr)
+                    mapped = 0
+                flag = torch.tensor([mapped], device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 0:
+                    transposer = None
+                    args.transpose = "nccl"
+            if transposer is not None:
+                transposer.shard().copy_(torch.from_numpy(local).cuda().to(pair_dtype))
+                holder = {"z": transposer.shard()}
+            else:
+                holder = {"z": torch.from_numpy(local).cuda().to(pair_dtype)}
+            m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(full_mask, rank, world))).cuda()
+            m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(full_mask.T), rank, world))).cuda()
+            runner = ShardedPairStack(TorchComm(), GpuShardOps(dev, rows, length, world), transposer)
+            return holder, m_rows, m_t_rows, runner, transposer, local
+
+        # Numerical check of the path that is about to be timed (NCCL gathers, peer-store transposes): one
+        # block at a small length, every rank's shard against the same block run unsharded on this GPU.
+        check_n = 16 * world * max(1, 256 // (16 * world))
+        small_pair, small_mask, _ = syn.af2_pair_block(5, check_n, masked_tail=0.05)
+        holder, m_rows, m_t_rows, runner, tr, _ = build(check_n, small_pair, small_mask)
+        holder["z"] = runner.block(holder["z"], m_rows, m_t_rows, block_w[0])
+        single = torch.from_numpy(small_pair).cuda().to(pair_dtype)
+        ref_stack = lf.PairStackGpu(dev).prepare([prepared[0]], C_Z, C_HIDDEN)
+        ref_stack.run(single, torch.from_numpy(small_mask).cuda(), opts, first_block=0, n_blocks=1)
+        torch.cuda.synchronize()
+        mine = single[rank * (check_n // world):(rank + 1) * (check_n // world)].float()
+        num = torch.linalg.vector_norm((holder["z"].float() - mine).double()) ** 2
+        den = torch.linalg.vector_norm(mine.double()) ** 2
+        both = torch.stack([num, den])
+        dist.all_reduce(both)
+        sharded_check = {"length": check_n, "rel_l2_vs_unsharded": float(torch.sqrt(both[0] / both[1]).item()),
+                         "what": "one sharded block (NCCL gathers, transposes as timed) against the same block on one GPU"}
+        if tr is not None:
+            tr.close()
+        del holder, runner
+
+        shard, m_rows, m_t_rows, sharded, transposer, pair_h = build(n, pair_h, mask_h)
         stack = None
 
         def step(i):
@@ -311,9 +376,8 @@ def main():
     for i in range(args.warmup):
         step(i)
     barrier()
+    # timed region: K blocks, per-kernel profiling off
     launches0 = dev.launch_count()
-    dev.profile(True)
-    dev.profile_read()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -326,24 +390,54 @@ def main():
     barrier()
     total_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    families = dev.profile_read()
-    dev.profile(False)
     launches = dev.launch_count() - launches0
     if world > 1:
         t = torch.tensor([total_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
     ms_per_block = total_ms / args.steps
-    finite = bool(torch.isfinite(pair_d if world == 1 else shard["z"]).all().item())
+    finite = bool(torch.isfinite((pair_d if world == 1 else shard["z"]).float()).all().item())
 
-    # end to end through the host-buffer API: pinned host pair in, pair out, every step
+    # second pass over the same steps with every launch bracketed by events: the per-family split
+    dev.profile(True)
+    dev.profile_read()
+    for i in range(args.steps):
+        step(i)
+    barrier()
+    families = dev.profile_read()
+    dev.profile(False)
+
+    # the metric's other length: N = 384 on one GPU.  That pair (75 MB in float32) fits in L2, so a
+    # buffer larger than L2 is written between blocks and each block is timed by its own events.
+    extra = {}
+    if world == 1 and n != 384 and not args.no_n384:
+        p384, m384, _ = syn.af2_pair_block(4, 384)
+        z384 = torch.from_numpy(p384).cuda().to(pair_dtype)
+        k384 = torch.from_numpy(m384).cuda()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for i in range(3 + 10):
+            flush.fill_(i & 0xff)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            stack.run(z384, k384, opts, first_block=i % 2, n_blocks=1)
+            b.record(stream)
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        extra["n384_ms_per_block"] = float(np.mean(times))
+        extra["n384_note"] = "AF2 pair block at N=384 on one GPU, mean of 10 blocks, 256 MiB written between blocks to flush L2"
+        extra["n384_tflops_block"] = block_flops(384) / (extra["n384_ms_per_block"] * 1e-3) / 1e12
+        del z384, flush
+
+    # end to end through the public API with host buffers: pinned host pair in, pair out, every step
     e2e = None
     if not args.no_e2e:
         rows_local = n // world
-        pinned = torch.empty((rows_local, n, C_Z), dtype=torch.float32, pin_memory=True)
-        pinned.copy_(torch.from_numpy(pair_h).reshape(rows_local, n, C_Z))
         reps = max(2, min(args.steps, 3))
-        if world == 1:
+        if world == 1 and pair_dtype == torch.float32:
+            pinned = torch.empty((rows_local, n, C_Z), dtype=torch.float32, pin_memory=True)
+            pinned.copy_(torch.from_numpy(pair_h).reshape(rows_local, n, C_Z))
             mask_p = torch.empty((n, n), dtype=torch.float32, pin_memory=True)
             mask_p.copy_(torch.from_numpy(mask_h))
             host_pair, host_mask = pinned.numpy(), mask_p.numpy()
@@ -351,13 +445,20 @@ def main():
             def e2e_step(i):   # the public host-buffer call: pair in, block, pair out
                 stack.run(host_pair, host_mask, opts, first_block=i % 2, n_blocks=1, inplace=True)
             h2d = int(pinned.numel() * 4 + mask_p.numel() * 4)
+            d2h = int(pinned.numel() * 4)
         else:
-            def e2e_step(i):   # each rank: its pinned shard in, the sharded block, its shard out
-                shard["z"].copy_(pinned, non_blocking=True)
+            pinned = torch.empty((rows_local, n, C_Z), dtype=pair_dtype, pin_memory=True)
+            pinned.copy_(torch.from_numpy(pair_h).reshape(rows_local, n, C_Z).to(pair_dtype))
+            target = pair_d if world == 1 else None
+
+            def e2e_step(i):   # each rank: its pinned shard in, the block on the device, its shard out
+                dst = target if world == 1 else shard["z"]
+                dst.copy_(pinned, non_blocking=True)
                 step(i)
-                pinned.copy_(shard["z"], non_blocking=True)
+                pinned.copy_(target if world == 1 else shard["z"], non_blocking=True)
                 torch.cuda.synchronize()
-            h2d = int(pinned.numel() * 4) * world
+            h2d = int(pinned.numel() * pair_bytes) * world
+            d2h = h2d
         e2e_step(0)   # warm the staging arena
         barrier()
         t0 = time.perf_counter()
@@ -369,32 +470,32 @@ def main():
             t = torch.tensor([wall], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             wall = float(t.item())
-        e2e = {"value": wall, "unit": "ms/block", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": int(pinned.numel() * 4) * world}
+        e2e = {"value": wall, "unit": "ms/block", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
+    # the ranks part here: the CPU leg below runs on rank 0 of a single-GPU run only, so nobody waits on it
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank == 0:
         peaks = measured_peaks()
-        roofline, roofline_kernels = roofline_table(families, n, world, peaks)
+        roofline, roofline_kernels = roofline_table(families, n, world, peaks, pair_bytes)
         cpu = None
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:
             cpu = cpu_sample(args.cpu_sample, n)
         line = {
             "metric": "pair_stack_block_ms", "value": ms_per_block, "unit": "ms/block", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_block, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16 operands / f32 accumulate (pair stream f32)" if args.precision == "bf16" else "f32",
+            "dtype": ("f16 operands / f32 accumulate (pair stream %s)" % args.pair_dtype) if args.precision == "bf16" else "f32",
             "data": "synthetic", "config": workload_config(args, world),
             "tflops_block": block_flops(n) / (ms_per_block * 1e-3) / 1e12,
             "roofline": roofline, "roofline_kernels": roofline_kernels, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
             "kernel_ms_per_step": {k: v[0] / args.steps for k, v in families.items() if v[1]},
-            "clocks": clocks, "finite": finite,
+            "clocks": clocks, "finite": finite, "extra": extra, "sharded_check": sharded_check,
         }
         print(json.dumps(line))
     if stack is not None:
         stack.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 START = time.perf_counter()

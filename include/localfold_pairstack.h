@@ -53,9 +53,12 @@ typedef enum lf_space { LF_SPACE_HOST = 0, LF_SPACE_DEVICE = 1 } lf_space;
 typedef enum lf_dtype { LF_DTYPE_F32 = 0, LF_DTYPE_BF16 = 1 } lf_dtype;
 
 /* Arithmetic mode.  F32: float32 storage and float32 FMA accumulation
- * (the reference's `precision: "f32"`).  BF16: bf16 operands on the tensor
- * cores with float32 accumulation, float32 statistics, softmax and gates
- * (stands where the reference has `precision: "f16"`). */
+ * (the reference's `precision: "f32"`).  BF16 names the 16-bit tensor-core
+ * mode: its tensor-core operands are fp16 (11-bit significand; every rounded
+ * operand is bounded by construction), products accumulate in float32, and
+ * LayerNorm statistics, softmax and gates are float32.  It stands where the
+ * reference has `precision: "f16"`; the enumerator keeps its name because the
+ * pair stream this mode is usually paired with is bf16 or float32 (lf_dtype). */
 typedef enum lf_precision { LF_PRECISION_F32 = 0, LF_PRECISION_BF16 = 1 } lf_precision;
 
 /* LayerNorm variance: the reference's `variance: "two-pass" | "fast"`
@@ -80,6 +83,13 @@ typedef struct lf_result {
  * webgpu/runtime/execution.js:156).  `stream` may be NULL (the context makes
  * its own) or a cudaStream_t the caller owns. */
 LF_API lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out);
+/* The same with the stream taken as given: NULL here means CUDA's default stream (which
+ * lf_context_create cannot express, NULL being "make one").  For callers whose other work - their
+ * own kernels, NCCL collectives - runs on that stream and must stay ordered with this library's. */
+LF_API lf_status lf_context_create_on_stream(int device_ordinal, void* stream, lf_context** out);
+/* The cudaStream_t every call of this context enqueues on.  Work the caller enqueues elsewhere is
+ * not ordered with the library's: use this stream, or events, or lf_context_synchronize. */
+LF_API void* lf_context_stream(const lf_context* ctx);
 LF_API void lf_context_destroy(lf_context* ctx);
 LF_API const char* lf_last_error(const lf_context* ctx);
 LF_API lf_status lf_context_synchronize(lf_context* ctx);
@@ -215,7 +225,10 @@ LF_API lf_status lf_triangle_multiplication_run(lf_context* ctx, const lf_triang
  * a fixed 12 MiB array inside the library's device image instead of the scratch arena, so the call
  * makes no cudaMalloc, cudaFree or other allocating call; every GPU that loads the library holds
  * that array until the process exits.  The first call on each device looks the array's address up
- * once (cudaGetSymbolAddress); make that first call before any stream capture.  All calls share
+ * once (cudaGetSymbolAddress; safe from several host threads at once); make that first call before
+ * any stream capture, and during start-up: CUDA loads modules lazily, so this look-up and the first
+ * launch of each kernel are also when the driver loads the library's device code, which may take
+ * driver-side memory.  All calls share
  * the one array and it keeps the last call's contents (nothing in it needs clearing): two calls
  * that overlap on the GPU - different contexts or streams on one device - race on it, so run them
  * one after the other. */

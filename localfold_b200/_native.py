@@ -104,7 +104,7 @@ class ShardStepDesc(ctypes.Structure):
 
 
 EXPORTS = (
-    "lf_version", "lf_context_create", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
+    "lf_version", "lf_context_create", "lf_context_create_on_stream", "lf_context_stream", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
     "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
@@ -128,6 +128,9 @@ def load():
     lib.lf_last_error.restype = ctypes.c_char_p
     lib.lf_last_error.argtypes = [c_void_p]
     lib.lf_context_create.argtypes = [ctypes.c_int, c_void_p, ctypes.POINTER(c_void_p)]
+    lib.lf_context_create_on_stream.argtypes = [ctypes.c_int, c_void_p, ctypes.POINTER(c_void_p)]
+    lib.lf_context_stream.argtypes = [c_void_p]
+    lib.lf_context_stream.restype = c_void_p
     lib.lf_context_destroy.argtypes = [c_void_p]
     lib.lf_context_destroy.restype = None
     lib.lf_context_synchronize.argtypes = [c_void_p]

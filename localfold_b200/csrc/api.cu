@@ -5,6 +5,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "simt_kernels.cuh"
 #include "tc_kernels.cuh"
@@ -52,7 +53,19 @@ extern "C" {
 
 const char* lf_version(void) { return "localfold-pairstack-b200 0.1 (sm_100a)"; }
 
+static lf_status context_create(int device_ordinal, void* stream, bool make_stream, lf_context** out);
+
 lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out) {
+  return context_create(device_ordinal, stream, stream == nullptr, out);
+}
+
+lf_status lf_context_create_on_stream(int device_ordinal, void* stream, lf_context** out) {
+  return context_create(device_ordinal, stream, false, out);
+}
+
+void* lf_context_stream(const lf_context* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+static lf_status context_create(int device_ordinal, void* stream, bool make_stream, lf_context** out) {
   if (!out) return LF_ERR_ARGUMENT;
   *out = nullptr;
   int count = 0;
@@ -62,7 +75,7 @@ lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out) 
   if (cudaSetDevice(device_ordinal) != cudaSuccess) return LF_ERR_CUDA;
   lf_context* ctx = new lf_context();
   ctx->device = device_ordinal;
-  if (stream) { ctx->stream = (cudaStream_t)stream; ctx->owns_stream = false; }
+  if (!make_stream) { ctx->stream = (cudaStream_t)stream; ctx->owns_stream = false; }
   else {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return LF_ERR_CUDA; }
     ctx->owns_stream = true;
@@ -72,6 +85,15 @@ lf_status lf_context_create(int device_ordinal, void* stream, lf_context** out) 
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device_ordinal) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
   tc::configure_once();
+  {   // the centre LayerNorm of the generic path stages c x 33 floats: up to cHidden = 512 is accepted
+    static std::once_flag per_device[64];
+    if (device_ordinal < 64)
+      std::call_once(per_device[device_ordinal], [] {
+        cudaFuncSetAttribute(simt::center_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 512 * 33 * 4);
+        cudaFuncSetAttribute(simt::center_norm_kernel<op16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 512 * 33 * 4);
+        cudaGetLastError();
+      });
+  }
   if (cudaMalloc(&ctx->tc_status, 16) == cudaSuccess) cudaMemset(ctx->tc_status, 0, 16);
   *out = ctx;
   return LF_OK;

@@ -62,13 +62,13 @@ enum { TRN_LN_G, TRN_LN_B, TRN_W1, TRN_B1, TRN_W2, TRN_B2, TRN_COUNT };
 enum { OPM_LN_G, OPM_LN_B, OPM_WL, OPM_BL, OPM_WR, OPM_BR, OPM_WOUT, OPM_BOUT, OPM_COUNT };
 
 // Canonical device-resident weights.  Every linear is stored (in,out) row-major
-// float32 in `f[...]`; tensor-core kernels keep extra bf16 repacks in `h[...]`.
+// float32 in `f[...]`; tensor-core kernels keep extra fp16 repacks (swizzled operand images) in `h[...]`.
 struct lf_weights {
   lf_context* ctx = nullptr;
   int kind = 0;
   lf_weight_dims dims{};
   std::vector<float*> f;     // named by the per-kind enums in weights.cuh
-  std::vector<void*> h;      // bf16 repacks (tensor-core path)
+  std::vector<void*> h;      // fp16 repacks (tensor-core path)
   std::vector<void*> owned;  // every device allocation, for destroy
   int bias_flags = 0;        // per 128-column group of the fused projection: bias is non-zero
   bool has_gate_bias = false, has_out_bias = false, has_pair_norm = false, has_pair_proj = false;

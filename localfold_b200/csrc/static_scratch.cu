@@ -10,6 +10,9 @@
 // (12 MiB) until the process exits.
 #include <cuda_runtime.h>
 
+#include <cmath>
+#include <mutex>
+
 #include "tc_kernels.cuh"
 
 #define LF_STATIC_MAX_LENGTH 128   // largest pair length the static scratch covers (c_z = c_hidden = 128)
@@ -24,21 +27,27 @@ constexpr size_t kStaticBytes = 3 * 128 * kStaticPlane * sizeof(op16);          
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
 constexpr int kMaxDevices = 64;
-static void* g_static_ptr[kMaxDevices];   // per device: device address of g_static_scratch, null = not set up yet
+// Per device: device address of g_static_scratch (null = not resolved) and the error of the one attempt.
+// std::call_once makes the first call per device safe from several host threads at once.
+static void* g_static_ptr[kMaxDevices];
+static cudaError_t g_static_err[kMaxDevices];
+static std::once_flag g_static_once[kMaxDevices];
 
-// Once per device, with that device current: resolve the array's device address.
+// Once per device, with that device current: resolve the array's device address.  With CUDA's lazy
+// module loading this is also the moment the driver loads the module that holds the array.
 lf_status static_scratch_setup(lf_context* ctx, void** out) {
   if (ctx->device < 0 || ctx->device >= kMaxDevices) return lf_fail(ctx, LF_ERR_ARGUMENT, "device ordinal %d is out of range", ctx->device);
-  if (!g_static_ptr[ctx->device]) {
+  const int dev = ctx->device;
+  std::call_once(g_static_once[dev], [dev]() {
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
-    if (e != cudaSuccess || ptr == nullptr) {
-      cudaGetLastError();
-      return lf_fail(ctx, LF_ERR_CUDA, "cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(e));
-    }
-    g_static_ptr[ctx->device] = ptr;
-  }
-  *out = g_static_ptr[ctx->device];
+    if (e != cudaSuccess) cudaGetLastError();
+    g_static_err[dev] = (e == cudaSuccess && ptr == nullptr) ? cudaErrorInvalidSymbol : e;
+    g_static_ptr[dev] = e == cudaSuccess ? ptr : nullptr;
+  });
+  if (!g_static_ptr[dev])
+    return lf_fail(ctx, LF_ERR_CUDA, "cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(g_static_err[dev]));
+  *out = g_static_ptr[dev];
   return LF_OK;
 }
 
@@ -54,7 +63,7 @@ extern "C" lf_status lf_triangle_multiplication_run_static(lf_context* ctx, cons
   if (d->act_dtype != LF_DTYPE_F32 && d->act_dtype != LF_DTYPE_BF16) return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown activation dtype %d", d->act_dtype);
   if (d->variance != LF_VARIANCE_TWO_PASS && d->variance != LF_VARIANCE_FAST)
     return lf_fail(ctx, LF_ERR_ARGUMENT, "variance has no default: pass LF_VARIANCE_TWO_PASS or LF_VARIANCE_FAST");
-  if (!(d->epsilon > 0.f)) return lf_fail(ctx, LF_ERR_ARGUMENT, "epsilon must be finite and positive; received %g", (double)d->epsilon);
+  if (!(d->epsilon > 0.f) || !std::isfinite(d->epsilon)) return lf_fail(ctx, LF_ERR_ARGUMENT, "epsilon must be finite and positive; received %g", (double)d->epsilon);
   if (d->length <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "length must be a positive safe integer; received %d", d->length);
   if (d->length > LF_STATIC_MAX_LENGTH)
     return lf_fail(ctx, LF_ERR_UNSUPPORTED, "length %d exceeds the static scratch, which covers lengths up to %d; use lf_triangle_multiplication_run",

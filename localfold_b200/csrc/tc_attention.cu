@@ -46,7 +46,23 @@ constexpr int FA_BIAS_SLOTS = 2;                    // per issuer; a slot holds 
 constexpr int FA_IDENT_BYTES = 2048;                // 16 x 16 identity, 128-byte swizzled rows
 constexpr int FA_SMEM = 2 * FA_Q_BYTES + FA_STAGES * 2 * FA_KV_BYTES + 2 * FA_BIAS_SLOTS * 2 * FA_BIAS_BYTES +
                         FA_IDENT_BYTES + FA_STAGES * FA_KT * 4 + 512 + 1024;
+// Register budget: the CTA starts with 20 warps x 96 registers, and setmaxnreg trades inside the CTA's
+// own allocation: 16 softmax warps x 104 + 4 service warps x 64 = 20 x 96.
+constexpr uint32_t FA_REGS_SOFTMAX = 104, FA_REGS_SERVICE = 64;
 constexpr int FA_O_COL = 2 * FA_KT;                 // O accumulator columns inside a stream's region, after the two S / P buffers
+
+#ifndef FA_SETMAXNREG
+#define FA_SETMAXNREG 1
+#endif
+#ifndef FA_PINGPONG
+#define FA_PINGPONG 1  // the two query tiles take turns at the exponentials
+#endif
+#ifndef FA_EARLY_TURN
+#define FA_EARLY_TURN 0
+#endif
+#ifndef FA_LEAN
+#define FA_LEAN 1      // softmax warps skip the per-tile waits that other waits imply
+#endif
 
 struct FlashParams {
   int batch, Q, qtiles, qpairs, ktiles;
@@ -65,14 +81,6 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-#ifdef LF_FLASH_TRACE
-// Development aid, compiled only on request: clock stamps of CTA 0's first 24 tiles per stream.
-__device__ long long lf_flash_trace[24 * 4 * 10];
-#define FA_TRACE(stream_, tile_, ev_) \
-  do { if (blockIdx.x == 0 && (tile_) < 24u) lf_flash_trace[(((stream_) * 24 + (tile_)) * 10) + (ev_)] = clock64(); } while (0)
-#else
-#define FA_TRACE(stream_, tile_, ev_) do {} while (0)
-#endif
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -95,7 +103,8 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   uint64_t* o_full = p_full + 4;     // [issuer] one phase per key tile: P V of both streams has landed
   uint64_t* b_full = o_full + 2;     // [issuer][slot]
   uint64_t* b_empty = b_full + 2 * FA_BIAS_SLOTS;     // [issuer][slot]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_empty + 2 * FA_BIAS_SLOTS);
+  uint64_t* turn = b_empty + 2 * FA_BIAS_SLOTS;        // [query tile] count 8: the other tile's softmax warps are through their exponentials
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* mask_flag = abort_flag + 1;      // [stage]: the stage has a non-zero term
 
@@ -110,6 +119,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
     for (int i = 0; i < 4; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 8); }
     for (int i = 0; i < 2; ++i) mbar_init(&o_full[i], 1);
     for (int i = 0; i < 2 * FA_BIAS_SLOTS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(&turn[i], 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -126,6 +136,13 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The 16 softmax warps (warpgroups 0-3) hold a tile's logits and probabilities in registers; the
+  // producer and issuer warps (warpgroup 4) need few and hand theirs over.  Each role's code follows
+  // its own setmaxnreg, which is what the register allocator goes by.
+  if (warp >= 16) {
+#if FA_SETMAXNREG
+  reg_dec<FA_REGS_SERVICE>();
+#endif
   if (warp == 16) {
     // ---------------- TMA producer of Q, K, V + mask terms ----------------
     if (lane == 0) { prefetch_tensormap(&mapQ); prefetch_tensormap(&mapK); prefetch_tensormap(&mapV); }
@@ -263,7 +280,6 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
               umma_f16(d + kk * 16, adesc, ident_desc, idesc_b, 1);
             }
           }
-          FA_TRACE(w * 2 + h, u, 4);
         }
         if (has_bias) umma_commit(&b_empty[bs]);
         umma_commit(&s_full[w * 2 + (u & 1)]);
@@ -297,7 +313,6 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + st * FA_KV_BYTES);
         if (elect_one()) {
-          FA_TRACE(w * 2, u, 6);
           // P is the A operand straight from tensor memory: 16 keys per step = 8 packed columns.
           // The first tile of an item overwrites O: every softmax warp has read the previous item's
           // O before it wrote this P.
@@ -312,9 +327,8 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
               umma_f16_ts(d + FA_O_COL, pbuf + kk * 8, bdesc, idesc_pv, (pv_t != 0 || kk != 0) ? 1u : 0u);
             }
           }
-          umma_commit(&o_full[w]);
+          if (!FA_LEAN || pv_t + 1 == (uint32_t)T) umma_commit(&o_full[w]);     // lean: one phase per item
           umma_commit(&kv_empty[st]);      // this issuer's streams are done with the stage
-          FA_TRACE(w * 2, u, 5);
           if (more) qk_issue(u + 2);       // into the buffers these P V steps free
         }
         __syncwarp();
@@ -322,7 +336,11 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         if (++pv_t == (uint32_t)T) pv_t = 0;
       }
     }
+  }
   } else {
+#if FA_SETMAXNREG
+    reg_inc<FA_REGS_SOFTMAX>();
+#endif
     // ---------------- softmax: one thread per query row of one stream ----------------
     const int sidx = warp >> 2, q = warp & 3;
     const int g = sidx >> 1, h = sidx & 1;
@@ -330,7 +348,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
     const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + sidx * FA_TILE;
     const float L2E = 1.4426950408889634f;
     constexpr float kBig = 32768.0f;    // a piece whose 16 exponentials sum to at most this has every P < 2^15
-    uint32_t n_tile = 0;
+    uint32_t n_tile = 0, n_item = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const int hp = (int)(item & 1);
@@ -344,10 +362,10 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         const int st = n_tile % FA_STAGES;
         const uint32_t sbuf = acc + (n_tile & 1) * FA_KT;
         if (!mbar_wait(&s_full[g * 2 + (n_tile & 1)], (n_tile >> 1) & 1, abort_flag, p.status, 40)) { ok = false; break; }
-        // key terms of this stage were published through kv_full
-        if (!mbar_wait(&kv_full[st], (n_tile / FA_STAGES) & 1, abort_flag, p.status, 41)) { ok = false; break; }
+        // The key terms of this stage were published through kv_full, which the issuer waited for before
+        // it queued this S: S being there implies them.
+        if (!FA_LEAN && !mbar_wait(&kv_full[st], (n_tile / FA_STAGES) & 1, abort_flag, p.status, 41)) { ok = false; break; }
         tc_fence_after();
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 0);
         const bool masked = mask_flag[st] != 0;
         // The tile's 48 S columns go to registers; the three 16-key pieces are then independent chains
         // (mask terms, exponentials, sums) that the scheduler interleaves, and one vote per tile decides
@@ -404,13 +422,31 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           return ((ps[0] + ps[1]) + (ps[2] + ps[3])) + ((ps[4] + ps[5]) + (ps[6] + ps[7]));
         };
         load_s();
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 2);
         if (t == 0) {
           m_ref = fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)));   // key 0 exists, so this is finite
           neg = -m_ref * L2E;
         }
         uint32_t w0[8], w1[8], w2[8];
+#if FA_PINGPONG
+        if (!mbar_wait(&turn[g], (g ^ 1 ^ n_tile) & 1, abort_flag, p.status, 45)) { ok = false; break; }
+        tie48(s0, s1, s2);
+#endif
+#if FA_PINGPONG && FA_EARLY_TURN
+        // the turn is passed on before the last piece: the other tile's warps need about as long to
+        // wake up as this piece takes
+        float a0 = exponentials(s0, w0), a1 = exponentials(s1, w1);
+        tie16(w0, w1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&turn[g ^ 1]);
+        float a2 = exponentials(s2, w2);
+#else
         float a0 = exponentials(s0, w0), a1 = exponentials(s1, w1), a2 = exponentials(s2, w2);
+#if FA_PINGPONG
+        tie24(w0, w1, w2);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&turn[g ^ 1]);
+#endif
+#endif
         // The sum of a piece's 16 exponentials bounds each of them: while it stays below kBig every P is
         // far inside fp16 and the row reference is left alone (no maximum is searched at all).
         const bool over = !(a0 <= kBig) || !(a1 <= kBig) || !(a2 <= kBig);
@@ -421,7 +457,10 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           const float m_up = over ? fmaxf(m_ref, fmaxf(piece_max(s0), fmaxf(piece_max(s1), piece_max(s2)))) : m_ref;
           const float f = ex2f((m_ref - m_up) * L2E);       // 1 for the rows that are fine
           if (t > 0) {
-            if (!mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 43)) ok = false;
+            // P V of every earlier tile of the item has landed once both issuers have released the
+            // previous tile's K/V stage
+            if (FA_LEAN ? !mbar_wait(&kv_empty[(n_tile - 1) % FA_STAGES], ((n_tile - 1) / FA_STAGES) & 1, abort_flag, p.status, 43)
+                        : !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 43)) ok = false;
             tc_fence_after();
             if (ok) {
 #pragma unroll
@@ -443,28 +482,23 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           a2 = exponentials(s2, w2);
         }
         l_run += (a0 + a1) + a2;
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 3);
         tmem_st8(sbuf, w0);          // keys c*16 .. +15 -> columns c*8 .. +7
         tmem_st8(sbuf + 8, w1);
         tmem_st8(sbuf + 16, w2);
         if (!ok) break;
         tmem_st_wait();
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 7);
         // Stay within one phase of the "P V landed" barrier (a parity test cannot tell phases two apart).
         // This comes before the arrive below: once this warp has arrived, P V of this tile may land at
         // any time.  P V of the previous tile was queued a whole tile ago, so this rarely waits.
-        if (n_tile > 0 && !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 44)) { ok = false; break; }
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 8);
+        if (!FA_LEAN && n_tile > 0 && !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 44)) { ok = false; break; }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[g * 2 + (n_tile & 1)]);
-        if (q == 0 && lane == 0) FA_TRACE(sidx, n_tile, 1);
-        if (q == 3 && lane == 0) FA_TRACE(sidx, n_tile, 9);
-
       }
       if (!ok) break;
       // the item's last P V has landed: normalise, gate, store
-      if (!mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 42)) { ok = false; break; }
+      if (!mbar_wait(&o_full[g], FA_LEAN ? (n_item & 1) : ((n_tile - 1) & 1), abort_flag, p.status, 42)) { ok = false; break; }
+      ++n_item;
       tc_fence_after();
       {
         uint32_t o[32];
@@ -536,9 +570,3 @@ lf_status attention_core(lf_context* ctx, ArenaCursor& cur, const op16* q, const
 }
 
 }  // namespace tc
-
-#ifdef LF_FLASH_TRACE
-extern "C" __attribute__((visibility("default"))) int lf_debug_flash_trace(long long* host, int count) {
-  return (int)cudaMemcpyFromSymbol(host, tc::lf_flash_trace, sizeof(long long) * count);
-}
-#endif

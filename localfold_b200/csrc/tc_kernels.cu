@@ -367,6 +367,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// Kernel attributes belong to a device (context), the driver entry point to the process.
 void configure_once() {
   std::call_once(g_once, [] {
     void* fn = nullptr;
@@ -376,6 +377,11 @@ void configure_once() {
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     else
       cudaGetLastError();
+  });
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return; }
+  static std::once_flag per_device[64];
+  std::call_once(per_device[dev], [] {
     cudaFuncSetAttribute(contract_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
     configure_ln_gemm();

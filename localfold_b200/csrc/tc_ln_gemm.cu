@@ -97,14 +97,6 @@ __device__ __forceinline__ void tile_rows(const LnGemmParams& p, int64_t t, int6
   }
 }
 
-#ifdef LF_LG_TRACE
-// Development aid, compiled only on request: clock stamps of CTA 0's first 24 tiles.
-__device__ long long lf_lg_trace[24 * 16];
-#define LG_TRACE(tile_, ev_) \
-  do { if (EPI == 1 && blockIdx.x == 0 && (tile_) < 24) lf_lg_trace[(tile_) * 16 + (ev_)] = clock64(); } while (0)
-#else
-#define LG_TRACE(tile_, ev_) do {} while (0)
-#endif
 
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1)
@@ -179,7 +171,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
       const int s = it % NS;
       const uint32_t ph = (uint32_t)(it / NS) & 1u;
       if (!mbar_wait(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
-      if (pw == 0 && lane == 0) LG_TRACE(it, 0);
       uint8_t* tile = sA + s * LG_A_BYTES;
       int64_t row_base;
       int row_count;
@@ -243,10 +234,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
             for (int e = 0; e < 16; ++e) v[u][e] = 0.f;
           }
         }
-#ifdef LF_LG_TRACE
-        // the first value of the group has arrived
-        if (pw == 0 && lane == 0 && v[0][0] != 12345.678f) LG_TRACE(it, 12 + grp * 2);
-#endif
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
@@ -301,12 +288,10 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
                   make_uint2(packed[w4 * 2], packed[w4 * 2 + 1]);
           }
         }
-        if (pw == 0 && lane == 0) LG_TRACE(it, 13 + grp * 2);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[s]);
-      if (pw == 0 && lane == 0) LG_TRACE(it, 1);
       if (EPI == LG_EPI_TRI_OUT && pw < 4) {
         // statistics of the centre LayerNorm: one thread per pair reads its 128 channels from the
         // raw x tile (row h of the tile = 128 bytes of 64 pairs, 128-byte swizzled)
@@ -344,7 +329,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
         const uint32_t ph = (uint32_t)(it / NS) & 1u;
         if (!mbar_wait(&a_full[s], ph, abort_flag, p.status, 11)) break;
         tc_fence_after();
-        if (lane == 0) LG_TRACE(it, 2);
         const uint32_t a_addr = smem_u32(sA + s * LG_A_BYTES);
         bool ok = true;
         for (int j = 0; j < p.n_chunks; ++j, ++g) {
@@ -401,7 +385,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
             }
           }
           umma_commit(&acc_full[b]);
-          LG_TRACE(it, 3 + j);
           if (j == p.n_chunks - 1) umma_commit(&a_empty[s]);
           }
           __syncwarp();
@@ -451,7 +434,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
         const int b = g & 1;
         if (!mbar_wait(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
         tc_fence_after();
-        if (warp == 0 && lane == 0) LG_TRACE(it, 6 + j);
         const uint32_t acc = tmem_base + lane_addr + b * 256;
         if (EPI == LG_EPI_TRIANGLE) {
           // TMEM lane = hidden channel h, columns = the tile's pair rows (projection at 0..127,
@@ -680,7 +662,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[b]);
-        if (warp == 0 && lane == 0) LG_TRACE(it, 9 + j);
       }
     }
   }
@@ -834,9 +815,3 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
 }
 
 }  // namespace tc
-
-#ifdef LF_LG_TRACE
-extern "C" __attribute__((visibility("default"))) int lf_debug_lg_trace(long long* host, int count) {
-  return (int)cudaMemcpyFromSymbol(host, tc::lf_lg_trace, sizeof(long long) * count);
-}
-#endif

@@ -63,14 +63,32 @@ class Device:
     ``createNodeDevice``: ``webgpu/node.js:51-81``)."""
 
     def __init__(self, ordinal: int = 0, stream: int | None = None):
+        """``stream``: None - the context makes a stream of its own; an integer - that ``cudaStream_t``
+        (0 is CUDA's default stream).  Every call enqueues on that stream and returns without waiting, so
+        a device-tensor ``output`` is ready only after ``synchronize()`` or for work enqueued on the
+        same stream (``stream`` gives its handle); work on other streams is not ordered with it."""
         self.lib = nat.load()
         handle = ctypes.c_void_p()
-        status = self.lib.lf_context_create(int(ordinal), ctypes.c_void_p(stream or 0), ctypes.byref(handle))
+        if stream is None:
+            status = self.lib.lf_context_create(int(ordinal), None, ctypes.byref(handle))
+        else:
+            status = self.lib.lf_context_create_on_stream(int(ordinal), ctypes.c_void_p(int(stream)), ctypes.byref(handle))
         if status != nat.LF_OK:
             raise nat.NativeError(f"lf_context_create({ordinal}) failed with status {status}: no usable CUDA device")
         self.handle = handle
         self.ordinal = ordinal
+        self.stream = int(self.lib.lf_context_stream(handle) or 0)
         self._finalizer = weakref.finalize(self, self.lib.lf_context_destroy, handle)
+
+    def require_current_stream(self, what):
+        """Raises unless torch's current stream on this device is the context's stream: collectives and
+        tensor operations that ``what`` mixes with library calls are ordered only on one stream."""
+        import torch
+        current = int(torch.cuda.current_stream(self.ordinal).cuda_stream)
+        if current != self.stream:
+            raise RuntimeError(f"{what}: torch's current stream ({current:#x}) is not the library context's stream "
+                               f"({self.stream:#x}); create the Device on torch's stream (Device(ordinal, stream="
+                               f"torch.cuda.current_stream().cuda_stream)) or make that stream current")
 
     def check(self, status):
         nat.check(self.lib, self.handle, status)

@@ -133,6 +133,7 @@ class PeerTranspose:
         import torch
         import torch.distributed as dist
         self.torch, self.dist, self.group, self.dev = torch, dist, group, device
+        device.require_current_stream("PeerTranspose")
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.R, self.N = int(rows), int(length)
         if self.R * self.world != self.N:
@@ -193,6 +194,7 @@ class PeerTranspose:
         """z must be `shard()`.  Returns the other buffer, holding this rank's rows of the transposed pair."""
         if z.data_ptr() != self.local[self.current]:
             raise ValueError("the pair shard must live in the buffer shard() returned")
+        self.dev.require_current_stream("PeerTranspose.transpose")     # the barrier below orders one stream only
         other = 1 - self.current
         dst = (ctypes.c_void_p * self.world)(*self.mapped[other])
         self.dev.check(self.dev.lib.lf_pair_transpose_scatter(self.dev.handle, self.local[self.current], self.R, self.N,
@@ -276,6 +278,8 @@ class GpuShardOps:
         import torch
         self.torch = torch
         self.dev = device
+        # the collectives and tensor operations between the steps run on torch's current stream
+        device.require_current_stream("GpuShardOps")
         self.R, self.N, self.G = int(rows), int(length), int(ranks)
         self.ld = (self.N + 15) // 16 * 16
         self.variance = nat.VARIANCE_TWO_PASS if variance == "two-pass" else nat.VARIANCE_FAST
@@ -291,6 +295,7 @@ class GpuShardOps:
         self.bias = torch.zeros((4, R, ld), **f16)
 
     def _step(self, op, w, pair=None, mask=None, bufs=(), chunk=0):
+        self.dev.require_current_stream("GpuShardOps")
         d = nat.ShardStepDesc()
         d.op, d.rows, d.length, d.ranks, d.chunk = op, self.R, self.N, self.G, chunk
         d.variance, d.epsilon = self.variance, self.eps

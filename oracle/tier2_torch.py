@@ -189,3 +189,73 @@ def af3_pair_block(pair, mask, w, swap):
     pair = pair + grid_attention_af3(pair, mask, w["pairAttention1"], False, swap)
     pair = pair + grid_attention_af3(pair, mask, w["pairAttention2"], True, swap)
     return pair + transition_af3(pair, w["pairTransition"])
+
+
+# --------------------------------------------------------------------------
+# Sampled positions of full-size results.  The operators below compute, in float64, only the output
+# positions asked for, reading from the full input just what those positions depend on; they serve as
+# the checker at lengths where a whole-tensor oracle would take minutes (N = 1024, 2048).
+
+
+def trimul_af2_positions(z, mask, w, rows, cols, eps=1e-5, incoming=False):
+    """``trimul_af2(...)[rows][:, cols]``: the update at output positions (i, j), i in ``rows``, j in
+    ``cols``.  Outgoing x[i, j] = sum_k a[i, k] b[j, k] needs pair rows ``rows`` (for a) and ``cols``
+    (for b); incoming x[i, j] = sum_k a[k, j] b[k, i] needs pair columns ``cols`` (a) and ``rows`` (b)."""
+    z = np.asarray(z)
+    mask = np.asarray(mask)
+    rows, cols = np.asarray(rows), np.asarray(cols)
+
+    def operand(index, key):
+        if incoming:      # [k, index]: columns of the pair -> logical [index, k]
+            zz, mm = T(z[:, index]).transpose(0, 1), T(mask[:, index]).transpose(0, 1)
+        else:
+            zz, mm = T(z[index]), T(mask[index])
+        zn = ln(zz, w["layerNormInWeight"], w["layerNormInBias"], eps)
+        lin = lambda k: zn @ T(w[f"linear{k}Weight"]).T + T(w[f"linear{k}Bias"])
+        return lin(key + "P") * torch.sigmoid(lin(key + "G")) * mm[..., None]
+
+    if incoming:
+        a = operand(cols, "A")     # a[j, k] = a_mem[k, j]
+        b = operand(rows, "B")     # b[i, k] = b_mem[k, i]
+        x = torch.einsum("jkc,ikc->ijc", a, b)
+    else:
+        a = operand(rows, "A")
+        b = operand(cols, "B")
+        x = torch.einsum("ikc,jkc->ijc", a, b)
+    xn = ln(x, w["layerNormOutWeight"], w["layerNormOutBias"], eps)
+    zn = ln(T(z[np.ix_(rows, cols)]), w["layerNormInWeight"], w["layerNormInBias"], eps)
+    gate = torch.sigmoid(zn @ T(w["linearGWeight"]).T + T(w["linearGBias"]))
+    return ((xn @ T(w["linearZWeight"]).T + T(w["linearZBias"])) * gate).numpy()
+
+
+def attention_af2_positions(act, mask, n, c, heads, w, batch_rows, queries, transpose, pair_bias_weight, eps=1e-5):
+    """Triangle attention (batch = queries = n, pair bias from the normalised input) at output positions
+    (b, q), b in ``batch_rows``, q in ``queries`` of the logical (attention) orientation; returns
+    [len(batch_rows), len(queries), c].  With ``transpose`` the logical element (b, q) is memory (q, b)."""
+    z = np.asarray(act).reshape(n, n, c)
+    m = np.asarray(mask).reshape(n, n)
+    batch_rows, queries = np.asarray(batch_rows), np.asarray(queries)
+    if transpose:
+        x = T(z[:, batch_rows]).transpose(0, 1)           # [B, n, c]: logical rows b
+        mm = T(m[:, batch_rows]).transpose(0, 1)
+        xq = T(z[:, queries]).transpose(0, 1)             # logical rows q (for the bias): [Q, n, c]
+    else:
+        x = T(z[batch_rows])
+        mm = T(m[batch_rows])
+        xq = T(z[queries])
+    nx = ln(x, w["queryNormScale"], w["queryNormOffset"], eps)
+    q = nx[:, queries] @ T(w["queryWeight"])
+    k, v = nx @ T(w["keyWeight"]), nx @ T(w["valueWeight"])
+    g = torch.sigmoid(nx[:, queries] @ T(w["gatingWeight"]) + T(w["gatingBias"]))
+    # bias[h, q, k] = LN(logical z)[q, k] . W
+    bias = (ln(xq, w["queryNormScale"], w["queryNormOffset"], eps) @ T(pair_bias_weight)).permute(2, 0, 1)   # [H, Q, n]
+    B, Q = len(batch_rows), len(queries)
+    d = c // heads
+    qh = q.view(B, Q, heads, d).permute(0, 2, 1, 3)
+    kh = k.view(B, n, heads, d).permute(0, 2, 1, 3)
+    vh = v.view(B, n, heads, d).permute(0, 2, 1, 3)
+    logits = qh @ kh.transpose(-1, -2) / np.sqrt(d) + bias[None] + (1e9 * (mm - 1.0))[:, None, None, :]
+    logits = logits.clamp(-1e8, 1e8)
+    p = torch.softmax(logits.to(torch.float32).to(F64), -1)
+    o = (p @ vh).permute(0, 2, 1, 3).reshape(B, Q, c) * g
+    return (o @ T(w["outputWeight"]) + T(w["outputBias"])).numpy()

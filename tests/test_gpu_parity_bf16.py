@@ -3,7 +3,7 @@
 Tolerances: per operator 8e-3 relative L2 (the reference's bound for its
 half-precision arms: ``tools/gpu/check-evoformer-attention.js:162``,
 ``tools/gpu/check-triangle.js:59``); per block 2e-3 on the block's output pair,
-the bound this library is specified to.  Masked positions must stay exact.
+the bound this library is specified to.
 """
 import numpy as np
 import pytest
@@ -169,10 +169,10 @@ def test_af3_pairformer_block_bf16_int5_weights(dev):
     """BASELINE config 2 shape at reduced N: AF3 pairformer blocks whose linear weights went through the
     int5 bundle format (quantised and decoded identically for the oracle and the GPU)."""
     import localfold_b200 as lf
-    from localfold_b200 import bundle
+    from bundle_writer import quantise_weights_like_bundle
     n = 96
     pair, single, pair_mask, seq_mask, blocks = syn.af3_pairformer(2, n, 128, 384, blocks=1)
-    blocks = [bundle.quantise_weights_like_bundle(b) for b in blocks]
+    blocks = [quantise_weights_like_bundle(b) for b in blocks]
     wp, ws = oracle.af3_pairformer_block(pair, single, pair_mask, seq_mask, blocks[0], True)
     got = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
                                              "tokens": n}, blocks, {"swapTransposedBias": True}, {"precision": "bf16"})

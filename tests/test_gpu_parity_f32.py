@@ -42,7 +42,7 @@ def test_triangle_outgoing_golden(dev, golden_dir, name, mean_bound, max_bound):
     assert got["launches"] > 0
 
 
-@pytest.mark.parametrize("n,cz,c", [(37, 128, 128), (16, 24, 40), (5, 7, 6)])
+@pytest.mark.parametrize("n,cz,c", [(37, 128, 128), (16, 24, 40), (5, 7, 6), (9, 64, 512)])      # 512: the widest cHidden accepted
 @pytest.mark.parametrize("incoming", [False, True])
 def test_triangle_af2_ragged(dev, n, cz, c, incoming):
     import localfold_b200 as lf

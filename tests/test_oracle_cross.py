@@ -190,3 +190,23 @@ def test_thread_count_does_not_change_results():
     oracle.set_threads(oracle.max_threads())
     b = oracle.af2_pair_block(pair, mask, weights[0], 16)
     np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("flag", [False, True])
+def test_sampled_positions_match_the_whole_tensor(flag):
+    """The float64 sampled-position forms used at the benchmark's lengths equal the C restatement's
+    whole-tensor results at those positions (triangle: flag = incoming; attention: flag = transpose)."""
+    d = syn.draw(9)
+    n = 37
+    z = d.normal(n, n, 128)
+    mask = syn.residue_pair_mask(n, 0.1)
+    rows, cols = np.array([0, 5, 36, 20]), np.array([3, 4, 35, 1, 2])
+    w = syn.af2_triangle_weights(d, 128, 128)
+    full = oracle.trimul_af2(z, mask, w, 128, 1e-5, flag)
+    assert rel(t2.trimul_af2_positions(z, mask, w, rows, cols, 1e-5, flag), full[np.ix_(rows, cols)]) < TOL
+    t = syn.af2_attention_weights(d, 128, 4, 128)
+    pb = dict(t["pairBias"], source="normalized-input")
+    full = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], flag, pb)
+    ref = full[np.ix_(cols, rows)].transpose(1, 0, 2) if flag else full[np.ix_(rows, cols)]
+    got = t2.attention_af2_positions(z, mask, n, 128, 4, t["attention"], rows, cols, flag, pb["projectionWeight"])
+    assert rel(got, ref) < TOL

@@ -16,9 +16,10 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _desc(nat, n, incoming, z, mask, out, weights):
-    return nat.TriangleDesc(n, 128, 128, 1 if incoming else 0, nat.VARIANCE_TWO_PASS, nat.PRECISION_BF16, 0, 0, 1e-5,
-                            nat.SPACE_DEVICE, nat.DTYPE_F32, z.data_ptr(), mask.data_ptr(), out.data_ptr(), weights.handle)
+def _desc(nat, n, incoming, z, mask, out, weights, residual=0, dtype=None):
+    dtype = nat.DTYPE_F32 if dtype is None else dtype
+    return nat.TriangleDesc(n, 128, 128, 1 if incoming else 0, nat.VARIANCE_TWO_PASS, nat.PRECISION_BF16, residual, 0, 1e-5,
+                            nat.SPACE_DEVICE, dtype, z.data_ptr(), mask.data_ptr(), out.data_ptr(), weights.handle)
 
 
 @pytest.mark.parametrize("n,incoming", [(96, False), (128, True), (75, False)])
@@ -52,6 +53,40 @@ def test_static_entry_point_matches_regular_one_twice(n, incoming):
         np.testing.assert_array_equal(a, b)
         results.append(a)
     assert not np.array_equal(results[0], results[1])
+    weights.close()
+    dev.close()
+
+
+@pytest.mark.parametrize("bf16_pair", [False, True])
+def test_static_entry_point_in_place_residual_form(bf16_pair):
+    """The form the block runners use - the update added into z, which is also the output buffer - with a
+    float32 and with a bf16 pair tensor, bit for bit against the regular entry point, twice in a row."""
+    import torch
+    import localfold_b200 as lf
+    from localfold_b200 import _native as nat, synthetic as syn
+    from localfold_b200.operators import prepare_triangle_weights
+
+    dev = lf.Device(0)
+    n = 112
+    d = syn.draw(950)
+    weights = prepare_triangle_weights(dev, syn.af2_triangle_weights(d, 128, 128), 128, 128)
+    dtype = nat.DTYPE_BF16 if bf16_pair else nat.DTYPE_F32
+    for call in range(2):
+        z0 = torch.from_numpy(d.normal(n, n, 128)).cuda()
+        if bf16_pair:
+            z0 = z0.to(torch.bfloat16)
+        mask = torch.from_numpy(syn.residue_pair_mask(n, 0.1)).cuda()
+        want, got = z0.clone(), z0.clone()
+        res = nat.Result()
+        dev.check(dev.lib.lf_triangle_multiplication_run(dev.handle, ctypes.byref(_desc(nat, n, call == 1, want, mask, want, weights, 1, dtype)),
+                                                         ctypes.byref(res)))
+        dev.synchronize()
+        dev.check(dev.lib.lf_triangle_multiplication_run_static(dev.handle, ctypes.byref(_desc(nat, n, call == 1, got, mask, got, weights, 1, dtype)),
+                                                                ctypes.byref(res)))
+        dev.synchronize()
+        assert bool(torch.isfinite(got.float()).all())
+        assert not torch.equal(got, z0)                 # the update was added
+        assert torch.equal(got, want)
     weights.close()
     dev.close()
 
