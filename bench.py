@@ -244,9 +244,12 @@ def workload_config(args, n_gpus):
                         f"tri-attention 4x32, transition 4x, seed 4, mask ones (BASELINE config 4 shape)",
             "length": args.length, "precision": args.precision, "pair_dtype": args.pair_dtype,
             "parallelism": "single GPU" if n_gpus == 1 else
-            f"pair rows sharded over {n_gpus} GPUs (NCCL all-gather of the triangle operand b and of the pair bias; "
-            f"4 transposes per block by " + ("one peer-store kernel each over NVLink" if args.transpose == "peer"
-                                            else "NCCL all-to-all") + ")",
+            (f"pair rows sharded over {n_gpus} GPUs; triangle multiplication channel-sharded, its operands, product and the pair "
+             f"bias stored into the peers' memory by the producing kernels over NVLink; 2 transposes per block by one peer-store "
+             f"kernel each" if args.trimul == "channel" and args.transpose == "peer" else
+             f"pair rows sharded over {n_gpus} GPUs (NCCL all-gather of the triangle operand b and of the pair bias; "
+             f"4 transposes per block by " + ("one peer-store kernel each over NVLink" if args.transpose == "peer"
+                                             else "NCCL all-to-all") + ")"),
             "l2": "inputs larger than L2 (pair tensor %.0f MiB)" % (args.length ** 2 * C_Z * (2 if args.pair_dtype == "bf16" else 4) / 2 ** 20)}
 
 
@@ -264,6 +267,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-n384", action="store_true", help="skip the N = 384 leg")
+    ap.add_argument("--trimul", default="channel", choices=["channel", "rows"],
+                    help="N > 1: triangle multiplication channel-sharded with the exchange fused into the kernels (peer stores), "
+                         "or row-sharded with an NCCL all-gather of the operand b")
     ap.add_argument("--transpose", default="peer", choices=["peer", "nccl"],
                     help="N > 1: transposes of the sharded pair by peer stores (one kernel) or by NCCL all-to-all")
     args = ap.parse_args()
@@ -305,8 +311,8 @@ def main():
             stack.run(pair_d, mask_d, opts, first_block=i % 2, n_blocks=1)
     else:
         # strong scaling: the same block, pair rows sharded over the ranks
-        from localfold_b200.sharded import (GpuShardOps, PeerTranspose, ShardedPairStack, TorchComm, prepared_block_weights,
-                                            shard_rows)
+        from localfold_b200.sharded import (GpuShardOps, PeerExchange, PeerTranspose, ShardedPairStack, TorchComm,
+                                            prepared_block_weights, shard_rows)
         if n % (16 * world):
             raise SystemExit(f"--length {n} must be a multiple of 16 x {world} ranks")
         pair_h, mask_h, weights = syn.af2_pair_block(4, n, blocks=2)
@@ -337,12 +343,23 @@ def main():
                 holder = {"z": torch.from_numpy(local).cuda().to(pair_dtype)}
             m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(full_mask, rank, world))).cuda()
             m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(full_mask.T), rank, world))).cuda()
-            runner = ShardedPairStack(TorchComm(), GpuShardOps(dev, rows, length, world), transposer)
-            return holder, m_rows, m_t_rows, runner, transposer, local
+            exchange = None
+            if args.trimul == "channel" and transposer is None:
+                args.trimul = "rows"
+            if args.trimul == "channel":    # the fused exchange needs the same peer mappings
+                try:
+                    exchange = PeerExchange(dev, None, rows, length)
+                except Exception as exc:    # raised on every rank together (the ranks agree inside)
+                    print(f"rank {rank}: fused exchange unavailable ({exc}); row-sharded triangle multiplication", file=sys.stderr)
+                    args.trimul = "rows"
+            runner = ShardedPairStack(TorchComm(), GpuShardOps(dev, rows, length, world), transposer, exchange)
+            return holder, m_rows, m_t_rows, runner, (transposer, exchange), local
 
         # Numerical check of the path that is about to be timed (NCCL gathers, peer-store transposes): one
         # block at a small length, every rank's shard against the same block run unsharded on this GPU.
-        check_n = 16 * world * max(1, 256 // (16 * world))
+        if args.trimul == "channel" and (128 % world or (n // world) % 128):
+            args.trimul = "rows"
+        check_n = 128 * world if args.trimul == "channel" else 16 * world * max(1, 256 // (16 * world))
         small_pair, small_mask, _ = syn.af2_pair_block(5, check_n, masked_tail=0.05)
         holder, m_rows, m_t_rows, runner, tr, _ = build(check_n, small_pair, small_mask)
         holder["z"] = runner.block(holder["z"], m_rows, m_t_rows, block_w[0])
@@ -357,8 +374,9 @@ def main():
         dist.all_reduce(both)
         sharded_check = {"length": check_n, "rel_l2_vs_unsharded": float(torch.sqrt(both[0] / both[1]).item()),
                          "what": "one sharded block (NCCL gathers, transposes as timed) against the same block on one GPU"}
-        if tr is not None:
-            tr.close()
+        for part in tr:
+            if part is not None:
+                part.close()
         del holder, runner
 
         shard, m_rows, m_t_rows, sharded, transposer, pair_h = build(n, pair_h, mask_h)

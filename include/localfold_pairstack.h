@@ -375,6 +375,38 @@ typedef struct lf_shard_step_desc {
 LF_API lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_result* r);
 
 /* ------------------------------------------------------------------------------------------
+ * The same steps with the exchange between the GPUs of one box fused into the kernels that produce
+ * the data (plain stores into the peers' memory over NVLink; buffers shared as for the transpose
+ * below).  The reference is single-device: no counterpart there.
+ *
+ * Triangle multiplication, channel-sharded: rank g contracts channels [g c, (g+1) c), c = 128 / ranks,
+ * over the whole N x N plane, so every tile of the contraction is full-size and neither direction
+ * needs a transposed pair.
+ *   TRIANGLE_PROJECT   the epilogue of the LayerNorm + projection kernel stores channel h of this
+ *                      shard's rows into a[h / c], b[h / c] (rank h / c's [c][length][ld] buffers) at
+ *                      rows rank*rows ..: 7/8 of the operands leave over NVLink while the kernel runs
+ *   TRIANGLE_CONTRACT  a[rank], b[rank] (complete after a barrier of the caller's) -> rows i of
+ *                      the product of channel h go to x[i / rows] (rank i / rows's [128][rows][ld] buffer)
+ *                      at channel rank*c + h; `incoming` picks the form
+ *   ATTENTION_PROJECT  buf0..3 = q, k, v, gate as for lf_pair_shard_step; the shard's pair-bias rows are
+ *                      stored into every bias[g] ([4][length][ld], all query rows) at rows rank*rows ..
+ * After each step the caller runs a barrier on the same stream (e.g. a one-element NCCL all-reduce):
+ * when it has passed on a rank, every peer's stores into that rank's buffers have landed.  The
+ * remaining steps (TRIANGLE_OUTPUT on x[rank], ATTENTION_CORE on bias[rank], ...) are lf_pair_shard_step's.
+ * length must be a multiple of 16 and rows a multiple of 128; 128 % ranks == 0.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct lf_shard_peers {
+  int32_t rank;          /* this rank */
+  int32_t incoming;      /* TRIANGLE_CONTRACT: 0 outgoing, 1 incoming */
+  void* a[16];           /* per rank, as mapped in this process (entry `rank` is the local buffer) */
+  void* b[16];
+  void* x[16];
+  void* bias[16];
+} lf_shard_peers;
+LF_API lf_status lf_pair_shard_exchange_step(lf_context* ctx, const lf_shard_step_desc* d, const lf_shard_peers* peers,
+                                             lf_result* r);
+
+/* ------------------------------------------------------------------------------------------
  * Transpose of the row-sharded pair across the GPUs of one box, written directly into the
  * peers' memory.  The reference is single-device: no counterpart there.
  *

@@ -103,13 +103,18 @@ class ShardStepDesc(ctypes.Structure):
                 ("mask", c_void_p), ("buf", c_void_p * 6), ("weights", c_void_p)]
 
 
+class ShardPeers(ctypes.Structure):
+    _fields_ = [("rank", c_int32), ("incoming", c_int32), ("a", c_void_p * 16), ("b", c_void_p * 16),
+                ("x", c_void_p * 16), ("bias", c_void_p * 16)]
+
+
 EXPORTS = (
     "lf_version", "lf_context_create", "lf_context_create_on_stream", "lf_context_stream", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
     "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
-    "lf_pair_shard_step", "lf_peer_buffer_create", "lf_peer_buffer_open", "lf_peer_buffer_close",
+    "lf_pair_shard_step", "lf_pair_shard_exchange_step", "lf_peer_buffer_create", "lf_peer_buffer_open", "lf_peer_buffer_close",
     "lf_peer_buffer_destroy", "lf_pair_transpose_scatter",
 )
 
@@ -155,6 +160,8 @@ def load():
                        ("lf_single_attention_run", SingleAttentionDesc), ("lf_pair_stack_run", PairStackDesc),
                        ("lf_pair_shard_step", ShardStepDesc)):
         getattr(lib, name).argtypes = [c_void_p, ctypes.POINTER(desc), ctypes.POINTER(Result)]
+    lib.lf_pair_shard_exchange_step.argtypes = [c_void_p, ctypes.POINTER(ShardStepDesc), ctypes.POINTER(ShardPeers),
+                                                ctypes.POINTER(Result)]
     lib.lf_peer_buffer_create.argtypes = [c_void_p, ctypes.c_size_t, ctypes.POINTER(c_void_p), ctypes.c_char_p]
     lib.lf_peer_buffer_open.argtypes = [c_void_p, ctypes.c_char_p, ctypes.POINTER(c_void_p)]
     lib.lf_peer_buffer_close.argtypes = [c_void_p, c_void_p]

@@ -1075,6 +1075,72 @@ lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_re
   return LF_OK;
 }
 
+lf_status lf_pair_shard_exchange_step(lf_context* ctx, const lf_shard_step_desc* d, const lf_shard_peers* peers, lf_result* r) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!d || !d->weights || !peers) return lf_fail(ctx, LF_ERR_ARGUMENT, "exchange step: null argument");
+  if (d->rows <= 0 || d->length <= 0 || d->ranks <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "shard dimensions must be positive safe integers");
+  if (d->ranks > tc::kMaxPeers || 128 % d->ranks != 0) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "exchange step: %d ranks do not divide 128 channels", d->ranks);
+  if (peers->rank < 0 || peers->rank >= d->ranks) return lf_fail(ctx, LF_ERR_ARGUMENT, "exchange step: rank %d of %d", peers->rank, d->ranks);
+  if ((int64_t)d->rows * d->ranks != d->length) return lf_fail(ctx, LF_ERR_SHAPE, "exchange step: rows %d x ranks %d must equal length %d", d->rows, d->ranks, d->length);
+  if (d->length % 16 != 0 || (d->ranks > 1 && d->rows % 128 != 0))
+    return lf_fail(ctx, LF_ERR_UNSUPPORTED, "exchange step: length must be a multiple of 16 and rows a multiple of 128; received %d, %d", d->length, d->rows);
+  if (d->act_dtype != LF_DTYPE_F32 && d->act_dtype != LF_DTYPE_BF16) return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown activation dtype %d", d->act_dtype);
+  const lf_weights* w = d->weights;
+  const int R = d->rows, n = d->length, ld = n, G = d->ranks, rank = peers->rank, cpr = 128 / G;
+  auto table = [&](void* const* src, tc::PeerPtrs& out, const char* name) -> lf_status {
+    for (int g = 0; g < G; ++g) {
+      if (!src[g]) return lf_fail(ctx, LF_ERR_ARGUMENT, "exchange step: %s buffer of rank %d is null", name, g);
+      out.p[g] = src[g];
+    }
+    return LF_OK;
+  };
+  cudaSetDevice(ctx->device);
+  const uint64_t before = ctx->launches;
+  ArenaCursor cur{ctx, 0, false};
+  const float xscale = ldexpf(1.0f, -(int)(0.5f * log2f((float)n)));
+  lf_status s = LF_OK;
+  switch (d->op) {
+    case LF_SHARD_TRIANGLE_PROJECT: {
+      if (!((w->kind == LF_WEIGHTS_TRIANGLE_AF2 || w->kind == LF_WEIGHTS_TRIANGLE_AF3) && tc::ln_gemm_supported(w)))
+        return lf_fail(ctx, LF_ERR_UNSUPPORTED, "exchange step needs triangle weights with cZ = cHidden = 128");
+      if (d->variance != LF_VARIANCE_TWO_PASS && d->variance != LF_VARIANCE_FAST)
+        return lf_fail(ctx, LF_ERR_ARGUMENT, "variance has no default: pass LF_VARIANCE_TWO_PASS or LF_VARIANCE_FAST");
+      if (!d->pair || !d->mask) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle project: null buffer");
+      tc::PeerPtrs pa{}, pb{};
+      LF_TRY(table(peers->a, pa, "a"));
+      LF_TRY(table(peers->b, pb, "b"));
+      s = tc::triangle_project_scatter(ctx, cur, d->pair, d->act_dtype, d->mask, R, n, ld, d->variance, d->epsilon, w, pa, pb, G, rank * R);
+      break;
+    }
+    case LF_SHARD_TRIANGLE_CONTRACT: {
+      tc::PeerPtrs px{};
+      LF_TRY(table(peers->x, px, "x"));
+      if (!peers->a[rank] || !peers->b[rank]) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle contract: null operand buffer");
+      s = tc::contract_scatter(ctx, cur, (const op16*)peers->a[rank], (const op16*)peers->b[rank], n, ld, cpr, peers->incoming ? 1 : 0,
+                               xscale, px, R, 128, rank * cpr);
+      break;
+    }
+    case LF_SHARD_ATTENTION_PROJECT: {
+      if (!(w->kind == LF_WEIGHTS_ATTENTION_AF2 && tc::ln_gemm_supported(w) && w->dims.heads == 4 && w->has_pair_proj && !w->has_pair_norm))
+        return lf_fail(ctx, LF_ERR_UNSUPPORTED, "exchange step needs AF2 attention weights: 128 channels, 4 heads, normalized-input pair bias");
+      if (d->variance != LF_VARIANCE_TWO_PASS && d->variance != LF_VARIANCE_FAST)
+        return lf_fail(ctx, LF_ERR_ARGUMENT, "variance has no default: pass LF_VARIANCE_TWO_PASS or LF_VARIANCE_FAST");
+      op16** b = (op16**)d->buf;
+      if (!d->pair || !b[0] || !b[1] || !b[2] || !b[3]) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention project: null buffer");
+      tc::PeerPtrs pbias{};
+      LF_TRY(table(peers->bias, pbias, "bias"));
+      s = tc::attention_project_scatter(ctx, cur, d->pair, d->act_dtype, R, n, d->variance, d->epsilon, 4, w, b[0], b[1], b[2], b[3],
+                                        pbias, G, n, rank * R, ld);
+      break;
+    }
+    default: return lf_fail(ctx, LF_ERR_ARGUMENT, "exchange step: step %d has no exchange form", d->op);
+  }
+  if (s != LF_OK) return s;
+  LF_CUDA(ctx, cudaGetLastError());
+  if (r) { r->elapsed_ms = 0.f; r->peak_bytes = ctx->arena_peak; r->launches = (uint32_t)(ctx->launches - before); }
+  return LF_OK;
+}
+
 lf_status lf_int5_decode(lf_context* ctx, const uint8_t* payload, uint64_t payload_bytes, uint64_t scale_offset,
                          uint64_t zero_offset, int64_t elements, int32_t block, lf_space out_space, float* out) {
   if (!ctx) return LF_ERR_ARGUMENT;

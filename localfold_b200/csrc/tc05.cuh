@@ -275,13 +275,6 @@ __device__ __forceinline__ void tie24(uint32_t (&a)[8], uint32_t (&b)[8], uint32
                :
                : "memory");
 }
-__device__ __forceinline__ void tie16(uint32_t (&a)[8], uint32_t (&b)[8]) {
-  asm volatile(""
-               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(b[0]),
-                 "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
-               :
-               : "memory");
-}
 // Register hand-over between warpgroups (every warp of a warpgroup executes the same instruction).
 template <uint32_t R>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R)); }

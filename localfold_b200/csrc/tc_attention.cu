@@ -22,6 +22,14 @@
 // into the buffer P V frees, S of tile u+2 (the tensor pipe keeps their order).  The N x N x N
 // logits and probabilities never exist outside tensor memory.
 //
+// What bounds the kernel is the softmax warps' per-tile chain, not a pipe: every shared-memory or
+// tensor-memory round trip in it (barrier test, tcgen05.ld / st, wait) queues behind the exponentials
+// the other warps have in flight.  So the chain is kept to the waits it cannot do without ("S is
+// there" implies the K/V stage and its mask terms; "P V landed" is waited once per item), and the two
+// query tiles take turns at the exponentials so that one pair of streams computes while the other
+// stores and loads.  Computing part of the exponentials on the FMA pipe (a polynomial 2^x) was
+// measured and is slower: the kernel is short of issue slots before it is short of the exponent unit.
+//
 // Warp roles: warp w < 16: softmax of stream w / 4 (TMEM lane quadrant = w % 4); 16: TMA producer
 // of Q, K, V and the mask terms; 17 / 18: MMA issuers of streams 0-1 / 2-3, each handling its two
 // streams together (17 owns the TMEM allocation); 19: TMA producer of the bias tiles (one ring
@@ -50,19 +58,6 @@ constexpr int FA_SMEM = 2 * FA_Q_BYTES + FA_STAGES * 2 * FA_KV_BYTES + 2 * FA_BI
 // own allocation: 16 softmax warps x 104 + 4 service warps x 64 = 20 x 96.
 constexpr uint32_t FA_REGS_SOFTMAX = 104, FA_REGS_SERVICE = 64;
 constexpr int FA_O_COL = 2 * FA_KT;                 // O accumulator columns inside a stream's region, after the two S / P buffers
-
-#ifndef FA_SETMAXNREG
-#define FA_SETMAXNREG 1
-#endif
-#ifndef FA_PINGPONG
-#define FA_PINGPONG 1  // the two query tiles take turns at the exponentials
-#endif
-#ifndef FA_EARLY_TURN
-#define FA_EARLY_TURN 0
-#endif
-#ifndef FA_LEAN
-#define FA_LEAN 1      // softmax warps skip the per-tile waits that other waits imply
-#endif
 
 struct FlashParams {
   int batch, Q, qtiles, qpairs, ktiles;
@@ -100,7 +95,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   uint64_t* kv_empty = kv_full + FA_STAGES;     // [stage] count 2: one commit per issuer
   uint64_t* s_full = kv_empty + FA_STAGES;      // [issuer][buffer]: S of both its streams is there
   uint64_t* p_full = s_full + 4;     // [issuer][buffer] count 8: the eight softmax warps of its two streams
-  uint64_t* o_full = p_full + 4;     // [issuer] one phase per key tile: P V of both streams has landed
+  uint64_t* o_full = p_full + 4;     // [issuer] one phase per item: the last P V of both streams has landed
   uint64_t* b_full = o_full + 2;     // [issuer][slot]
   uint64_t* b_empty = b_full + 2 * FA_BIAS_SLOTS;     // [issuer][slot]
   uint64_t* turn = b_empty + 2 * FA_BIAS_SLOTS;        // [query tile] count 8: the other tile's softmax warps are through their exponentials
@@ -140,9 +135,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
   // producer and issuer warps (warpgroup 4) need few and hand theirs over.  Each role's code follows
   // its own setmaxnreg, which is what the register allocator goes by.
   if (warp >= 16) {
-#if FA_SETMAXNREG
   reg_dec<FA_REGS_SERVICE>();
-#endif
   if (warp == 16) {
     // ---------------- TMA producer of Q, K, V + mask terms ----------------
     if (lane == 0) { prefetch_tensormap(&mapQ); prefetch_tensormap(&mapK); prefetch_tensormap(&mapV); }
@@ -327,7 +320,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
               umma_f16_ts(d + FA_O_COL, pbuf + kk * 8, bdesc, idesc_pv, (pv_t != 0 || kk != 0) ? 1u : 0u);
             }
           }
-          if (!FA_LEAN || pv_t + 1 == (uint32_t)T) umma_commit(&o_full[w]);     // lean: one phase per item
+          if (pv_t + 1 == (uint32_t)T) umma_commit(&o_full[w]);     // one phase per item: its last P V has landed
           umma_commit(&kv_empty[st]);      // this issuer's streams are done with the stage
           if (more) qk_issue(u + 2);       // into the buffers these P V steps free
         }
@@ -338,9 +331,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
     }
   }
   } else {
-#if FA_SETMAXNREG
     reg_inc<FA_REGS_SOFTMAX>();
-#endif
     // ---------------- softmax: one thread per query row of one stream ----------------
     const int sidx = warp >> 2, q = warp & 3;
     const int g = sidx >> 1, h = sidx & 1;
@@ -362,9 +353,10 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         const int st = n_tile % FA_STAGES;
         const uint32_t sbuf = acc + (n_tile & 1) * FA_KT;
         if (!mbar_wait(&s_full[g * 2 + (n_tile & 1)], (n_tile >> 1) & 1, abort_flag, p.status, 40)) { ok = false; break; }
-        // The key terms of this stage were published through kv_full, which the issuer waited for before
-        // it queued this S: S being there implies them.
-        if (!FA_LEAN && !mbar_wait(&kv_full[st], (n_tile / FA_STAGES) & 1, abort_flag, p.status, 41)) { ok = false; break; }
+        // The key terms of this stage were published through kv_full, which the issuer waited for before it
+        // queued this S: S being there implies them, and this warp spares itself the wait.  (Every wait in
+        // this loop costs far more than its instructions: its shared-memory round trip queues behind the
+        // other warps' exponentials, so the loop keeps to the waits it cannot do without.)
         tc_fence_after();
         const bool masked = mask_flag[st] != 0;
         // The tile's 48 S columns go to registers; the three 16-key pieces are then independent chains
@@ -427,26 +419,16 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           neg = -m_ref * L2E;
         }
         uint32_t w0[8], w1[8], w2[8];
-#if FA_PINGPONG
+        // The two query tiles take turns at the exponentials: tile 1's warps start a key tile's
+        // exponentials when tile 0's are through theirs, and the other way round for the next key tile,
+        // so that on every scheduler two warps have the exponent unit while the other two store, hand
+        // over, wait and load.  (Without the turns the four warps of a scheduler fall into step.)
         if (!mbar_wait(&turn[g], (g ^ 1 ^ n_tile) & 1, abort_flag, p.status, 45)) { ok = false; break; }
         tie48(s0, s1, s2);
-#endif
-#if FA_PINGPONG && FA_EARLY_TURN
-        // the turn is passed on before the last piece: the other tile's warps need about as long to
-        // wake up as this piece takes
-        float a0 = exponentials(s0, w0), a1 = exponentials(s1, w1);
-        tie16(w0, w1);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&turn[g ^ 1]);
-        float a2 = exponentials(s2, w2);
-#else
         float a0 = exponentials(s0, w0), a1 = exponentials(s1, w1), a2 = exponentials(s2, w2);
-#if FA_PINGPONG
         tie24(w0, w1, w2);
         __syncwarp();
         if (lane == 0) mbar_arrive(&turn[g ^ 1]);
-#endif
-#endif
         // The sum of a piece's 16 exponentials bounds each of them: while it stays below kBig every P is
         // far inside fp16 and the row reference is left alone (no maximum is searched at all).
         const bool over = !(a0 <= kBig) || !(a1 <= kBig) || !(a2 <= kBig);
@@ -459,8 +441,7 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
           if (t > 0) {
             // P V of every earlier tile of the item has landed once both issuers have released the
             // previous tile's K/V stage
-            if (FA_LEAN ? !mbar_wait(&kv_empty[(n_tile - 1) % FA_STAGES], ((n_tile - 1) / FA_STAGES) & 1, abort_flag, p.status, 43)
-                        : !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 43)) ok = false;
+            if (!mbar_wait(&kv_empty[(n_tile - 1) % FA_STAGES], ((n_tile - 1) / FA_STAGES) & 1, abort_flag, p.status, 43)) ok = false;
             tc_fence_after();
             if (ok) {
 #pragma unroll
@@ -487,17 +468,13 @@ flash_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ C
         tmem_st8(sbuf + 16, w2);
         if (!ok) break;
         tmem_st_wait();
-        // Stay within one phase of the "P V landed" barrier (a parity test cannot tell phases two apart).
-        // This comes before the arrive below: once this warp has arrived, P V of this tile may land at
-        // any time.  P V of the previous tile was queued a whole tile ago, so this rarely waits.
-        if (!FA_LEAN && n_tile > 0 && !mbar_wait(&o_full[g], (n_tile - 1) & 1, abort_flag, p.status, 44)) { ok = false; break; }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[g * 2 + (n_tile & 1)]);
       }
       if (!ok) break;
       // the item's last P V has landed: normalise, gate, store
-      if (!mbar_wait(&o_full[g], FA_LEAN ? (n_item & 1) : ((n_tile - 1) & 1), abort_flag, p.status, 42)) { ok = false; break; }
+      if (!mbar_wait(&o_full[g], n_item & 1, abort_flag, p.status, 42)) { ok = false; break; }
       ++n_item;
       tc_fence_after();
       {

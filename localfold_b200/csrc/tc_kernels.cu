@@ -230,7 +230,7 @@ template <int MAJOR>
 __global__ void __launch_bounds__(CT_THREADS, 1)
 contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 op16* __restrict__ x, int m_rows, int n_rows, int k_len, int ldx, int64_t x_plane, int col0, int c,
-                float scale, Status* status) {
+                float scale, Status* status, const __grid_constant__ PeerPtrs xpeer, int rows_per_rank, int ch0) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CT_STAGES * CT_STAGE_BYTES);
@@ -332,7 +332,16 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_flag, status, 4)) break;
       tc_fence_after();
       const int gi = mi * CT_BM + row;
-      op16* dst_row = x + (int64_t)h * x_plane + (int64_t)gi * ldx + col0;
+      op16* dst_row;
+      if (rows_per_rank > 0) {
+        // row gi of the product belongs to rank gi / rows_per_rank: stored into that rank's
+        // [channels][rows_per_rank][ldx] buffer (x_plane = rows_per_rank * ldx)
+        int owner = gi / rows_per_rank;
+        if (gi >= m_rows) owner = 0;      // not stored
+        dst_row = reinterpret_cast<op16*>(xpeer.p[owner]) + (int64_t)(ch0 + h) * x_plane + (int64_t)(gi - owner * rows_per_rank) * ldx + col0;
+      } else {
+        dst_row = x + (int64_t)h * x_plane + (int64_t)gi * ldx + col0;
+      }
       const int col_limit = (n_rows + 15) / 16 * 16 < ldx - col0 ? (n_rows + 15) / 16 * 16 : ldx - col0;
 #pragma unroll 1
       for (int cc = 0; cc < CT_BN / 32; ++cc) {
@@ -393,8 +402,26 @@ void configure_once() {
 
 bool contract_supported(int n, int c) { return n >= 1 && c >= 1 && g_encode != nullptr; }
 
+static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
+                               int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale,
+                               const PeerPtrs* peers, int rows_per_rank, int ch0);
+
 lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                         int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale) {
+  return contract_impl(ctx, cur, a, b, x, m_rows, n_rows, k_len, ld_ab, ldx, x_plane, col0, c, incoming, scale, nullptr, 0, 0);
+}
+
+lf_status contract_scatter(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, int n, int ld, int c, int incoming,
+                           float scale, const PeerPtrs& x_peers, int rows_per_rank, int total_channels, int ch0) {
+  (void)total_channels;
+  // the product's planes at the row owners hold rows_per_rank rows of ld elements
+  return contract_impl(ctx, cur, a, b, nullptr, n, n, n, ld, ld, (int64_t)rows_per_rank * ld, 0, c, incoming, scale, &x_peers,
+                       rows_per_rank, ch0);
+}
+
+static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
+                               int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale,
+                               const PeerPtrs* peers, int rows_per_rank, int ch0) {
   if (cur.dry) return LF_OK;
   if (ld_ab % 8 != 0 || ld_ab < k_len || ldx % 8 != 0 || col0 % 8 != 0)
     return lf_fail(ctx, LF_ERR_ARGUMENT, "contraction strides must be multiples of 8 and cover the row");
@@ -412,9 +439,9 @@ lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const 
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_CONTRACT);
   if (!incoming)
-    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status);
+    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0);
   else
-    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status);
+    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;

@@ -7,6 +7,11 @@
 
 namespace tc {
 
+// Device buffers of the other ranks of a box as mapped into this process (entry `rank` = the local
+// buffer).  Kernels only ever store to them with plain st.global.
+constexpr int kMaxPeers = 16;
+struct PeerPtrs { void* p[kMaxPeers]; };
+
 void configure_once();
 lf_status prepare_weights(lf_context* ctx, lf_weights* w);
 // Reads the device status word; LF_ERR_TIMEOUT if a bounded wait expired in a kernel.
@@ -24,6 +29,12 @@ lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16*
 lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                         int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale);
 
+// Channel-sharded form for the GPUs of one box: a, b are this rank's `c` channels over all n rows
+// ([c][n][ld]); row i of channel h of the product goes to rank i / rows_per_rank, into its buffer
+// x_peers[...] laid out [all channels][rows_per_rank][ldx], at channel ch0 + h.
+lf_status contract_scatter(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, int n, int ld, int c, int incoming,
+                           float scale, const PeerPtrs& x_peers, int rows_per_rank, int total_channels, int ch0);
+
 // LayerNorm + projection kernels for 128-channel activations (weights repacked by
 // prepare_weights into lf_weights::h).
 bool ln_gemm_supported(const lf_weights* w);
@@ -34,12 +45,23 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 // `rows` pair rows of length n (rows = n for the whole pair, fewer for a row shard)
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
                            int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b);
+// The same for a row shard whose operands are wanted channel-sharded: channel h of the shard's rows goes
+// to rank h / (128 / ranks), into its buffers a_peers / b_peers laid out [128 / ranks][n][ld], at rows
+// row0 .. row0 + rows (row0 = this rank's first pair row).
+lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
+                                   int n, int ld, int variance, float eps, const lf_weights* w, const PeerPtrs& a_peers,
+                                   const PeerPtrs& b_peers, int ranks, int row0);
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 logical rows [batch][ld][128] stored in 8-row x
 // 8-channel pieces (element (b, q, c) at b*ld*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ld = Q rounded up to 16) and the
 // pair bias fp16 [heads][batch rows][ldb] (null = none) from the normalised input
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
+// The same for a row shard: its bias rows are written into every rank's copy of the whole bias
+// [heads][bias_rows][ldb] at query rows row0 .. row0 + batch.
+lf_status attention_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
+                                    int variance, float eps, int heads, const lf_weights* w, op16* q, op16* k, op16* v,
+                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb);
 lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,
                            const lf_weights* w, const void* resid, void* out, int act_dtype);
 lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int rows, int n, int ld, float x_eps,

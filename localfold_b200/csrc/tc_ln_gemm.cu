@@ -50,10 +50,16 @@ struct LnGemmParams {
   op16* out_b;
   int n, ld;                // pair row length and operand row stride
   int plane_rows;           // pair rows held (n for a whole pair, fewer for a row shard)
+  // channel-sharded destinations (peer_ranks > 1): channel h goes to rank h / ch_per_rank, plane h % ch_per_rank of
+  // its [ch_per_rank][peer_plane_rows][ld] buffer, at rows peer_row0 + local row; stores go to the peers' memory
+  int peer_ranks, ch_per_rank, peer_plane_rows, peer_row0;
+  PeerPtrs peer_a, peer_b;
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // logical rows, stored in 8 x 8 pieces (see ldq)
   op16* out_bias;           // fp16 [heads][batch rows][ldb] (head, query, key)
   int ldb;
+  int bias_ranks, bias_rows, bias_row0;   // bias_ranks > 0: the bias rows go to every rank's [heads][bias_rows][ldb] at bias_row0 + query row
+  PeerPtrs peer_bias;
   int ldq;                  // attention activations (q, k, v, gate, o) are stored in 8-row x 8-channel pieces: element (b, q, c)
                             // of a [batch][Q][128] tensor sits at b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ldq = Q rounded up to 16
   int heads, bias_swap;
@@ -100,7 +106,7 @@ __device__ __forceinline__ void tile_rows(const LnGemmParams& p, int64_t t, int6
 
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1)
-ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const LnGemmParams p) {
+ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const __grid_constant__ LnGemmParams p) {
   // operand stages: the triangle output keeps one (its shared memory goes to the staging rows of the pair tile instead);
   // the producers of tile t+1 then start when the MMAs of tile t have completed, i.e. beside the epilogue of tile t
   constexpr int NS = EPI == LG_EPI_TRI_OUT ? 1 : 2;
@@ -440,7 +446,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
           // gate at 128..255).  Each thread owns one channel and writes runs of consecutive k.
           const int h = row;
           const float bias_p = sBias[j * 256 + h], bias_g = sBias[j * 256 + 128 + h];
-          op16* plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.plane_rows * p.ld;
+          op16* plane_base;
+          if (p.peer_ranks > 1) {
+            const int owner = h / p.ch_per_rank;
+            plane_base = reinterpret_cast<op16*>(j == 0 ? p.peer_a.p[owner] : p.peer_b.p[owner]) +
+                         ((int64_t)(h - owner * p.ch_per_rank) * p.peer_plane_rows + p.peer_row0) * p.ld;
+          } else {
+            plane_base = (j == 0 ? p.out_a : p.out_b) + (int64_t)h * p.plane_rows * p.ld;
+          }
           const bool vec = (p.n & 15) == 0;
           const uint32_t un = (uint32_t)p.n;
           // rows of this warp's quarter: r0 .. r0+31, as (i, k) with 32-bit arithmetic
@@ -653,9 +666,20 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
               // row-major per head: [head][batch rows][ldb]
               const int64_t dst = bq * p.ldb + bk;
               const int64_t qq = (int64_t)p.batch * p.ldb;
+              if (p.bias_ranks > 0) {
+                // every rank keeps the bias of all query rows: this shard's rows go to each of them
+                const int64_t pq = (int64_t)p.bias_rows * p.ldb, pdst = (p.bias_row0 + bq) * p.ldb + bk;
+                for (int g2 = 0; g2 < p.bias_ranks; ++g2) {
+                  op16* ob = reinterpret_cast<op16*>(p.peer_bias.p[g2]);
 #pragma unroll
-              for (int h = 0; h < 16; ++h)
-                if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]));
+                  for (int h = 0; h < 16; ++h)
+                    if (h < p.heads) ob[h * pq + pdst] = __float2half_rn(__uint_as_float(v[h]));
+                }
+              } else {
+#pragma unroll
+                for (int h = 0; h < 16; ++h)
+                  if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]));
+              }
             }
           }
         }
@@ -725,11 +749,56 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
   return LF_OK;
 }
 
+lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
+                                   int n, int ld, int variance, float eps, const lf_weights* w, const PeerPtrs& a_peers,
+                                   const PeerPtrs& b_peers, int ranks, int row0) {
+  if (cur.dry) return LF_OK;
+  LnGemmParams p{};
+  p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
+  p.plane_rows = rows;
+  p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
+  p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
+  p.mask = mask; p.n = n; p.ld = ld; p.status = (Status*)ctx->tc_status;
+  p.peer_ranks = ranks; p.ch_per_rank = 128 / ranks; p.peer_plane_rows = n; p.peer_row0 = row0;
+  p.peer_a = a_peers; p.peer_b = b_peers;
+  p.out_a = (op16*)a_peers.p[0]; p.out_b = (op16*)b_peers.p[0];      // ranks == 1: plain form
+  const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
+  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  return LF_OK;
+}
+
+static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
+                                        int transpose, int variance, float eps, int heads, int bias_swap, const lf_weights* w,
+                                        op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb, const PeerPtrs* bias_peers,
+                                        int ranks, int bias_rows, int row0);
+
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb) {
+  (void)head_dim;
+  return attention_project_impl(ctx, cur, act, act_dtype, batch, Q, transpose, variance, eps, heads, bias_swap, w, q, k, v, g,
+                                bias, ldb, nullptr, 0, 0, 0);
+}
+
+lf_status attention_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
+                                    int variance, float eps, int heads, const lf_weights* w, op16* q, op16* k, op16* v,
+                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb) {
+  return attention_project_impl(ctx, cur, act, act_dtype, batch, Q, 0, variance, eps, heads, 0, w, q, k, v, g,
+                                (op16*)bias_peers.p[0], ldb, &bias_peers, ranks, bias_rows, row0);
+}
+
+static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
+                                        int transpose, int variance, float eps, int heads, int bias_swap, const lf_weights* w,
+                                        op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb, const PeerPtrs* bias_peers,
+                                        int ranks, int bias_rows, int row0) {
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
+  if (bias_peers) { p.bias_ranks = ranks; p.bias_rows = bias_rows; p.bias_row0 = row0; p.peer_bias = *bias_peers; }
   p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
   p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 528; p.bias = (const float*)w->h[1]; p.n_bias = 528;
@@ -739,7 +808,6 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
   p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.ldb = ldb; p.heads = heads; p.bias_swap = bias_swap;
   p.ldq = (Q + 15) / 16 * 16;
   p.bias_flags = w->bias_flags;
-  (void)head_dim;
   p.status = (Status*)ctx->tc_status;
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);

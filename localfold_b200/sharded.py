@@ -16,6 +16,16 @@ The reference is single-device.  Here the pair tensor is sharded by rows: rank g
                                    normalised pair); then the pair transition (row-local)
     -> R       transpose back
 
+With a ``PeerExchange`` the triangle multiplication runs channel-sharded instead and the exchange is
+fused into the kernels (stores into the peers' memory over NVLink, one barrier per step):
+
+    R layout   triangle outgoing   projection epilogue stores channel h of the local rows into rank
+               and incoming        h / (128/G)'s operand planes; that rank contracts its 128/G channels over
+                                   the whole N x N plane (full tiles, either direction, no transposed pair) and
+                                   its epilogue stores row i of the product to rank i / R; output is row-local
+    R layout   attention starting  the projection epilogue stores the shard's pair-bias rows into every rank
+    -> T, attention ending, transition, -> R as above: two transposes per block instead of four
+
 Collectives go through ``torch.distributed`` (NCCL between GPUs; gloo in the CPU tests).  The
 arithmetic of every step is behind an ``ops`` object: ``GpuShardOps`` calls the library's
 ``lf_pair_shard_step``; tests plug in a float64 CPU implementation to check the orchestration.
@@ -117,6 +127,111 @@ class _DeviceArray:
                                          "version": 3, "strides": None}
 
 
+def share_buffers(device, group, sizes):
+    """Allocates one device buffer per entry of ``sizes`` (bytes) and maps every other rank's buffers into
+    this process as CUDA IPC handles.  Returns (local pointers, mapped[buffer][rank] pointers valid here,
+    pointers opened from peers).  Every rank reaches every collective even when its own part fails, and all
+    ranks agree on the outcome before anyone relies on the mapping."""
+    import torch.distributed as dist
+    lib = device.lib
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    local, opened, mapped, handles, error = [], [], [], [], None
+    try:
+        for nbytes in sizes:
+            ptr = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            device.check(lib.lf_peer_buffer_create(device.handle, int(nbytes), ctypes.byref(ptr), handle))
+            local.append(ptr.value)
+            handles.append(handle.raw)
+    except Exception as exc:      # keep going: every rank must reach the collectives below
+        error = exc
+        handles = [b""] * len(sizes)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, handles, group=group)
+    if error is None and all(len(h) == 64 for hs in gathered for h in hs):
+        try:
+            for b in range(len(sizes)):
+                row = []
+                for g in range(world):
+                    if g == rank:
+                        row.append(local[b])
+                        continue
+                    ptr = ctypes.c_void_p()
+                    device.check(lib.lf_peer_buffer_open(device.handle, gathered[g][b], ctypes.byref(ptr)))
+                    row.append(ptr.value)
+                    opened.append(ptr.value)
+                mapped.append(row)
+        except Exception as exc:
+            error = exc
+    elif error is None:
+        error = RuntimeError("another rank could not allocate its peer buffers")
+    verdicts = [None] * world
+    dist.all_gather_object(verdicts, error is None, group=group)
+    if not all(verdicts):
+        release_buffers(device, group, local, opened)
+        raise error if error is not None else RuntimeError("another rank could not map the peer buffers")
+    return local, mapped, opened
+
+
+def release_buffers(device, group, local, opened):
+    import torch.distributed as dist
+    lib = device.lib
+    for p in opened:
+        lib.lf_peer_buffer_close(device.handle, p)
+    dist.barrier(group=group)      # nobody frees a buffer a peer still has mapped
+    for p in local:
+        lib.lf_peer_buffer_destroy(device.handle, p)
+
+
+class PeerExchange:
+    """Buffers of the fused exchange (``lf_pair_shard_exchange_step``): per rank the channel-sharded triangle
+    operands a, b ``[128/G][N][N]`` fp16, the product x ``[128][R][N]`` and the pair bias of all query rows
+    ``[4][N][N]``, each shared with the other ranks' processes as CUDA IPC handles.  ``barrier()`` is a
+    one-element all-reduce on the current stream: once it has passed on a rank, every peer kernel enqueued
+    before its own barrier has finished, so its stores into this rank's buffers have landed.  Each buffer
+    is written by one step and read by the next, with a barrier in between and the reader's kernel ahead of
+    the writer's next barrier in stream order, so single buffers are enough.  GPUs of one box only."""
+
+    def __init__(self, device, group, rows, length):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.group, self.dev = torch, dist, group, device
+        device.require_current_stream("PeerExchange")
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.R, self.N = int(rows), int(length)
+        if self.R * self.world != self.N:
+            raise ValueError("shard rows times ranks must equal the row length")
+        if 128 % self.world or self.N % 16 or (self.world > 1 and self.R % 128):
+            raise ValueError("the fused exchange needs ranks dividing 128, length a multiple of 16 and shard rows a multiple of 128")
+        cpr = 128 // self.world
+        plane = self.N * self.N * 2
+        sizes = [cpr * plane, cpr * plane, 128 * self.R * self.N * 2, 4 * plane]
+        self.local, self.mapped, self.opened = share_buffers(device, group, sizes)
+        where = f"cuda:{device.ordinal}"
+        half = lambda ptr, shape: torch.as_tensor(_DeviceArray(ptr, shape, "<u2"), device=where).view(torch.float16)
+        self.x = half(self.local[2], (128, self.R, self.N))
+        self.bias = half(self.local[3], (4, self.N, self.N))
+        self.bias.zero_()
+        self.flag = torch.zeros(1, device=where)
+        self.peers = nat.ShardPeers()
+        self.peers.rank = self.rank
+        for g in range(self.world):
+            self.peers.a[g], self.peers.b[g] = self.mapped[0][g], self.mapped[1][g]
+            self.peers.x[g], self.peers.bias[g] = self.mapped[2][g], self.mapped[3][g]
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def barrier(self):
+        self.dev.require_current_stream("PeerExchange.barrier")
+        self.dist.all_reduce(self.flag, group=self.group)
+
+    def close(self):
+        self.dev.synchronize()
+        self.dist.barrier(group=self.group)
+        release_buffers(self.dev, self.group, self.local, self.opened)
+        self.local, self.opened = [], []
+
+
 class PeerTranspose:
     """Transposes of the row-sharded pair with one kernel per rank that stores into the peers' memory
     (``lf_pair_transpose_scatter``), instead of pack -> all-to-all -> unpack.
@@ -141,44 +256,7 @@ class PeerTranspose:
         self.dtype = dtype
         self.vector_bytes = 128 * (4 if dtype == torch.float32 else 2)
         nbytes = self.R * self.N * self.vector_bytes
-        lib = device.lib
-        self.local, self.opened, self.mapped = [], [], []
-        handles, error = [], None
-        try:
-            for _ in range(2):
-                ptr = ctypes.c_void_p()
-                handle = ctypes.create_string_buffer(64)
-                device.check(lib.lf_peer_buffer_create(device.handle, nbytes, ctypes.byref(ptr), handle))
-                self.local.append(ptr.value)
-                handles.append(handle.raw)
-        except Exception as exc:      # keep going: every rank must reach the collectives below
-            error = exc
-            handles = [b"", b""]
-        gathered = [None] * self.world
-        dist.all_gather_object(gathered, handles, group=group)
-        if error is None and all(len(h[0]) == 64 for h in gathered):
-            try:
-                for b in range(2):       # [buffer][rank] -> device pointer valid in this process
-                    row = []
-                    for g in range(self.world):
-                        if g == self.rank:
-                            row.append(self.local[b])
-                            continue
-                        ptr = ctypes.c_void_p()
-                        device.check(lib.lf_peer_buffer_open(device.handle, gathered[g][b], ctypes.byref(ptr)))
-                        row.append(ptr.value)
-                        self.opened.append(ptr.value)
-                    self.mapped.append(row)
-            except Exception as exc:
-                error = exc
-        elif error is None:
-            error = RuntimeError("another rank could not allocate its peer buffers")
-        # all ranks agree on the outcome before anyone relies on the mapping
-        verdicts = [None] * self.world
-        dist.all_gather_object(verdicts, error is None, group=group)
-        if not all(verdicts):
-            self._release()
-            raise error if error is not None else RuntimeError("another rank could not map the peer buffers")
+        self.local, self.mapped, self.opened = share_buffers(device, group, [nbytes, nbytes])
         typestr = "<f4" if dtype == torch.float32 else "<u2"
         views = [torch.as_tensor(_DeviceArray(p, (self.R, self.N, 128), typestr), device=f"cuda:{device.ordinal}") for p in self.local]
         self.views = [v if dtype == torch.float32 else v.view(torch.bfloat16) for v in views]
@@ -204,12 +282,7 @@ class PeerTranspose:
         return self.views[other]
 
     def _release(self):
-        lib = self.dev.lib
-        for p in self.opened:
-            lib.lf_peer_buffer_close(self.dev.handle, p)
-        self.dist.barrier(group=self.group)      # nobody frees a buffer a peer still has mapped
-        for p in self.local:
-            lib.lf_peer_buffer_destroy(self.dev.handle, p)
+        release_buffers(self.dev, self.group, self.local, self.opened)
         self.opened, self.local = [], []
 
     def close(self):
@@ -223,10 +296,13 @@ class ShardedPairStack:
     `transposer` (a ``PeerTranspose``) replaces the all-to-all transposes when given - the shard
     must then live in ``transposer.shard()``."""
 
-    def __init__(self, comm, ops, transposer=None):
+    def __init__(self, comm, ops, transposer=None, exchange=None):
+        """``exchange``: a ``PeerExchange`` (GPU) or True (operations that exchange through ``comm``, as the
+        CPU test operations do) switches to the channel-sharded triangle multiplication."""
         self.comm = comm
         self.ops = ops
         self.transposer = transposer
+        self.exchange = exchange
 
     def _transpose(self, z):
         return self.transposer.transpose(z) if self.transposer is not None else transpose_shard(self.comm, z)
@@ -251,9 +327,30 @@ class ShardedPairStack:
         o = ops.attention_core(q, k, v, g, bias_all, mask, w)
         ops.attention_output(o, z, w)
 
+    def _triangle_channel(self, z, mask, w, incoming):
+        """Channel-sharded: project (operands leave for their channel owners), contract 128/G channels over the
+        whole plane (product rows leave for their row owners), output on the local rows."""
+        ops = self.ops
+        ops.exchange_triangle_project(z, mask, w, self.exchange, self.comm)
+        x = ops.exchange_triangle_contract(w, self.exchange, self.comm, incoming)
+        ops.triangle_output(x, z, w)
+
+    def _attention_channel(self, z, mask, w):
+        ops = self.ops
+        q, k, v, g, bias_all = ops.exchange_attention_project(z, w, self.exchange, self.comm)
+        o = ops.attention_core(q, k, v, g, bias_all, mask, w)
+        ops.attention_output(o, z, w)
+
     def block(self, z, mask_rows, mask_t_rows, w):
         """One block on the local shard `z` (updated and returned; it may be a new tensor)."""
-        comm = self.comm
+        if self.exchange is not None:
+            self._triangle_channel(z, mask_rows, w["triangle_outgoing"], False)
+            self._triangle_channel(z, mask_rows, w["triangle_incoming"], True)
+            self._attention_channel(z, mask_rows, w["attention_starting"])
+            z = self._transpose(z)
+            self._attention_channel(z, mask_t_rows, w["attention_ending"])
+            self.ops.transition(z, w["transition"])
+            return self._transpose(z)
         self._triangle(z, mask_rows, w["triangle_outgoing"])
         z = self._transpose(z)
         self._triangle(z, mask_t_rows, w["triangle_incoming"])
@@ -326,13 +423,44 @@ class GpuShardOps:
         return q, k, v, g, self.bias
 
     def attention_core(self, q, k, v, g, bias_all, mask, w):
-        # gathered [rank][head][rows][ld] -> [head][all rows][ld]
-        bias_all = bias_all.permute(1, 0, 2, 3).reshape(4, self.N, self.ld).contiguous()
+        if bias_all.dim() == 4:      # gathered [rank][head][rows][ld] -> [head][all rows][ld]
+            bias_all = bias_all.permute(1, 0, 2, 3).reshape(4, self.N, self.ld).contiguous()
         self._step(nat.SHARD_ATTENTION_CORE, w, None, mask, (q, k, v, g, bias_all, self.o))
         return self.o
 
     def attention_output(self, o, z, w):
         self._step(nat.SHARD_ATTENTION_OUTPUT, w, z, None, (None, None, None, None, None, o))
+
+    # -- the fused exchange (``PeerExchange``): kernels store into the peers' buffers, then a barrier
+
+    def _exchange_step(self, op, w, ex, pair=None, mask=None, bufs=(), incoming=False):
+        self.dev.require_current_stream("GpuShardOps")
+        d = nat.ShardStepDesc()
+        d.op, d.rows, d.length, d.ranks, d.chunk = op, self.R, self.N, self.G, 0
+        d.variance, d.epsilon = self.variance, self.eps
+        d.act_dtype = nat.DTYPE_BF16 if (pair is not None and pair.dtype == self.torch.bfloat16) else nat.DTYPE_F32
+        d.pair = pair.data_ptr() if pair is not None else None
+        d.mask = mask.data_ptr() if mask is not None else None
+        for i, t in enumerate(bufs):
+            d.buf[i] = t.data_ptr() if t is not None else None
+        d.weights = w.handle
+        ex.peers.incoming = 1 if incoming else 0
+        self.dev.check(self.dev.lib.lf_pair_shard_exchange_step(self.dev.handle, ctypes.byref(d), ctypes.byref(ex.peers), None))
+
+    def exchange_triangle_project(self, z, mask, w, ex, comm):
+        self._exchange_step(nat.SHARD_TRIANGLE_PROJECT, w, ex, z, mask)
+        ex.barrier()          # every rank's operand rows have landed in the channel owners' planes
+
+    def exchange_triangle_contract(self, w, ex, comm, incoming):
+        self._exchange_step(nat.SHARD_TRIANGLE_CONTRACT, w, ex, incoming=incoming)
+        ex.barrier()          # every channel owner's product rows have landed here
+        return ex.x
+
+    def exchange_attention_project(self, z, w, ex, comm):
+        q, k, v, g = self.qkvg
+        self._exchange_step(nat.SHARD_ATTENTION_PROJECT, w, ex, z, None, (q, k, v, g))
+        ex.barrier()          # the bias rows of every shard have landed
+        return q, k, v, g, ex.bias
 
     def transition(self, z, w):
         self._step(nat.SHARD_TRANSITION, w, z)

@@ -51,6 +51,34 @@ class CpuShardOps:
         p = torch.softmax(logits.to(torch.float32).to(torch.float64), -1)
         return (p @ vh).permute(0, 2, 1, 3).reshape(self.R, self.N, -1) * g
 
+    # -- channel-sharded triangle multiplication and scattered bias, exchanged through `comm`
+    #    (what the GPU path does with stores into the peers' memory)
+
+    def exchange_triangle_project(self, z, mask, w, ex, comm):
+        a, b = self.triangle_project(z, mask, w)                   # [R][N][c]
+        G, c = comm.world, a.shape[-1]
+        cpr = c // G
+
+        def to_channel_owner(t):       # rank g receives channels [g cpr, (g+1) cpr) of every rank's rows
+            send = t.reshape(self.R, self.N, G, cpr).permute(2, 0, 1, 3).contiguous()      # [dest][r][k][cpr]
+            recv = comm.all_to_all(send)                                                   # [src][r][k][cpr]
+            return recv.reshape(G * self.R, self.N, cpr)                                   # [n][k][cpr]: all rows
+
+        self._a_cs, self._b_cs = to_channel_owner(a), to_channel_owner(b)
+
+    def exchange_triangle_contract(self, w, ex, comm, incoming):
+        a, b = self._a_cs, self._b_cs
+        x = torch.einsum("kjc,kic->ijc", a, b) if incoming else torch.einsum("ikc,jkc->ijc", a, b)   # [N][N][cpr]
+        G = comm.world
+        send = x.reshape(G, self.R, self.N, -1).contiguous()                                # [dest][r][j][cpr]
+        recv = comm.all_to_all(send)                                                        # [src = channel block][r][j][cpr]
+        self._x = recv.permute(1, 2, 0, 3).reshape(self.R, self.N, -1)                      # channels back in order
+        return self._x
+
+    def exchange_attention_project(self, z, t, ex, comm):
+        q, k, v, g, bias = self.attention_project(z, t)
+        return q, k, v, g, comm.all_gather(bias)
+
     def attention_output(self, o, z, t):
         w = t["attention"]
         z += o @ T(w["outputWeight"]) + T(w["outputBias"])

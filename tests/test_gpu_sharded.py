@@ -1,7 +1,10 @@
 """Row-sharded pair block on the GPU: two ranks (two processes on one device, exchanging through gloo
 with host staging, so no NCCL and no second GPU is needed) run the library's shard steps and must
 match the unsharded CPU oracle within the 16-bit per-block bound.  One case moves the transposes
-to the peer-store kernel (buffers shared between the two processes as CUDA IPC handles)."""
+to the peer-store kernel (buffers shared between the two processes as CUDA IPC handles), and one runs
+the fused exchange: channel-sharded triangle multiplication and pair bias written by the producing
+kernels straight into the other process's buffers.  The kernels never wait on one another: every
+barrier is a host-side collective between the launches."""
 import os
 import sys
 
@@ -22,8 +25,8 @@ def _worker(rank, world, port, n, result_path, peer):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import localfold_b200 as lf
     from localfold_b200 import synthetic as syn
-    from localfold_b200.sharded import (GpuShardOps, PeerTranspose, ShardedPairStack, TorchComm, prepared_block_weights,
-                                        shard_rows)
+    from localfold_b200.sharded import (GpuShardOps, PeerExchange, PeerTranspose, ShardedPairStack, TorchComm,
+                                        prepared_block_weights, shard_rows)
 
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
@@ -39,12 +42,15 @@ def _worker(rank, world, port, n, result_path, peer):
         transposer = PeerTranspose(dev, None, n // world, n, torch.float32)
         transposer.shard().copy_(z)
         z = transposer.shard()
-    stack = ShardedPairStack(TorchComm(via_host=True), GpuShardOps(dev, n // world, n, world), transposer)
+    exchange = PeerExchange(dev, None, n // world, n) if peer == "exchange" else None
+    stack = ShardedPairStack(TorchComm(via_host=True), GpuShardOps(dev, n // world, n, world), transposer, exchange)
     z = stack.run(z, m_rows, m_t_rows, [prepared_block_weights(b) for b in blocks])
     dev.synchronize()
     host = z.cpu()
     if transposer is not None:
         transposer.close()
+    if exchange is not None:
+        exchange.close()
     gathered = [torch.empty_like(host) for _ in range(world)]
     dist.all_gather(gathered, host)
     if rank == 0:
@@ -55,7 +61,7 @@ def _worker(rank, world, port, n, result_path, peer):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n,peer", [(64, False), (160, False), (160, True)])
+@pytest.mark.parametrize("n,peer", [(64, False), (160, False), (160, True), (256, "exchange")])
 def test_sharded_gpu_block_matches_oracle(tmp_path, n, peer):
     sys.path.insert(0, ROOT)
     from localfold_b200 import synthetic as syn

@@ -1,6 +1,8 @@
-"""The row-sharded pair stack on CPU: two gloo ranks run ``ShardedPairStack`` with float64 CPU steps and
-must reproduce the unsharded oracle block (checks the transposes, the gathers, incoming-as-outgoing on the
-transposed shard and ending-as-starting attention with the transposed mask)."""
+"""The row-sharded pair stack on CPU: gloo ranks run ``ShardedPairStack`` with float64 CPU steps and must
+reproduce the unsharded oracle block (checks the transposes, the gathers, incoming-as-outgoing on the
+transposed shard and ending-as-starting attention with the transposed mask), in both forms of the triangle
+multiplication: row-sharded with gathered b, and channel-sharded with the operands and the product
+exchanged (what the GPU path does with stores into the peers' memory)."""
 import os
 import sys
 
@@ -13,7 +15,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, n, result_path):
+def _worker(rank, world, port, n, result_path, exchange):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -27,7 +29,7 @@ def _worker(rank, world, port, n, result_path):
     z = torch.from_numpy(np.ascontiguousarray(shard_rows(pair, rank, world))).double()
     m_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(mask, rank, world))).double()
     m_t_rows = torch.from_numpy(np.ascontiguousarray(shard_rows(np.ascontiguousarray(mask.T), rank, world))).double()
-    stack = ShardedPairStack(TorchComm(), CpuShardOps(n // world, n, world))
+    stack = ShardedPairStack(TorchComm(), CpuShardOps(n // world, n, world), exchange=True if exchange else None)
     z = stack.run(z, m_rows, m_t_rows, [block_weights(w) for w in weights])
     gathered = [torch.empty_like(z) for _ in range(world)]
     dist.all_gather(gathered, z)
@@ -37,15 +39,16 @@ def _worker(rank, world, port, n, result_path):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", [False, True])       # True: channel-sharded triangle multiplication
 @pytest.mark.parametrize("world", [2, 4])
-def test_sharded_stack_matches_unsharded_oracle(tmp_path, world):
+def test_sharded_stack_matches_unsharded_oracle(tmp_path, world, exchange):
     sys.path.insert(0, ROOT)
     from localfold_b200 import synthetic as syn
     from oracle import oracle
     n = 16
-    port = 29600 + world + os.getpid() % 200
+    port = 29600 + world + 10 * int(exchange) + os.getpid() % 200
     result = str(tmp_path / "pair.npy")
-    mp.spawn(_worker, args=(world, port, n, result), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, n, result, exchange), nprocs=world, join=True)
     got = np.load(result)
     pair, mask, weights = syn.af2_pair_block(11, n, 16, 16, 2, blocks=2, masked_tail=0.2)
     want = pair
