@@ -270,6 +270,9 @@ def main():
     ap.add_argument("--trimul", default="channel", choices=["channel", "rows"],
                     help="N > 1: triangle multiplication channel-sharded with the exchange fused into the kernels (peer stores), "
                          "or row-sharded with an NCCL all-gather of the operand b")
+    ap.add_argument("--project-exchange", default="fused", choices=["fused", "copy"],
+                    help="--trimul channel: triangle operands to their channel owners by stores from the projection kernel's "
+                         "epilogue, or by a copy kernel after it")
     ap.add_argument("--transpose", default="peer", choices=["peer", "nccl"],
                     help="N > 1: transposes of the sharded pair by peer stores (one kernel) or by NCCL all-to-all")
     args = ap.parse_args()
@@ -352,7 +355,8 @@ def main():
                 except Exception as exc:    # raised on every rank together (the ranks agree inside)
                     print(f"rank {rank}: fused exchange unavailable ({exc}); row-sharded triangle multiplication", file=sys.stderr)
                     args.trimul = "rows"
-            runner = ShardedPairStack(TorchComm(), GpuShardOps(dev, rows, length, world), transposer, exchange)
+            runner = ShardedPairStack(TorchComm(), GpuShardOps(dev, rows, length, world, project_exchange=args.project_exchange),
+                                      transposer, exchange)
             return holder, m_rows, m_t_rows, runner, (transposer, exchange), local
 
         # Numerical check of the path that is about to be timed (NCCL gathers, peer-store transposes): one

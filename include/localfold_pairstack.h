@@ -405,6 +405,12 @@ typedef struct lf_shard_peers {
 } lf_shard_peers;
 LF_API lf_status lf_pair_shard_exchange_step(lf_context* ctx, const lf_shard_step_desc* d, const lf_shard_peers* peers,
                                              lf_result* r);
+/* The operand exchange as a copy of its own, for comparison with the fused form: src [channels][rows][length] fp16
+ * (what TRIANGLE_PROJECT of lf_pair_shard_step writes) -> plane h to rank h / (channels / ranks), plane
+ * h % (channels / ranks) of dst[...] ([channels / ranks][length][length]), rows rank*rows ..; each plane of the shard is
+ * one contiguous run, copied 16 bytes per lane over NVLink. */
+LF_API lf_status lf_pair_planes_scatter(lf_context* ctx, const void* src, int32_t channels, int32_t rows, int32_t length,
+                                        int32_t ranks, int32_t rank, void* const* dst);
 
 /* ------------------------------------------------------------------------------------------
  * Transpose of the row-sharded pair across the GPUs of one box, written directly into the

@@ -114,7 +114,7 @@ EXPORTS = (
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
-    "lf_pair_shard_step", "lf_pair_shard_exchange_step", "lf_peer_buffer_create", "lf_peer_buffer_open", "lf_peer_buffer_close",
+    "lf_pair_shard_step", "lf_pair_shard_exchange_step", "lf_pair_planes_scatter", "lf_peer_buffer_create", "lf_peer_buffer_open", "lf_peer_buffer_close",
     "lf_peer_buffer_destroy", "lf_pair_transpose_scatter",
 )
 
@@ -162,6 +162,7 @@ def load():
         getattr(lib, name).argtypes = [c_void_p, ctypes.POINTER(desc), ctypes.POINTER(Result)]
     lib.lf_pair_shard_exchange_step.argtypes = [c_void_p, ctypes.POINTER(ShardStepDesc), ctypes.POINTER(ShardPeers),
                                                 ctypes.POINTER(Result)]
+    lib.lf_pair_planes_scatter.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32, ctypes.POINTER(c_void_p)]
     lib.lf_peer_buffer_create.argtypes = [c_void_p, ctypes.c_size_t, ctypes.POINTER(c_void_p), ctypes.c_char_p]
     lib.lf_peer_buffer_open.argtypes = [c_void_p, ctypes.c_char_p, ctypes.POINTER(c_void_p)]
     lib.lf_peer_buffer_close.argtypes = [c_void_p, c_void_p]

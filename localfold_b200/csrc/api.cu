@@ -179,15 +179,48 @@ void put_columns(hvec& dst, int total, int col0, const float* src, int in, int n
     for (int j = 0; j < n; ++j) dst[(size_t)i * total + col0 + j] = src[(size_t)i * src_ld + src_col0 + (size_t)j * src_step];
 }
 
-lf_status upload(lf_context* ctx, lf_weights* w, int slot, const hvec& host) {
-  float* dev = nullptr;
-  size_t bytes = host.size() * sizeof(float);
-  LF_CUDA(ctx, cudaMalloc(&dev, bytes ? bytes : 4));
-  w->owned.push_back(dev);
-  if (bytes) LF_CUDA(ctx, cudaMemcpyAsync(dev, host.data(), bytes, cudaMemcpyHostToDevice, ctx->stream));
-  LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // `host` is a temporary
-  w->f[slot] = dev;
+// Tensors of one operator are staged here while it is being built, then go to the device in one
+// allocation with one synchronisation (finish_uploads).
+struct PendingUploads {
+  struct Item { int slot; hvec data; };
+  std::vector<Item> items;
+};
+thread_local PendingUploads g_pending;
+
+lf_status upload(lf_context* ctx, lf_weights* w, int slot, hvec host) {
+  (void)ctx; (void)w;
+  g_pending.items.push_back({slot, std::move(host)});
   return LF_OK;
+}
+
+lf_status finish_uploads(lf_context* ctx, lf_weights* w) {
+  size_t total = 0;
+  std::vector<size_t> offset;
+  for (auto& it : g_pending.items) {
+    offset.push_back(total);
+    total += lf_align_up(it.data.size() * sizeof(float) + 4, 256);
+  }
+  char* base = nullptr;
+  cudaError_t e = cudaMalloc(&base, total ? total : 256);
+  if (e != cudaSuccess) {
+    g_pending.items.clear();
+    cudaGetLastError();
+    return lf_fail(ctx, LF_ERR_MEMORY, "weight allocation of %zu bytes refused: %s", total, cudaGetErrorString(e));
+  }
+  w->owned.push_back(base);
+  lf_status s = LF_OK;
+  for (size_t i = 0; i < g_pending.items.size() && s == LF_OK; ++i) {
+    auto& it = g_pending.items[i];
+    float* dev = reinterpret_cast<float*>(base + offset[i]);
+    if (!it.data.empty() &&
+        cudaMemcpyAsync(dev, it.data.data(), it.data.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
+      cudaGetLastError();
+      s = lf_fail(ctx, LF_ERR_CUDA, "weight upload failed");
+    }
+    w->f[it.slot] = dev;
+  }
+  if (cudaStreamSynchronize(ctx->stream) != cudaSuccess && s == LF_OK) s = lf_fail(ctx, LF_ERR_CUDA, "weight upload failed");
+  return s;      // the staged host copies stay until the tensor-core repacks have read them (lf_weights_create)
 }
 
 struct Expect { const char* name; int64_t count; };
@@ -406,6 +439,13 @@ lf_status build_opm_af2(lf_context* ctx, lf_weights* w, const float* const* t, c
 
 }  // namespace
 
+// Host copy of a tensor of the operator being created (valid inside lf_weights_create only).
+const float* lf_weights_staged_host(int slot) {
+  for (auto& it : g_pending.items)
+    if (it.slot == slot) return it.data.data();
+  return nullptr;
+}
+
 extern "C" {
 
 lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,
@@ -416,6 +456,7 @@ lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weigh
   *out = nullptr;
   if (dims->channels <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "channels must be a positive integer; received %d", dims->channels);
   cudaSetDevice(ctx->device);
+  g_pending.items.clear();
   lf_weights* w = new lf_weights();
   w->ctx = ctx;
   w->kind = (int)kind;
@@ -432,7 +473,9 @@ lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weigh
     case LF_WEIGHTS_OPM_AF2: s = build_opm_af2(ctx, w, tensors, counts, n_tensors); break;
     default: s = lf_fail(ctx, LF_ERR_ARGUMENT, "unknown weight kind %d", (int)kind);
   }
+  if (s == LF_OK) s = finish_uploads(ctx, w);
   if (s == LF_OK) s = tc::prepare_weights(ctx, w);
+  g_pending.items.clear();
   if (s != LF_OK) { lf_weights_destroy(w); return s; }
   *out = w;
   return LF_OK;

@@ -50,6 +50,21 @@ __global__ void __launch_bounds__(256) transpose_scatter_kernel(const uint4* __r
   }
 }
 
+// Channel planes of a row shard to their channel owners: src [C][R][ld] fp16; plane h goes to rank
+// h / cpr, plane h % cpr of its [cpr][N][ld] buffer, rows rank R ..: one contiguous run of R x ld
+// elements per plane, copied 16 bytes per lane.
+__global__ void __launch_bounds__(256) planes_scatter_kernel(const uint4* __restrict__ src, PeerPtrs dst, int channels, int cpr,
+                                                             long long run16, long long dst_plane16, long long dst_row16) {
+  const long long total = (long long)channels * run16;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int h = (int)(i / run16);
+    const long long within = i - (long long)h * run16;
+    const int owner = h / cpr;
+    reinterpret_cast<uint4*>(dst.p[owner])[(long long)(h - owner * cpr) * dst_plane16 + dst_row16 + within] = __ldcs(src + i);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -118,6 +133,30 @@ LF_API lf_status lf_pair_transpose_scatter(lf_context* ctx, const void* src, int
   const int grid = ctx->sm_count * 8;
   lf_prof_begin(ctx, LF_KERNEL_ELEMENTWISE);
   transpose_scatter_kernel<<<grid, 256, 0, ctx->stream>>>((const uint4*)src, pp, rows, length, vector_bytes / 16, rank, vectors);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  LF_CUDA(ctx, cudaGetLastError());
+  return LF_OK;
+}
+
+LF_API lf_status lf_pair_planes_scatter(lf_context* ctx, const void* src, int channels, int rows, int length, int ranks, int rank,
+                                        void* const* dst) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!src || !dst) return lf_fail(ctx, LF_ERR_ARGUMENT, "planes scatter: null buffer");
+  if (ranks < 1 || ranks > kMaxRanks || rank < 0 || rank >= ranks || channels <= 0 || channels % ranks != 0)
+    return lf_fail(ctx, LF_ERR_ARGUMENT, "planes scatter: rank %d of %d, %d channels", rank, ranks, channels);
+  if (rows <= 0 || (int64_t)rows * ranks != length || length % 8 != 0)
+    return lf_fail(ctx, LF_ERR_SHAPE, "planes scatter: rows %d x ranks %d must equal length %d, a multiple of 8", rows, ranks, length);
+  PeerPtrs pp{};
+  for (int g = 0; g < ranks; ++g) {
+    if (!dst[g]) return lf_fail(ctx, LF_ERR_ARGUMENT, "planes scatter: destination %d is null", g);
+    pp.p[g] = (unsigned char*)dst[g];
+  }
+  LF_CUDA(ctx, cudaSetDevice(ctx->device));
+  const long long run16 = (long long)rows * length / 8;             // 16-byte pieces per plane of the shard
+  const long long plane16 = (long long)length * length / 8, row16 = (long long)rank * rows * length / 8;
+  lf_prof_begin(ctx, LF_KERNEL_ELEMENTWISE);
+  planes_scatter_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>((const uint4*)src, pp, channels, channels / ranks, run16, plane16, row16);
   lf_prof_end(ctx);
   ctx->launches++;
   LF_CUDA(ctx, cudaGetLastError());

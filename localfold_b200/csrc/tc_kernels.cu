@@ -111,13 +111,11 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->h.assign(4, nullptr);
     w->h[0] = img;
     // output kernel: rows 0..127 = (diag(gain) Wz)^T, rows 128..255 = Wg^T, plus the folded vectors
-    std::vector<float> wz(128 * 128), g(128), b(128), bz(128), bg(128), fold(384);
-    LF_CUDA(ctx, cudaMemcpyAsync(wz.data(), w->f[TRI_WZ], wz.size() * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(g.data(), w->f[TRI_LNO_G], 512, cudaMemcpyDeviceToHost, ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(b.data(), w->f[TRI_LNO_B], 512, cudaMemcpyDeviceToHost, ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(bz.data(), w->f[TRI_BZ], 512, cudaMemcpyDeviceToHost, ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(bg.data(), w->f[TRI_BG], 512, cudaMemcpyDeviceToHost, ctx->stream));
-    LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // (the operator's tensors are still staged on the host while it is being created)
+    const float *wz = lf_weights_staged_host(TRI_WZ), *g = lf_weights_staged_host(TRI_LNO_G), *b = lf_weights_staged_host(TRI_LNO_B),
+                *bz = lf_weights_staged_host(TRI_BZ), *bg = lf_weights_staged_host(TRI_BG);
+    if (!wz || !g || !b || !bz || !bg) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle weights are not staged");
+    std::vector<float> fold(384);
     std::vector<float> wfold(128 * 128);
     for (int cc = 0; cc < 128; ++cc) {
       double s1 = 0, t = bz[cc];
@@ -158,9 +156,9 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     pack_weight_image(ctx, w->f[ATT_W4], 128, 384, 528, 128, 512, img, 128, 1.0f);
     if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512, 1.0f);
     {
-      std::vector<float> hb(512);
-      LF_CUDA(ctx, cudaMemcpyAsync(hb.data(), w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      const float* staged = lf_weights_staged_host(ATT_B4);
+      if (!staged) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention weights are not staged");
+      std::vector<float> hb(staged, staged + 512);
       for (int i = 0; i < 128; ++i) hb[i] *= qs;
       w->bias_flags = 0;
       for (int grp = 0; grp < 4; ++grp)
@@ -223,7 +221,8 @@ constexpr int CT_BM = 128, CT_BN = 256, CT_BK = 64, CT_STAGES = 4;
 constexpr int CT_A_BYTES = CT_BM * CT_BK * 2;   // 16 KiB
 constexpr int CT_B_BYTES = CT_BN * CT_BK * 2;   // 32 KiB
 constexpr int CT_STAGE_BYTES = CT_A_BYTES + CT_B_BYTES;
-constexpr int CT_SMEM = CT_STAGES * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int CT_OUT_STAGE = 32 * 256;          // per epilogue warp: 32 rows x 128 fp16 columns, for stores into a peer's memory
+constexpr int CT_SMEM = CT_STAGES * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * CT_OUT_STAGE;
 constexpr int CT_THREADS = 192;
 
 template <int MAJOR>
@@ -240,6 +239,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   uint64_t* tmem_empty = tmem_full + 2;        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* out_stage = smem + CT_STAGES * CT_STAGE_BYTES + 256;     // [4 epilogue warps][CT_OUT_STAGE]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // x[h][i][col0 + j] for i < m_rows, j < n_rows; the contraction index runs over k_len
@@ -343,6 +343,44 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         dst_row = x + (int64_t)h * x_plane + (int64_t)gi * ldx + col0;
       }
       const int col_limit = (n_rows + 15) / 16 * 16 < ldx - col0 ? (n_rows + 15) / 16 * 16 : ldx - col0;
+      if (rows_per_rank > 0) {
+        // Rows bound for another GPU leave in 256-byte runs: a thread holds a row of the accumulator, so its
+        // own stores would be 16-byte pieces 32 rows apart, which NVLink carries as 32 small packets.  The
+        // warp's 32 rows x 128 columns are turned round in shared memory (16-byte pieces swizzled by row)
+        // and written two rows per instruction, 16 lanes x 16 bytes each.
+        uint8_t* stage = out_stage + (warp - 2) * CT_OUT_STAGE;
+        const int g_row0 = mi * CT_BM + q * 32;            // the warp's rows share an owner: rows_per_rank % 128 == 0
+        const int owner = g_row0 < m_rows ? g_row0 / rows_per_rank : 0;
+        op16* owner_base = reinterpret_cast<op16*>(xpeer.p[owner]) + (int64_t)(ch0 + h) * x_plane + col0;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * CT_BN + half * 128 + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
+              pk.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
+              pk.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
+              pk.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+              *reinterpret_cast<uint4*>(stage + lane * 256 + (((cc * 4 + v) ^ (lane & 15)) << 4)) = pk;
+            }
+          }
+          __syncwarp();
+#pragma unroll 4
+          for (int rr = 0; rr < 16; ++rr) {
+            const int srow = rr * 2 + (lane >> 4), piece = lane & 15;
+            const uint4 pk = *reinterpret_cast<const uint4*>(stage + srow * 256 + ((piece ^ (srow & 15)) << 4));
+            const int grow = g_row0 + srow, gj = nj * CT_BN + half * 128 + piece * 8;
+            if (grow < m_rows && gj < col_limit)
+              *reinterpret_cast<uint4*>(owner_base + (int64_t)(grow - owner * rows_per_rank) * ldx + gj) = pk;
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int cc = 0; cc < CT_BN / 32; ++cc) {
         uint32_t r[32];

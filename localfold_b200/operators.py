@@ -582,6 +582,18 @@ class OuterProductMeanGpu:
 # AF3 single attention (with the pair-logits pass that feeds it)
 
 
+def prepare_single_attention_weights(device, block_weights, channels, pair_channels):
+    """Resident weights of one block's single attention: its ``singleAttention`` object plus the block's
+    ``singlePairLogitsNormScale/Offset/Projection`` (``shared/af3/weights/weights.js:699-727``)."""
+    att = block_weights["singleAttention"]
+    tensors = [att[k] for k in SINGLE_ATTENTION_AF3_ORDER]
+    tensors += [block_weights["singlePairLogitsNormScale"], block_weights["singlePairLogitsNormOffset"],
+                block_weights["singlePairLogitsProjection"]]
+    return PreparedWeights(device, nat.WEIGHTS_SINGLE_ATTENTION_AF3,
+                           {"channels": channels, "heads": int(att["heads"]), "head_dim": int(att["dimension"]),
+                            "pair_channels": pair_channels}, tensors)
+
+
 class Af3SingleAttentionGpu:
     """``Af3SingleAttentionGpu`` (``webgpu/af3/trunk/single-attention.js:504``) fused
     with the block's pair-logits projection
@@ -597,13 +609,7 @@ class Af3SingleAttentionGpu:
         dev = self.device
         owned = None
         if not isinstance(weights, PreparedWeights):
-            att = weights["singleAttention"]
-            tensors = [att[k] for k in SINGLE_ATTENTION_AF3_ORDER]
-            tensors += [weights["singlePairLogitsNormScale"], weights["singlePairLogitsNormOffset"],
-                        weights["singlePairLogitsProjection"]]
-            owned = weights = PreparedWeights(dev, nat.WEIGHTS_SINGLE_ATTENTION_AF3,
-                                              {"channels": c, "heads": int(att["heads"]),
-                                               "head_dim": int(att["dimension"]), "pair_channels": pc}, tensors)
+            owned = weights = prepare_single_attention_weights(dev, weights, c, pc)
         try:
             s = _Buffer(single)
             p = _Buffer(pair)

@@ -371,8 +371,11 @@ class ShardedPairStack:
 class GpuShardOps:
     """Shard-local steps on the GPU through ``lf_pair_shard_step`` (16-bit tensor-core path)."""
 
-    def __init__(self, device, rows, length, ranks, variance="two-pass", epsilon=1e-5):
+    def __init__(self, device, rows, length, ranks, variance="two-pass", epsilon=1e-5, project_exchange="fused"):
+        """``project_exchange``: how the triangle operands reach their channel owners in the fused-exchange form -
+        "fused" (stores from the projection kernel's epilogue) or "copy" (a copy kernel after it)."""
         import torch
+        self.project_exchange = project_exchange
         self.torch = torch
         self.dev = device
         # the collectives and tensor operations between the steps run on torch's current stream
@@ -448,7 +451,14 @@ class GpuShardOps:
         self.dev.check(self.dev.lib.lf_pair_shard_exchange_step(self.dev.handle, ctypes.byref(d), ctypes.byref(ex.peers), None))
 
     def exchange_triangle_project(self, z, mask, w, ex, comm):
-        self._exchange_step(nat.SHARD_TRIANGLE_PROJECT, w, ex, z, mask)
+        if self.project_exchange == "fused":        # the projection's epilogue stores into the owners' planes
+            self._exchange_step(nat.SHARD_TRIANGLE_PROJECT, w, ex, z, mask)
+        else:                                       # projection into local planes, then one copy kernel per operand
+            self._step(nat.SHARD_TRIANGLE_PROJECT, w, z, mask, (self.a, self.b))
+            for local, table in ((self.a, ex.mapped[0]), (self.b, ex.mapped[1])):
+                dst = (ctypes.c_void_p * self.G)(*table)
+                self.dev.check(self.dev.lib.lf_pair_planes_scatter(self.dev.handle, local.data_ptr(), 128, self.R, self.N,
+                                                                   self.G, ex.rank, dst))
         ex.barrier()          # every rank's operand rows have landed in the channel owners' planes
 
     def exchange_triangle_contract(self, w, ex, comm, incoming):

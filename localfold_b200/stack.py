@@ -15,6 +15,7 @@ import numpy as np
 from . import _native as nat
 from .operators import (AttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, OuterProductMeanGpu,
                         PreparedWeights, TransitionGpu, _Buffer, _device, _precision, _variance,
+                        prepare_single_attention_weights,
                         SINGLE_ATTENTION_AF3_ORDER, TRANSITION_AF3_ORDER, TRANSITION_WEIGHT_ORDER,
                         prepare_attention_weights, prepare_grid_attention_weights,
                         prepare_triangle_weights)
@@ -178,12 +179,20 @@ class Af3PairformerStackGpu:
     """``Af3PairformerStackGpu.run(state, blocks, dialect, options)``
     (``webgpu/af3/trunk/pairformer-block.js:290-343``): per block the five pair
     updates, then single += singleAttention(single, pairLogits(pair)) and
-    single += transition(single) (``cpu/af3/trunk/pairformer.js:505-539``)."""
+    single += transition(single) (``cpu/af3/trunk/pairformer.js:505-539``).
+
+    The pair and the single representation stay on the device for the whole stack, as the
+    reference's ``pairBuffer`` / ``singleBuffer`` do (``pairformer-block.js:303-312``): host
+    arrays are uploaded once and read back once.  ``state["pair"]`` / ``state["single"]`` may
+    also be CUDA tensors (float32 or bfloat16 pair, float32 single), which are then updated in
+    place; ``options["keepPair"]`` returns the device tensors as ``pairTensor`` / ``singleTensor``
+    and skips the read-back; ``firstBlock`` starts in the middle of the stack."""
 
     def __init__(self, device=None):
         self.device = _device(device)
 
     def run(self, state, blocks, dialect, options=None):
+        import torch
         if dialect is None or dialect.get("swapTransposedBias") not in (True, False):
             raise ValueError("dialect.swapTransposedBias has no default")
         opts = dict(options or {})
@@ -191,27 +200,66 @@ class Af3PairformerStackGpu:
         n = int(state["tokens"])
         cz, cs = int(blocks[0]["pairChannels"]), int(blocks[0]["singleChannels"])
         first = int(opts.get("firstBlock", 0))
-        pair = np.array(state["pair"], np.float32, copy=True).reshape(n, n, cz)
-        single = None if state.get("single") is None else np.array(state["single"], np.float32, copy=True).reshape(n, cs)
-        stack = PairStackGpu(dev).prepare(blocks, cz, cz)
-        elapsed, launches = 0.0, 0
-        sub = {"precision": opts.get("precision", "f32"), "residual": True}
-        try:
-            for b in range(first, len(blocks)):
-                r = stack.run(pair, state["pairMask"], opts, first_block=b, n_blocks=1, dialect=dialect)
-                pair = r["pair"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-                if single is not None:
-                    w = blocks[b]
-                    r = Af3SingleAttentionGpu(dev).run(single, pair, state["seqMask"],
-                                                       {"n": n, "channels": cs, "pairChannels": cz}, w, sub)
-                    single = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-                    r = Af3TransitionGpu(dev).run(single, {"rows": n, "channels": cs, "factor": 4},
-                                                  w["singleTransition"], sub)
-                    single = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-                if opts.get("onBlockDone"):
-                    opts["onBlockDone"](b)
-        finally:
-            dev.synchronize()
-            stack.close()
-        return {"pair": pair, "single": single, "elapsedMilliseconds": elapsed,
-                "memory": {"peakBytes": 0}, "launches": launches}
+        where = f"cuda:{dev.ordinal}"
+
+        def resident(value, shape):
+            if value is None:
+                return None, False
+            if getattr(value, "is_cuda", False):
+                if tuple(value.shape) != shape and value.numel() != int(np.prod(shape)):
+                    raise nat.RangeError(f"state tensor has {value.numel()} values; expected {int(np.prod(shape))}")
+                return value.view(shape), True
+            host = np.ascontiguousarray(np.asarray(value, np.float32)).reshape(shape)
+            return torch.from_numpy(host).to(where), False
+
+        stream = torch.cuda.ExternalStream(dev.stream, device=where) if dev.stream else torch.cuda.default_stream(where)
+        with torch.cuda.stream(stream):       # uploads, the library's kernels and read-backs share one stream
+            pair, pair_given = resident(state["pair"], (n, n, cz))
+            single, single_given = resident(state.get("single"), (n, cs))
+            pair_mask, _ = resident(state["pairMask"], (n, n))
+            seq_mask = None
+            if single is not None:
+                seq_mask, _ = resident(state["seqMask"], (n,))
+            stack = PairStackGpu(dev).prepare(blocks, cz, cz)
+            single_w = []
+            if single is not None:       # resident weights of the single track, prepared before the first block runs
+                for b in range(first, len(blocks)):
+                    t = blocks[b]["singleTransition"]
+                    single_w.append((prepare_single_attention_weights(dev, blocks[b], cs, cz),
+                                     PreparedWeights(dev, nat.WEIGHTS_TRANSITION_AF3,
+                                                     {"channels": cs, "hidden": int(np.asarray(t["transition2"]).shape[0])},
+                                                     [t[k] for k in TRANSITION_AF3_ORDER])))
+            launches = 0
+            sub = {"precision": opts.get("precision", "f32"), "residual": True}
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            try:
+                for b in range(first, len(blocks)):
+                    r = stack.run(pair, pair_mask, opts, first_block=b, n_blocks=1, dialect=dialect)
+                    launches += r["launches"]
+                    if single is not None:
+                        att_w, trn_w = single_w[b - first]
+                        r = Af3SingleAttentionGpu(dev).run(single, pair, seq_mask, {"n": n, "channels": cs, "pairChannels": cz},
+                                                           att_w, sub)
+                        single.copy_(r["output"])
+                        launches += r["launches"]
+                        r = Af3TransitionGpu(dev).run(single, {"rows": n, "channels": cs, "factor": 4}, trn_w, sub, out=single)
+                        launches += r["launches"]
+                    if opts.get("onBlockDone"):
+                        opts["onBlockDone"](b)
+                stop.record(stream)
+                dev.synchronize()
+            finally:
+                dev.synchronize()
+                stack.close()
+                for pair_of in single_w:
+                    for w in pair_of:
+                        w.close()
+            elapsed = start.elapsed_time(stop)
+            out = {"elapsedMilliseconds": float(elapsed), "memory": {"peakBytes": 0}, "launches": launches}
+            if opts.get("keepPair"):
+                out.update(pair=None, single=None, pairTensor=pair, singleTensor=single)
+            else:
+                out["pair"] = pair if pair_given else pair.float().cpu().numpy()
+                out["single"] = None if single is None else (single if single_given else single.cpu().numpy())
+        return out

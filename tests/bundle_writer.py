@@ -61,6 +61,24 @@ def int5_payload(values):
     return body + scales.astype("<f2").tobytes() + zeros.astype("<f2").tobytes(), scale_offset, zero_offset
 
 
+def packed_payload(values, bits, group):
+    """Asymmetric ``bits``-bit codes at any whole-byte group (the delta bundles use int3 at 128): same scheme
+    as int5 with 2^bits - 1 levels."""
+    grid = _groups(values, group)
+    levels = (1 << bits) - 1
+    lo, hi = grid.min(axis=1), grid.max(axis=1)
+    zeros = lo.astype(np.float16)
+    scales = ((hi - lo) / np.float32(levels)).astype(np.float16)
+    step = scales.astype(np.float32)
+    step = np.where(step == 0, np.float32(1), step)
+    codes = np.clip(np.rint((grid - zeros.astype(np.float32)[:, None]) / step[:, None]), 0, levels).astype(np.uint8)
+    stream = (codes[:, :, None] >> np.arange(bits, dtype=np.uint8)) & 1
+    body = np.packbits(stream.reshape(codes.shape[0], -1), axis=1, bitorder="little").tobytes() + b"\0"
+    body += b"\0" * (-len(body) % 4)
+    scale_offset = len(body)
+    return body + scales.astype("<f2").tobytes() + zeros.astype("<f2").tobytes(), scale_offset, scale_offset + 2 * scales.size
+
+
 def int8_payload(values):
     """(payload bytes, scale offset) of one int8 tensor, symmetric, groups of 64."""
     grid = _groups(values, 64)
@@ -74,7 +92,7 @@ def int8_payload(values):
     return body + scales.astype("<f2").tobytes(), len(body)
 
 
-def write_bundle(directory, tensors, shard_bytes=64 << 20, model="synthetic", dtypes=None):
+def write_bundle(directory, tensors, shard_bytes=64 << 20, model="synthetic", dtypes=None, manifest_extra=None, prefix="weights"):
     """``manifest.json`` + ``weights-NN.int5.bin`` shards for a dict of named float32 arrays.  ``dtypes``
     optionally maps a name to "int5", "int8", "float16" or "float32"; by default names that the reference
     keeps in float32 stay float32 and every other tensor becomes int5."""
@@ -92,6 +110,9 @@ def write_bundle(directory, tensors, shard_bytes=64 << 20, model="synthetic", dt
         elif kind == "int8":
             payload, scale_offset = int8_payload(array)
             record.update(block=64, scaleOffset=scale_offset)
+        elif kind == "int3":
+            payload, scale_offset, zero_offset = packed_payload(array, 3, 128)
+            record.update(block=128, scaleOffset=scale_offset, zeroOffset=zero_offset)
         else:
             payload, scale_offset, zero_offset = int5_payload(array)
             record.update(block=32, scaleOffset=scale_offset, zeroOffset=zero_offset)
@@ -100,7 +121,7 @@ def write_bundle(directory, tensors, shard_bytes=64 << 20, model="synthetic", dt
             shards.append(bytes(blob))
             blob, start = bytearray(), 0
         blob.extend(b"\0" * (start - len(blob)))
-        record["file"] = f"weights-{len(shards):02d}.int5.bin"
+        record["file"] = f"{prefix}-{len(shards):02d}.int5.bin"
         record["byteOffset"] = start
         for key in ("scaleOffset", "zeroOffset"):
             if key in record:
@@ -109,13 +130,14 @@ def write_bundle(directory, tensors, shard_bytes=64 << 20, model="synthetic", dt
         records[name] = record
     shards.append(bytes(blob))
     for index, data in enumerate(shards):
-        with open(os.path.join(directory, f"weights-{index:02d}.int5.bin"), "wb") as f:
+        with open(os.path.join(directory, f"{prefix}-{index:02d}.int5.bin"), "wb") as f:
             f.write(data)
     manifest = {"formatVersion": 1, "model": model, "tensors": records,
                 "quantisation": {"scheme": "asymmetric-per-group", "bits": 5, "group": 32,
                                  "scaleDtype": "float16", "zeroDtype": "float16"},
                 "bundle": {"bytes": sum(map(len, shards)), "tensorCount": len(records)}}
-    path = os.path.join(directory, "manifest.json")
+    manifest.update(manifest_extra or {})
+    path = os.path.join(directory, "manifest.json" if prefix == "weights" else f"{prefix}-manifest.json")
     with open(path, "w") as f:
         json.dump(manifest, f)
     return path

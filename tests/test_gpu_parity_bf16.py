@@ -178,3 +178,30 @@ def test_af3_pairformer_block_bf16_int5_weights(dev):
                                              "tokens": n}, blocks, {"swapTransposedBias": True}, {"precision": "bf16"})
     assert oracle.relative_l2(got["pair"], wp) <= BLOCK_TOL
     assert oracle.relative_l2(got["single"], ws) <= BLOCK_TOL
+
+
+def test_af3_blocks_from_an_int5_bundle_on_disk(dev, tmp_path):
+    """The whole loading path: an int5 bundle under the AF3 exporter's tensor names (stacked ``[blocks, ...]``
+    tensors) is read with the device decoder, mapped to pairformer block weights and run; the oracle runs on
+    the weights the host decoder gives, which must be the same numbers bit for bit."""
+    import localfold_b200 as lf
+    from localfold_b200 import bundle
+    import bundle_writer as writer
+    from test_bundle_mapping import af3_bundle_tensors
+    n = 64
+    pair, single, pair_mask, seq_mask, blocks = syn.af3_pairformer(3, n, 128, 384, blocks=2)
+    path = writer.write_bundle(str(tmp_path), af3_bundle_tensors(blocks), shard_bytes=4 << 20)
+    on_device = bundle.pairformer_stack_weights(bundle.FileTensorStore(path, device=dev))
+    on_host = bundle.pairformer_stack_weights(bundle.FileTensorStore(path))
+    for a, b in zip(on_device, on_host):
+        for key in ("triangleMultiplicationOutgoing", "pairAttention2", "pairTransition", "singleAttention"):
+            for field, value in a[key].items():
+                if isinstance(value, np.ndarray):
+                    np.testing.assert_array_equal(value, b[key][field], err_msg=f"{key}/{field}")
+    wp, ws = pair, single
+    for w in on_host:
+        wp, ws = oracle.af3_pairformer_block(wp, ws, pair_mask, seq_mask, w, True)
+    got = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
+                                             "tokens": n}, on_device, {"swapTransposedBias": True}, {"precision": "bf16"})
+    assert oracle.relative_l2(got["pair"], wp) <= 2 * BLOCK_TOL
+    assert oracle.relative_l2(got["single"], ws) <= 2 * BLOCK_TOL
