@@ -99,6 +99,11 @@ LF_API uint64_t lf_context_launch_count(const lf_context* ctx);
  * timed regions; release returns it to the driver. */
 LF_API lf_status lf_context_reserve(lf_context* ctx, uint64_t bytes);
 LF_API void lf_context_release_scratch(lf_context* ctx);
+/* Upper bound on the scratch arena (0 = none): larger requests are refused with LF_ERR_MEMORY without
+ * asking the driver.  For hosts that budget device memory, and for exercising the paths that run when
+ * the device is short of memory (lf_pair_stack_run then leaves a host-space pair in the caller's buffer
+ * and streams it through the device in chunks of rows: see there). */
+LF_API lf_status lf_context_limit_scratch(lf_context* ctx, uint64_t bytes);
 LF_API const char* lf_version(void);
 
 /* Per-kernel timing, the counterpart of the reference's timestamp-query
@@ -176,6 +181,27 @@ typedef struct lf_weight_dims {
 LF_API lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,
                                    const float* const* tensors, const int64_t* counts,
                                    int32_t n_tensors, lf_weights** out);
+/* The same from tensors as a bundle stores them: int5 payloads (and float32 for what the exporters keep
+ * in float32 - norms, offsets, biases) go to the device as they are, and one kernel decodes the codes
+ * straight into the resident weight arrays in the layout the operator's kernels use - the transposes,
+ * interleaves and column placements of lf_weights_create applied on the device.  No float32 copy of a
+ * quantised weight is made on the host.  Stands where the reference decodes on the device with its
+ * transpose / interleave maps (webgpu/weights/quantised-upload.js:100-120).  Tensor order and counts are
+ * those of lf_weights_create.  An int5 tensor is given by the bytes of its (group-aligned) range: the
+ * codes of whole groups of `block`, then - anywhere after them - one fp16 scale and one fp16 zero point
+ * per group at the two offsets; value = code * scale + zero (shared/weights/dtype.js:330-378). */
+typedef enum lf_tensor_encoding { LF_TENSOR_F32 = 0, LF_TENSOR_INT5 = 1 } lf_tensor_encoding;
+typedef struct lf_encoded_tensor {
+  int32_t dtype;               /* lf_tensor_encoding */
+  int32_t block;               /* int5: codes per group (32) */
+  const void* data;            /* host memory: `count` float32 values, or the int5 payload */
+  int64_t count;               /* elements */
+  uint64_t payload_bytes;      /* int5: bytes at `data` */
+  uint64_t scale_offset;       /* int5: byte offsets of the scales and of the zero points inside the payload */
+  uint64_t zero_offset;
+} lf_encoded_tensor;
+LF_API lf_status lf_weights_create_encoded(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,
+                                           const lf_encoded_tensor* tensors, int32_t n_tensors, lf_weights** out);
 LF_API void lf_weights_destroy(lf_weights* w);
 
 /* ---- int5 tensor decode ------------------------------------------------- */
@@ -312,7 +338,21 @@ LF_API lf_status lf_single_attention_run(lf_context* ctx, const lf_single_attent
  * for AF3 weights).  Runs blocks [first_block, first_block + n_blocks) of the
  * `blocks` table on the same pair, which is what EvoformerStackGpu /
  * ExtraMsaPairStackGpu / Af3PairformerStackGpu do with a resident pair
- * (webgpu/af2/evoformer/stack.js:44-163, webgpu/af3/trunk/pairformer-block.js:290-343). */
+ * (webgpu/af2/evoformer/stack.js:44-163, webgpu/af3/trunk/pairformer-block.js:290-343).
+ *
+ * Host-space calls whose pair does not fit on the device beside the operators' scratch (the arena is
+ * refused) do not fail: in the 16-bit mode with cZ = cHidden = 128, 4 heads and a length that is a
+ * multiple of 16 the pair stays in the caller's buffer (pinned for the call) and streams through the
+ * device in chunks of rows - columns for the ending-node attention - with one cudaMemcpyAsync /
+ * cudaMemcpy2DAsync per chunk and direction, double-buffered against the kernels; only the fp16
+ * triangle operands and the pair bias stay resident.  This stands where the reference has its host
+ * spill and row-chunked pair track (webgpu/runtime/host-spill.js:13-78,
+ * webgpu/af3/trunk/pair-track.js:967-1000).  Results are those of the resident path. */
+/* Order of the five updates inside a block.  EVOFORMER: triangle out, triangle in, attention start,
+ * attention end, transition (main and extra-MSA stacks, AF3 pair track).  TEMPLATE: attention start,
+ * attention end, triangle out, triangle in, transition - the template pair stack, which is the same
+ * block at 64 channels (encodeTemplatePairBlock: webgpu/af2/evoformer/block.js:1746-1781). */
+typedef enum lf_pair_block_order { LF_ORDER_EVOFORMER = 0, LF_ORDER_TEMPLATE = 1 } lf_pair_block_order;
 typedef struct lf_pair_block_weights {
   const lf_weights* triangle_outgoing;
   const lf_weights* triangle_incoming;
@@ -330,6 +370,7 @@ typedef struct lf_pair_stack_desc {
   const float* mask;           /* [length, length] */
   const lf_pair_block_weights* blocks;
   int32_t block_count, first_block, n_blocks;
+  int32_t order;               /* lf_pair_block_order */
 } lf_pair_stack_desc;
 LF_API lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_result* r);
 

@@ -6,7 +6,7 @@ eager fallback - a missing library raises on first use.
 """
 from .operators import (  # noqa: F401
     Af3GridSelfAttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, AttentionGpu, Device,
-    OuterProductMeanGpu, PreparedWeights, RangeError, TransitionGpu,
+    EncodedTensor, OuterProductMeanGpu, PreparedWeights, RangeError, TransitionGpu,
     TriangleMultiplicationIncomingGpu, TriangleMultiplicationOutgoingGpu,
     af3_triangle_multiplication, create_device, error_metrics, int5_decode, validate_triangle_input,
 )

@@ -15,6 +15,7 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 PRECISION_F32, PRECISION_BF16 = 0, 1
 VARIANCE_TWO_PASS, VARIANCE_FAST = 1, 2
 PAIR_BIAS_NONE, PAIR_BIAS_SEPARATE, PAIR_BIAS_NORMALIZED_INPUT = 0, 1, 2
+ORDER_EVOFORMER, ORDER_TEMPLATE = 0, 1
 (WEIGHTS_TRIANGLE_AF2, WEIGHTS_TRIANGLE_AF3, WEIGHTS_ATTENTION_AF2, WEIGHTS_GRID_ATTENTION_AF3,
  WEIGHTS_TRANSITION_AF2, WEIGHTS_TRANSITION_AF3, WEIGHTS_OPM_AF2, WEIGHTS_SINGLE_ATTENTION_AF3) = range(1, 9)
 
@@ -90,7 +91,7 @@ class PairStackDesc(ctypes.Structure):
                 ("swap_transposed_bias", c_int32), ("epsilon", c_float), ("space", c_int32),
                 ("act_dtype", c_int32), ("pair", c_void_p), ("mask", c_void_p),
                 ("blocks", ctypes.POINTER(PairBlockWeights)), ("block_count", c_int32),
-                ("first_block", c_int32), ("n_blocks", c_int32)]
+                ("first_block", c_int32), ("n_blocks", c_int32), ("order", c_int32)]
 
 
 (SHARD_TRIANGLE_PROJECT, SHARD_TRIANGLE_CONTRACT, SHARD_TRIANGLE_OUTPUT, SHARD_ATTENTION_PROJECT,
@@ -103,6 +104,14 @@ class ShardStepDesc(ctypes.Structure):
                 ("mask", c_void_p), ("buf", c_void_p * 6), ("weights", c_void_p)]
 
 
+class EncodedTensorDesc(ctypes.Structure):
+    _fields_ = [("dtype", c_int32), ("block", c_int32), ("data", c_void_p), ("count", c_int64),
+                ("payload_bytes", ctypes.c_uint64), ("scale_offset", ctypes.c_uint64), ("zero_offset", ctypes.c_uint64)]
+
+
+TENSOR_F32, TENSOR_INT5 = 0, 1
+
+
 class ShardPeers(ctypes.Structure):
     _fields_ = [("rank", c_int32), ("incoming", c_int32), ("a", c_void_p * 16), ("b", c_void_p * 16),
                 ("x", c_void_p * 16), ("bias", c_void_p * 16)]
@@ -110,7 +119,7 @@ class ShardPeers(ctypes.Structure):
 
 EXPORTS = (
     "lf_version", "lf_context_create", "lf_context_create_on_stream", "lf_context_stream", "lf_context_destroy", "lf_last_error", "lf_context_synchronize",
-    "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_weights_create",
+    "lf_context_launch_count", "lf_context_profile", "lf_context_profile_read", "lf_context_reserve", "lf_context_release_scratch", "lf_context_limit_scratch", "lf_weights_create", "lf_weights_create_encoded",
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_pair_stack_run",
@@ -145,11 +154,14 @@ def load():
     lib.lf_context_profile_read.argtypes = [c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double),
                                             ctypes.POINTER(ctypes.c_uint64)]
     lib.lf_context_reserve.argtypes = [c_void_p, ctypes.c_uint64]
+    lib.lf_context_limit_scratch.argtypes = [c_void_p, ctypes.c_uint64]
     lib.lf_context_release_scratch.argtypes = [c_void_p]
     lib.lf_context_release_scratch.restype = None
     lib.lf_weights_create.argtypes = [c_void_p, ctypes.c_int, ctypes.POINTER(WeightDims),
                                       ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_int32,
                                       ctypes.POINTER(c_void_p)]
+    lib.lf_weights_create_encoded.argtypes = [c_void_p, ctypes.c_int, ctypes.POINTER(WeightDims),
+                                              ctypes.POINTER(EncodedTensorDesc), c_int32, ctypes.POINTER(c_void_p)]
     lib.lf_weights_destroy.argtypes = [c_void_p]
     lib.lf_weights_destroy.restype = None
     lib.lf_int5_decode.argtypes = [c_void_p, c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "lib", "liblocalfold_pairstack.so")
-SOURCES = ("api.cu", "tc_kernels.cu", "tc_ln_gemm.cu", "tc_attention.cu", "tc_transition.cu", "static_scratch.cu", "peer_transpose.cu")
+SOURCES = ("api.cu", "tc_kernels.cu", "tc_ln_gemm.cu", "tc_attention.cu", "tc_transition.cu", "static_scratch.cu", "peer_transpose.cu", "pair_spill.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",

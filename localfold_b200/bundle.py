@@ -152,6 +152,27 @@ class FileTensorStore:
         raw = memoryview(blob)[start:]
         return decode_packed_host(raw, bits, block, g0, g1 - g0, scales, zeros)[lo:lo + count]
 
+    def tensor_source(self, name, first, count, shape=None):
+        """The stored bytes of a range, for decoding on the device: an ``EncodedTensor`` when the tensor is int5
+        and the range starts on a group boundary (and ends on one, or at the tensor's end); otherwise the decoded
+        float32 values (``tensorSource`` of the reference's stores: ``shared/bundles/alphafold-fixture.js:75-100``)."""
+        from .operators import EncodedTensor
+        record = self.record(name)
+        elements = int(np.prod(record["shape"])) if record["shape"] else 1
+        block = record.get("block")
+        shape = (count,) if shape is None else shape
+        if record["dtype"] != "int5" or first % block or not (count % block == 0 or first + count == elements):
+            return self.tensor_range(name, first, count).reshape(shape)
+        blob = self._bytes(record["file"])
+        start = record.get("byteOffset", 0)
+        g0, g1 = first // block, (first + count + block - 1) // block
+        group_bytes = block * BITS // 8
+        codes = blob[start + g0 * group_bytes:start + g1 * group_bytes] + b"\0"
+        codes += b"\0" * (-len(codes) % 4)
+        scales = blob[record["scaleOffset"] + 2 * g0:record["scaleOffset"] + 2 * g1]
+        zeros = blob[record["zeroOffset"] + 2 * g0:record["zeroOffset"] + 2 * g1]
+        return EncodedTensor(codes + scales + zeros, len(codes), len(codes) + len(scales), count, shape, block)
+
     def _int5_on_device(self, blob, record, start, g0, g1, count, block):
         """A group-aligned range through ``lf_int5_decode``: the codes of groups g0..g1 with their scales and
         zeros, laid out as a payload of their own."""
@@ -225,13 +246,16 @@ class DeltaTensorStore:
 # bundle tensors -> weight objects
 
 
-def stacked(store, name, index):
+def stacked(store, name, index, encoded=False):
     """Block ``index`` of a tensor stacked along its first axis, shaped as one block
-    (``stacked``: ``shared/af3/weights/weights.js:154-184``)."""
+    (``stacked``: ``shared/af3/weights/weights.js:154-184``).  ``encoded``: hand over the stored bytes
+    (``EncodedTensor``) where the store can, for decoding on the device."""
     shape = store.shape(name)
     if index >= shape[0]:
         raise IndexError(f"{name} has {shape[0]} blocks; asked for {index}")
     stride = int(np.prod(shape[1:])) if len(shape) > 1 else 1
+    if encoded and hasattr(store, "tensor_source"):
+        return store.tensor_source(name, index * stride, stride, tuple(shape[1:]))
     return store.tensor_range(name, index * stride, stride).reshape(shape[1:])
 
 
@@ -341,12 +365,12 @@ class AlphaFoldFixture:
         return result
 
 
-def pair_track(store, root, index):
+def pair_track(store, root, index, encoded=False):
     """The five pair-track modules of block ``index`` of an AF3-lineage stack (``pairTrack``:
     ``shared/af3/weights/weights.js:402-454``).  Heads and head dimension of the grid attention come from its
     own ``q_projection/weights`` ``[blocks, heads, dimension, channels]``; a block without
     ``pair_attention1`` (a PairMixer block) has no grid attention fields."""
-    at = lambda leaf: stacked(store, f"{root}/{leaf}", index)
+    at = lambda leaf: stacked(store, f"{root}/{leaf}", index, encoded)
     has = lambda leaf: store.has(f"{root}/{leaf}")
     out = {}
     for direction in ("outgoing", "incoming"):
@@ -376,15 +400,15 @@ def pair_track(store, root, index):
     return out
 
 
-def pairformer_block_weights(store, index, root=PAIRFORMER):
+def pairformer_block_weights(store, index, root=PAIRFORMER, encoded=False):
     """``pairformerBlockWeights`` (``shared/af3/weights/weights.js:699-727``): block ``index`` of a pairformer
     stack.  The four widths come from the tensors: ``single_attention_q_projection/weights`` is
     ``[blocks, singleChannels, heads, dimension]`` and ``single_pair_logits_norm/scale`` ``[blocks, pairChannels]``."""
-    at = lambda leaf: stacked(store, f"{root}/{leaf}", index)
+    at = lambda leaf: stacked(store, f"{root}/{leaf}", index, encoded)
     _, single_channels, heads, dimension = store.shape(f"{root}/single_attention_q_projection/weights")
     _, pair_channels = store.shape(f"{root}/single_pair_logits_norm/scale")
     out = {"pairChannels": int(pair_channels), "singleChannels": int(single_channels)}
-    out.update(pair_track(store, root, index))
+    out.update(pair_track(store, root, index, encoded))
     out.update({
         "singlePairLogitsNormScale": at("single_pair_logits_norm/scale"),
         "singlePairLogitsNormOffset": at("single_pair_logits_norm/offset"),
@@ -404,7 +428,9 @@ def pairformer_block_weights(store, index, root=PAIRFORMER):
     return out
 
 
-def pairformer_stack_weights(store, root=PAIRFORMER):
-    """Every block of a pairformer stack (block count from the stacked leading axis)."""
+def pairformer_stack_weights(store, root=PAIRFORMER, encoded=False):
+    """Every block of a pairformer stack (block count from the stacked leading axis).  ``encoded``: int5 tensors
+    stay encoded (``EncodedTensor``) and are decoded on the device when the operators prepare their weights
+    (the reference's on-device decode: ``webgpu/weights/quantised-upload.js:100-120``)."""
     blocks = store.shape(f"{root}/single_pair_logits_norm/scale")[0]
-    return [pairformer_block_weights(store, b, root) for b in range(blocks)]
+    return [pairformer_block_weights(store, b, root, encoded) for b in range(blocks)]

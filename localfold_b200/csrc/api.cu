@@ -5,6 +5,7 @@
 
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 #include "simt_kernels.cuh"
@@ -30,6 +31,8 @@ static void profile_collect(lf_context* ctx) {
 
 
 lf_status lf_arena_ensure(lf_context* ctx, size_t bytes) {
+  if (ctx->arena_limit && bytes > ctx->arena_limit)
+    return lf_fail(ctx, LF_ERR_MEMORY, "scratch arena of %zu bytes exceeds the limit of %zu bytes set for this context", bytes, ctx->arena_limit);
   if (bytes <= ctx->arena_bytes) return LF_OK;
   // Work that still reads the old arena must finish before it is freed.
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -144,6 +147,12 @@ lf_status lf_context_reserve(lf_context* ctx, uint64_t bytes) {
   if (!ctx) return LF_ERR_ARGUMENT;
   cudaSetDevice(ctx->device);
   return lf_arena_ensure(ctx, (size_t)bytes);
+}
+
+lf_status lf_context_limit_scratch(lf_context* ctx, uint64_t bytes) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  ctx->arena_limit = (size_t)bytes;
+  return LF_OK;
 }
 
 void lf_context_release_scratch(lf_context* ctx) {
@@ -439,6 +448,106 @@ lf_status build_opm_af2(lf_context* ctx, lf_weights* w, const float* const* t, c
 
 }  // namespace
 
+// Lays the operator's tensors out in the canonical arrays (staged on the host in g_pending).
+static lf_status build_weights(lf_context* ctx, lf_weights* w, const float* const* tensors, const int64_t* counts, int n_tensors) {
+  switch (w->kind) {
+    case LF_WEIGHTS_TRIANGLE_AF2: return build_triangle_af2(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_TRIANGLE_AF3: return build_triangle_af3(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_ATTENTION_AF2: return build_attention_af2(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_GRID_ATTENTION_AF3: return build_grid_attention_af3(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_SINGLE_ATTENTION_AF3: return build_single_attention_af3(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_TRANSITION_AF2: return build_transition(ctx, w, tensors, counts, n_tensors, false);
+    case LF_WEIGHTS_TRANSITION_AF3: return build_transition(ctx, w, tensors, counts, n_tensors, true);
+    case LF_WEIGHTS_OPM_AF2: return build_opm_af2(ctx, w, tensors, counts, n_tensors);
+    default: return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown weight kind %d", w->kind);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Weights from encoded tensors (int5 payloads as they sit in a bundle): the codes go to the device as they
+// are and one gather kernel decodes them straight into the canonical arrays, through a layout map that says,
+// for every element of every canonical array, which input tensor and which of its elements it is (or that it
+// is a constant zero).  The map is derived from the very functions that lay out float32 inputs, by running
+// them on stand-in tensors that hold their own element numbers, so the two paths cannot disagree; it
+// depends only on the operator's kind and shape and is cached per device.
+
+namespace {
+
+constexpr int kMaxSources = 16;
+struct SourceTable {
+  const uint8_t* base[kMaxSources];
+  const __half* scales[kMaxSources];
+  const __half* zeros[kMaxSources];
+  int block[kMaxSources];           // 0 = float32 values
+};
+
+__global__ void gather_decode_kernel(const int32_t* __restrict__ map, int64_t count, const __grid_constant__ SourceTable src,
+                                     float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const int32_t tensor = map[2 * i], index = map[2 * i + 1];
+  float v = 0.f;
+  if (tensor >= 0) {
+    const int block = src.block[tensor];
+    if (block == 0) {
+      v = reinterpret_cast<const float*>(src.base[tensor])[index];
+    } else {
+      const int g = index / block, bit = (index - g * block) * 5;
+      const uint8_t* codes = src.base[tensor] + (size_t)g * (block * 5 / 8);
+      const unsigned two = codes[bit >> 3] | ((unsigned)codes[(bit >> 3) + 1] << 8);
+      v = fmaf((float)((two >> (bit & 7)) & 31u), __half2float(src.scales[tensor][g]), __half2float(src.zeros[tensor][g]));
+    }
+  }
+  out[i] = v;
+}
+
+struct LayoutMaps {
+  std::vector<std::vector<int32_t>> slot;      // per canonical array: (tensor, element) pairs; tensor -1 = zero
+  lf_weights flags;                            // what the layout functions set besides the arrays
+  int32_t* device[64] = {nullptr};             // per device ordinal: all slots' maps, one after the other
+};
+std::mutex g_maps_mutex;
+std::map<std::vector<int64_t>, LayoutMaps> g_maps;
+
+// Runs the layout functions once per input tensor, that tensor holding 1, 2, 3, ... and the others zeros: a
+// canonical element that comes out as v > 0 is element v - 1 of that tensor.
+lf_status derive_maps(lf_context* ctx, int kind, const lf_weight_dims& dims, const int64_t* counts, int n, LayoutMaps& maps) {
+  std::vector<std::vector<float>> fake(n);
+  std::vector<const float*> ptr(n);
+  for (int i = 0; i < n; ++i) {
+    if (counts[i] >= (1 << 24)) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "tensor %d has %lld elements; encoded tensors are limited to 16777215", i, (long long)counts[i]);
+    fake[i].assign((size_t)counts[i], 0.f);
+    ptr[i] = counts[i] ? fake[i].data() : nullptr;
+  }
+  for (int i = 0; i < n; ++i) {
+    if (!counts[i]) continue;
+    for (int64_t e = 0; e < counts[i]; ++e) fake[i][(size_t)e] = (float)(e + 1);
+    lf_weights tmp;
+    tmp.kind = kind;
+    tmp.dims = dims;
+    g_pending.items.clear();
+    lf_status s = build_weights(ctx, &tmp, ptr.data(), counts, n);
+    if (s != LF_OK) { g_pending.items.clear(); return s; }
+    if (maps.slot.empty()) {
+      maps.slot.resize(tmp.f.size());
+      for (auto& it : g_pending.items) maps.slot[it.slot].assign(it.data.size() * 2, -1);
+      maps.flags = tmp;
+      maps.flags.f.clear();
+    }
+    for (auto& it : g_pending.items) {
+      auto& m = maps.slot[it.slot];
+      for (size_t e = 0; e < it.data.size(); ++e)
+        if (it.data[e] > 0.f) { m[2 * e] = i; m[2 * e + 1] = (int32_t)it.data[e] - 1; }
+    }
+    g_pending.items.clear();
+    std::fill(fake[i].begin(), fake[i].end(), 0.f);
+  }
+  if (maps.slot.empty()) return lf_fail(ctx, LF_ERR_ARGUMENT, "no tensor has any element");
+  return LF_OK;
+}
+
+}  // namespace
+
 // Host copy of a tensor of the operator being created (valid inside lf_weights_create only).
 const float* lf_weights_staged_host(int slot) {
   for (auto& it : g_pending.items)
@@ -461,21 +570,116 @@ lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weigh
   w->ctx = ctx;
   w->kind = (int)kind;
   w->dims = *dims;
-  lf_status s;
-  switch (kind) {
-    case LF_WEIGHTS_TRIANGLE_AF2: s = build_triangle_af2(ctx, w, tensors, counts, n_tensors); break;
-    case LF_WEIGHTS_TRIANGLE_AF3: s = build_triangle_af3(ctx, w, tensors, counts, n_tensors); break;
-    case LF_WEIGHTS_ATTENTION_AF2: s = build_attention_af2(ctx, w, tensors, counts, n_tensors); break;
-    case LF_WEIGHTS_GRID_ATTENTION_AF3: s = build_grid_attention_af3(ctx, w, tensors, counts, n_tensors); break;
-    case LF_WEIGHTS_SINGLE_ATTENTION_AF3: s = build_single_attention_af3(ctx, w, tensors, counts, n_tensors); break;
-    case LF_WEIGHTS_TRANSITION_AF2: s = build_transition(ctx, w, tensors, counts, n_tensors, false); break;
-    case LF_WEIGHTS_TRANSITION_AF3: s = build_transition(ctx, w, tensors, counts, n_tensors, true); break;
-    case LF_WEIGHTS_OPM_AF2: s = build_opm_af2(ctx, w, tensors, counts, n_tensors); break;
-    default: s = lf_fail(ctx, LF_ERR_ARGUMENT, "unknown weight kind %d", (int)kind);
-  }
+  lf_status s = build_weights(ctx, w, tensors, counts, n_tensors);
   if (s == LF_OK) s = finish_uploads(ctx, w);
   if (s == LF_OK) s = tc::prepare_weights(ctx, w);
   g_pending.items.clear();
+  if (s != LF_OK) { lf_weights_destroy(w); return s; }
+  *out = w;
+  return LF_OK;
+}
+
+lf_status lf_weights_create_encoded(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,
+                                    const lf_encoded_tensor* tensors, int32_t n_tensors, lf_weights** out) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!dims || !tensors || !out) return lf_fail(ctx, LF_ERR_ARGUMENT, "lf_weights_create_encoded: null argument");
+  *out = nullptr;
+  if (dims->channels <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "channels must be a positive integer; received %d", dims->channels);
+  if (n_tensors <= 0 || n_tensors > kMaxSources) return lf_fail(ctx, LF_ERR_ARGUMENT, "expected 1 to %d tensors; received %d", kMaxSources, n_tensors);
+  if (ctx->device < 0 || ctx->device >= 64) return lf_fail(ctx, LF_ERR_ARGUMENT, "device ordinal %d is out of range", ctx->device);
+  std::vector<int64_t> counts(n_tensors);
+  size_t input_bytes = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    const lf_encoded_tensor& t = tensors[i];
+    counts[i] = t.count;
+    if (t.count < 0 || (t.count > 0 && !t.data)) return lf_fail(ctx, LF_ERR_ARGUMENT, "tensor %d is null", i);
+    if (t.dtype == LF_TENSOR_F32) input_bytes += lf_align_up((size_t)t.count * 4 + 4, 256);
+    else if (t.dtype == LF_TENSOR_INT5) {
+      if (t.block <= 0 || (t.block * 5) % 8) return lf_fail(ctx, LF_ERR_ARGUMENT, "tensor %d: group %d of 5 bits does not pack into whole bytes", i, t.block);
+      const uint64_t groups = ((uint64_t)t.count + t.block - 1) / t.block, code_bytes = groups * (t.block * 5 / 8) + 1;
+      if (t.scale_offset < code_bytes || t.scale_offset % 2 || t.zero_offset % 2 || t.scale_offset + groups * 2 > t.payload_bytes ||
+          t.zero_offset + groups * 2 > t.payload_bytes)
+        return lf_fail(ctx, LF_ERR_SHAPE, "tensor %d: int5 payload of %llu bytes does not hold %lld codes, scales and zeros", i,
+                       (unsigned long long)t.payload_bytes, (long long)t.count);
+      input_bytes += lf_align_up((size_t)t.payload_bytes + 4, 256);
+    } else return lf_fail(ctx, LF_ERR_ARGUMENT, "tensor %d has unknown encoding %d", i, t.dtype);
+  }
+  cudaSetDevice(ctx->device);
+
+  // the layout map of this kind and shape
+  std::vector<int64_t> key = {(int64_t)kind, dims->channels, dims->hidden, dims->heads, dims->head_dim, dims->pair_channels, dims->out_channels};
+  key.insert(key.end(), counts.begin(), counts.end());
+  LayoutMaps* maps = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    auto found = g_maps.find(key);
+    if (found == g_maps.end()) {
+      LayoutMaps fresh;
+      LF_TRY(derive_maps(ctx, (int)kind, *dims, counts.data(), n_tensors, fresh));
+      found = g_maps.emplace(key, std::move(fresh)).first;
+    }
+    maps = &found->second;
+    if (!maps->device[ctx->device]) {
+      size_t total = 0;
+      for (auto& m : maps->slot) total += m.size();
+      int32_t* dev = nullptr;
+      LF_CUDA(ctx, cudaMalloc(&dev, (total ? total : 1) * sizeof(int32_t)));
+      size_t at = 0;
+      for (auto& m : maps->slot) {
+        if (!m.empty()) LF_CUDA(ctx, cudaMemcpyAsync(dev + at, m.data(), m.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        at += m.size();
+      }
+      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      maps->device[ctx->device] = dev;      // kept for the life of the process: one per operator shape
+    }
+  }
+
+  // inputs to the device as they are (scratch arena), canonical arrays in one allocation
+  LF_TRY(lf_arena_ensure(ctx, input_bytes));
+  ArenaCursor cur{ctx, 0, false};
+  SourceTable table{};
+  for (int i = 0; i < n_tensors; ++i) {
+    const lf_encoded_tensor& t = tensors[i];
+    if (!t.count) continue;
+    const size_t bytes = t.dtype == LF_TENSOR_F32 ? (size_t)t.count * 4 : (size_t)t.payload_bytes;
+    uint8_t* dev = cur.take<uint8_t>(bytes + 4);
+    LF_CUDA(ctx, cudaMemcpyAsync(dev, t.data, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    table.base[i] = dev;
+    if (t.dtype == LF_TENSOR_INT5) {
+      table.block[i] = t.block;
+      table.scales[i] = reinterpret_cast<const __half*>(dev + t.scale_offset);
+      table.zeros[i] = reinterpret_cast<const __half*>(dev + t.zero_offset);
+    }
+  }
+  lf_weights* w = new lf_weights();
+  w->ctx = ctx;
+  w->kind = (int)kind;
+  w->dims = maps->flags.dims;
+  w->has_gate_bias = maps->flags.has_gate_bias; w->has_out_bias = maps->flags.has_out_bias;
+  w->has_pair_norm = maps->flags.has_pair_norm; w->has_pair_proj = maps->flags.has_pair_proj;
+  w->f.assign(maps->slot.size(), nullptr);
+  size_t total = 0;
+  std::vector<size_t> offset;
+  for (auto& m : maps->slot) { offset.push_back(total); total += lf_align_up(m.size() / 2 * sizeof(float) + 4, 256); }
+  char* base = nullptr;
+  cudaError_t e = cudaMalloc(&base, total ? total : 256);
+  if (e != cudaSuccess) { cudaGetLastError(); delete w; return lf_fail(ctx, LF_ERR_MEMORY, "weight allocation of %zu bytes refused: %s", total, cudaGetErrorString(e)); }
+  w->owned.push_back(base);
+  size_t at = 0;
+  for (size_t sl = 0; sl < maps->slot.size(); ++sl) {
+    const int64_t count = (int64_t)maps->slot[sl].size() / 2;
+    float* dst = reinterpret_cast<float*>(base + offset[sl]);
+    if (count) {
+      gather_decode_kernel<<<lf_ceil_div(count, 256), 256, 0, ctx->stream>>>(maps->device[ctx->device] + at, count, table, dst);
+      ctx->launches++;
+    }
+    w->f[sl] = dst;
+    at += maps->slot[sl].size();
+  }
+  lf_status s = cudaGetLastError() == cudaSuccess ? LF_OK : lf_fail(ctx, LF_ERR_CUDA, "weight decode launch failed");
+  g_pending.items.clear();                 // nothing is staged on the host: the repacks read the device arrays
+  if (s == LF_OK) s = tc::prepare_weights(ctx, w);
+  if (s == LF_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) s = lf_fail(ctx, LF_ERR_CUDA, "weight decode failed");   // the caller's payloads may go
   if (s != LF_OK) { lf_weights_destroy(w); return s; }
   *out = w;
   return LF_OK;
@@ -1005,6 +1209,7 @@ lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_res
   if (d->first_block < 0 || d->n_blocks < 0 || d->first_block + d->n_blocks > d->block_count)
     return lf_fail(ctx, LF_ERR_ARGUMENT, "blocks [%d, %d) are outside the table of %d", d->first_block, d->first_block + d->n_blocks, d->block_count);
   LF_TRY(check_common(ctx, d->variance, d->precision, d->space, d->act_dtype, d->epsilon));
+  if (d->order != LF_ORDER_EVOFORMER && d->order != LF_ORDER_TEMPLATE) return lf_fail(ctx, LF_ERR_ARGUMENT, "unknown block order %d", d->order);
   if (d->c_z % d->heads != 0) return lf_fail(ctx, LF_ERR_SHAPE, "cZ %d is not a multiple of heads %d", d->c_z, d->heads);
   for (int b = d->first_block; b < d->first_block + d->n_blocks; ++b) {
     const lf_pair_block_weights& bw = d->blocks[b];
@@ -1019,7 +1224,7 @@ lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_res
   const bool host = d->space == LF_SPACE_HOST;
   const int n = d->length, cz = d->c_z;
   const size_t P = (size_t)n * n, es = dtype_size(d->act_dtype);
-  return run_with_arena(ctx, r, host, [&](ArenaCursor& cur) -> lf_status {
+  const lf_status status = run_with_arena(ctx, r, host, [&](ArenaCursor& cur) -> lf_status {
     Staging st{ctx, &cur, host};
     void* pair = host ? st.out(d->pair, P * cz * es) : d->pair;
     if (host && !cur.dry) cudaMemcpyAsync(pair, d->pair, P * cz * es, cudaMemcpyHostToDevice, ctx->stream);
@@ -1027,25 +1232,33 @@ lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_res
     const size_t scratch_base = cur.offset;
     for (int b = d->first_block; b < d->first_block + d->n_blocks; ++b) {
       const lf_pair_block_weights& bw = d->blocks[b];
-      for (int dir = 0; dir < 2; ++dir) {
-        cur.offset = scratch_base;
-        TriArgs a{n, cz, d->c_hidden, dir, d->variance, 1, 0, d->epsilon, d->act_dtype, pair, mask, pair,
-                  dir ? bw.triangle_incoming : bw.triangle_outgoing};
-        LF_TRY(tri_dispatch(ctx, cur, a, d->precision));
-      }
-      for (int t = 0; t < 2; ++t) {
-        cur.offset = scratch_base;
-        const lf_weights* w = t ? bw.attention_ending : bw.attention_starting;
-        const bool af3 = w->kind == LF_WEIGHTS_GRID_ATTENTION_AF3;
-        AttArgs a{};
-        a.batch = n; a.Q = n; a.ch = cz; a.heads = d->heads; a.d = w->dims.head_dim; a.transpose = t;
-        a.variance = d->variance; a.residual = 1; a.bias_mode = 2;
-        a.bias_swap = (af3 && t && !d->swap_transposed_bias) ? 1 : 0;
-        a.mask_mode = af3 ? 1 : 0; a.clamp = af3 ? 0 : 1; a.eps = d->epsilon; a.pair_eps = d->epsilon;
-        a.pair_variance = d->variance; a.act_dtype = d->act_dtype; a.pair_dtype = d->act_dtype;
-        a.act = pair; a.mask = mask; a.out = pair; a.w = w;
-        LF_TRY(att_dispatch(ctx, cur, a, d->precision));
-      }
+      auto triangles = [&]() -> lf_status {
+        for (int dir = 0; dir < 2; ++dir) {
+          cur.offset = scratch_base;
+          TriArgs a{n, cz, d->c_hidden, dir, d->variance, 1, 0, d->epsilon, d->act_dtype, pair, mask, pair,
+                    dir ? bw.triangle_incoming : bw.triangle_outgoing};
+          LF_TRY(tri_dispatch(ctx, cur, a, d->precision));
+        }
+        return LF_OK;
+      };
+      auto attentions = [&]() -> lf_status {
+        for (int t = 0; t < 2; ++t) {
+          cur.offset = scratch_base;
+          const lf_weights* w = t ? bw.attention_ending : bw.attention_starting;
+          const bool af3 = w->kind == LF_WEIGHTS_GRID_ATTENTION_AF3;
+          AttArgs a{};
+          a.batch = n; a.Q = n; a.ch = cz; a.heads = d->heads; a.d = w->dims.head_dim; a.transpose = t;
+          a.variance = d->variance; a.residual = 1; a.bias_mode = 2;
+          a.bias_swap = (af3 && t && !d->swap_transposed_bias) ? 1 : 0;
+          a.mask_mode = af3 ? 1 : 0; a.clamp = af3 ? 0 : 1; a.eps = d->epsilon; a.pair_eps = d->epsilon;
+          a.pair_variance = d->variance; a.act_dtype = d->act_dtype; a.pair_dtype = d->act_dtype;
+          a.act = pair; a.mask = mask; a.out = pair; a.w = w;
+          LF_TRY(att_dispatch(ctx, cur, a, d->precision));
+        }
+        return LF_OK;
+      };
+      if (d->order == LF_ORDER_TEMPLATE) { LF_TRY(attentions()); LF_TRY(triangles()); }
+      else { LF_TRY(triangles()); LF_TRY(attentions()); }
       cur.offset = scratch_base;
       TrnArgs a{(int64_t)P, cz, d->transition_hidden, bw.transition->kind == LF_WEIGHTS_TRANSITION_AF3 ? 1 : 0, d->variance, 1,
                 d->epsilon, d->act_dtype, pair, pair, bw.transition};
@@ -1054,6 +1267,9 @@ lf_status lf_pair_stack_run(lf_context* ctx, const lf_pair_stack_desc* d, lf_res
     st.flush();
     return LF_OK;
   });
+  // The device cannot hold the pair beside the operators' scratch: leave the pair in the caller's buffer and stream it through in chunks.
+  if (status == LF_ERR_MEMORY && host) return lf_pair_stack_spilled(ctx, d, r);
+  return status;
 }
 
 lf_status lf_pair_shard_step(lf_context* ctx, const lf_shard_step_desc* d, lf_result* r) {

@@ -30,6 +30,7 @@ struct lf_context {
   size_t arena_bytes = 0;
   size_t arena_used = 0;
   size_t arena_peak = 0;
+  size_t arena_limit = 0;      // 0 = none; otherwise requests above it are refused without asking the driver (lf_context_limit_scratch)
   uint64_t launches = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int sm_count = 148;
@@ -119,6 +120,8 @@ struct ArenaCursor {
 };
 
 lf_status lf_arena_ensure(lf_context* ctx, size_t bytes);
+// The pair stack with the pair left in host memory (pair_spill.cu).
+lf_status lf_pair_stack_spilled(lf_context* ctx, const lf_pair_stack_desc* d, lf_result* r);
 // Host copy of a tensor (slot of lf_weights::f) of the operator being created; null outside lf_weights_create.
 const float* lf_weights_staged_host(int slot);
 

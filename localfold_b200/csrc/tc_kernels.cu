@@ -97,6 +97,24 @@ lf_status check_status(lf_context* ctx) {
 
 bool ln_gemm_supported(const lf_weights* w) { return w && !w->h.empty() && w->h[0] != nullptr; }
 
+// The centre LayerNorm folded into the output projection: W' = diag(gain) Wz, s1[c] = sum_h fp16(W'[h][c]) (what the
+// tensor core will multiply the mean by), t[c] = bz[c] + sum_h offset[h] Wz[h][c]; fold = (s1 | t | bg).
+__global__ void triangle_fold_kernel(const float* __restrict__ wz, const float* __restrict__ gain, const float* __restrict__ offset,
+                                     const float* __restrict__ bz, const float* __restrict__ bg, float* __restrict__ wfold,
+                                     float* __restrict__ fold) {
+  const int c = threadIdx.x;
+  double s1 = 0.0, t = bz[c];
+  for (int h = 0; h < 128; ++h) {
+    const float wf = gain[h] * wz[h * 128 + c];
+    wfold[h * 128 + c] = wf;
+    s1 += (double)__half2float(__float2half_rn(wf));
+    t += (double)offset[h] * wz[h * 128 + c];
+  }
+  fold[c] = (float)s1;
+  fold[128 + c] = (float)t;
+  fold[256 + c] = bg[c];
+}
+
 // bf16/fp16 repacks for the tensor-core kernels: h[0] = swizzled fp16 image of the fused
 // projection W^T (plus the pair-bias projection rows for attention), h[1] = its bias vector.
 lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
@@ -111,30 +129,11 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->h.assign(4, nullptr);
     w->h[0] = img;
     // output kernel: rows 0..127 = (diag(gain) Wz)^T, rows 128..255 = Wg^T, plus the folded vectors
-    // (the operator's tensors are still staged on the host while it is being created)
-    const float *wz = lf_weights_staged_host(TRI_WZ), *g = lf_weights_staged_host(TRI_LNO_G), *b = lf_weights_staged_host(TRI_LNO_B),
-                *bz = lf_weights_staged_host(TRI_BZ), *bg = lf_weights_staged_host(TRI_BG);
-    if (!wz || !g || !b || !bz || !bg) return lf_fail(ctx, LF_ERR_ARGUMENT, "triangle weights are not staged");
-    std::vector<float> fold(384);
-    std::vector<float> wfold(128 * 128);
-    for (int cc = 0; cc < 128; ++cc) {
-      double s1 = 0, t = bz[cc];
-      for (int h = 0; h < 128; ++h) {
-        const float wf = g[h] * wz[h * 128 + cc];
-        wfold[h * 128 + cc] = wf;
-        s1 += (double)__half2float(__float2half_rn(wf));   // what the tensor core will multiply by
-        t += (double)b[h] * wz[h * 128 + cc];
-      }
-      fold[cc] = (float)s1;
-      fold[128 + cc] = (float)t;
-      fold[256 + cc] = bg[cc];
-    }
     float* dfold = nullptr; float* dw = nullptr; op16* img2 = nullptr;
-    LF_CUDA(ctx, cudaMalloc(&dfold, fold.size() * 4)); w->owned.push_back(dfold);
-    LF_CUDA(ctx, cudaMalloc(&dw, wfold.size() * 4)); w->owned.push_back(dw);
+    LF_CUDA(ctx, cudaMalloc(&dfold, 384 * 4)); w->owned.push_back(dfold);
+    LF_CUDA(ctx, cudaMalloc(&dw, 128 * 128 * 4)); w->owned.push_back(dw);
     LF_CUDA(ctx, cudaMalloc(&img2, 256 * 256)); w->owned.push_back(img2);
-    LF_CUDA(ctx, cudaMemcpyAsync(dfold, fold.data(), fold.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
-    LF_CUDA(ctx, cudaMemcpyAsync(dw, wfold.data(), wfold.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    triangle_fold_kernel<<<1, 128, 0, ctx->stream>>>(w->f[TRI_WZ], w->f[TRI_LNO_G], w->f[TRI_LNO_B], w->f[TRI_BZ], w->f[TRI_BG], dw, dfold);
     pack_weight_image(ctx, dw, 128, 128, 256, 0, 128, img2, 0, 1.0f);
     pack_weight_image(ctx, w->f[TRI_WG], 128, 128, 256, 0, 128, img2, 128, 1.0f);
     LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -156,9 +155,14 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     pack_weight_image(ctx, w->f[ATT_W4], 128, 384, 528, 128, 512, img, 128, 1.0f);
     if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512, 1.0f);
     {
-      const float* staged = lf_weights_staged_host(ATT_B4);
-      if (!staged) return lf_fail(ctx, LF_ERR_ARGUMENT, "attention weights are not staged");
-      std::vector<float> hb(staged, staged + 512);
+      // the fused projection's bias vector: from the host copy staged while the operator is created, or (weights
+      // decoded on the device) read back - 2 KiB of values that bundles keep in float32 anyway
+      std::vector<float> hb(512);
+      if (const float* staged = lf_weights_staged_host(ATT_B4)) std::copy(staged, staged + 512, hb.begin());
+      else {
+        LF_CUDA(ctx, cudaMemcpyAsync(hb.data(), w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+        LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      }
       for (int i = 0; i < 128; ++i) hb[i] *= qs;
       w->bias_flags = 0;
       for (int grp = 0; grp < 4; ++grp)

@@ -58,15 +58,19 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);
 // The same for a row shard: its bias rows are written into every rank's copy of the whole bias
-// [heads][bias_rows][ldb] at query rows row0 .. row0 + batch.
+// [heads][bias_rows][ldb] at query rows row0 .. row0 + batch.  `transpose`: the shard is held as [Q][batch]
+// (logical row (b, q) at memory row q*batch + b), as for a block of columns of the pair.
 lf_status attention_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                                     int variance, float eps, int heads, const lf_weights* w, op16* q, op16* k, op16* v,
-                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb);
+                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb,
+                                    int transpose = 0);
 lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,
                            const lf_weights* w, const void* resid, void* out, int act_dtype);
+// `x_plane_elems`: distance between the channel planes of x (0 = rows * ld, a dense shard; n * ld when x points at
+// `rows` rows inside whole planes)
 lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int rows, int n, int ld, float x_eps,
                           const void* z, int act_dtype, int variance, float eps, const lf_weights* w, const void* resid,
-                          void* out);
+                          void* out, int64_t x_plane_elems = 0);
 // out[b*Q+i][128] = (softmax_j(q_i.k_j + bias[h][i][j] + mask term_j) v_j) * gate, 4 heads x 32
 void configure_attention();
 // `bias`: fp16 [4][Q][ldb] (head, query, key; ldb a multiple of 16) or null

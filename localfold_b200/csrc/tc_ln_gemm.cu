@@ -50,7 +50,7 @@ struct LnGemmParams {
   op16* out_b;
   int n, ld;                // pair row length and operand row stride
   int plane_rows;           // pair rows held (n for a whole pair, fewer for a row shard)
-  // channel-sharded destinations (peer_ranks > 1): channel h goes to rank h / ch_per_rank, plane h % ch_per_rank of
+  // channel-sharded destinations (peer_ranks >= 1; one rank = rows inside whole planes of this device): channel h goes to rank h / ch_per_rank, plane h % ch_per_rank of
   // its [ch_per_rank][peer_plane_rows][ld] buffer, at rows peer_row0 + local row; stores go to the peers' memory
   int peer_ranks, ch_per_rank, peer_plane_rows, peer_row0;
   PeerPtrs peer_a, peer_b;
@@ -447,7 +447,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
           const int h = row;
           const float bias_p = sBias[j * 256 + h], bias_g = sBias[j * 256 + 128 + h];
           op16* plane_base;
-          if (p.peer_ranks > 1) {
+          if (p.peer_ranks >= 1) {
             const int owner = h / p.ch_per_rank;
             plane_base = reinterpret_cast<op16*>(j == 0 ? p.peer_a.p[owner] : p.peer_b.p[owner]) +
                          ((int64_t)(h - owner * p.ch_per_rank) * p.peer_plane_rows + p.peer_row0) * p.ld;
@@ -787,8 +787,9 @@ lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, 
 
 lf_status attention_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                                     int variance, float eps, int heads, const lf_weights* w, op16* q, op16* k, op16* v,
-                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb) {
-  return attention_project_impl(ctx, cur, act, act_dtype, batch, Q, 0, variance, eps, heads, 0, w, q, k, v, g,
+                                    op16* g, const PeerPtrs& bias_peers, int ranks, int bias_rows, int row0, int ldb,
+                                    int transpose) {
+  return attention_project_impl(ctx, cur, act, act_dtype, batch, Q, transpose, variance, eps, heads, 0, w, q, k, v, g,
                                 (op16*)bias_peers.p[0], ldb, &bias_peers, ranks, bias_rows, row0);
 }
 
@@ -855,10 +856,11 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
 // out = resid + (LN_c(x) Wz + bz) * sigmoid(LN(z) Wg + bg); x is [128][n][ld] fp16 stored scaled by xscale
 lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int rows, int n, int ld, float x_eps,
                           const void* z, int act_dtype, int variance, float eps, const lf_weights* w, const void* resid,
-                          void* out) {
+                          void* out, int64_t x_plane_elems) {
   if (cur.dry) return LF_OK;
   CUtensorMap mapX;
-  LF_TRY(make_map_f16_3d_box(ctx, &mapX, x, n, rows, 128, (uint64_t)ld * 2, (uint64_t)rows * ld * 2, 64, 1, 128));
+  LF_TRY(make_map_f16_3d_box(ctx, &mapX, x, n, rows, 128, (uint64_t)ld * 2,
+                             (uint64_t)(x_plane_elems ? x_plane_elems : (int64_t)rows * ld) * 2, 64, 1, 128));
   LnGemmParams p{};
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;

@@ -115,6 +115,11 @@ class Device:
     def reserve(self, nbytes: int):
         self.check(self.lib.lf_context_reserve(self.handle, int(nbytes)))
 
+    def limit_scratch(self, nbytes: int):
+        """Upper bound on the scratch arena (0 = none); a host-space pair stack that needs more keeps the pair
+        in host memory and streams it through the device in chunks."""
+        self.check(self.lib.lf_context_limit_scratch(self.handle, int(nbytes)))
+
     def release_scratch(self):
         self.lib.lf_context_release_scratch(self.handle)
 
@@ -138,26 +143,68 @@ def _device(device):
     return _default_device
 
 
+class EncodedTensor:
+    """A tensor as a bundle stores it: the bytes of an int5 range (the codes of whole groups, then fp16 scales and
+    zero points at the two offsets) with its element count and shape.  Handed to the operators in place of a
+    float32 array, it goes to the device as it is and is decoded there, straight into the operator's resident
+    weight layout (``lf_weights_create_encoded``); ``decode()`` gives the float32 values on the host, for
+    reference arithmetic."""
+
+    def __init__(self, payload: bytes, scale_offset: int, zero_offset: int, count: int, shape, block: int = 32):
+        self.payload = bytes(payload)
+        self.scale_offset, self.zero_offset, self.count, self.block = int(scale_offset), int(zero_offset), int(count), int(block)
+        self.shape = tuple(int(v) for v in shape)
+
+    @property
+    def size(self):
+        return self.count
+
+    def decode(self):
+        from .bundle import decode_int5_host
+        return decode_int5_host(self.payload, self.scale_offset, self.zero_offset, self.count, self.block).reshape(self.shape)
+
+    def __array__(self, dtype=None, copy=None):
+        out = self.decode()
+        return out if dtype is None else out.astype(dtype)
+
+
 class PreparedWeights:
-    """Device-resident weights of one operator (``lf_weights``)."""
+    """Device-resident weights of one operator (``lf_weights``).  Tensors are float32 arrays or
+    ``EncodedTensor``s; with any of the latter the codes are decoded on the device."""
 
     def __init__(self, device: Device, kind: int, dims: dict, tensors):
         self.device = device
         self.kind = kind
         self.dims = dict(dims)
-        arrays = []
-        for t in tensors:
-            if t is None:
-                arrays.append(np.zeros(0, np.float32))
-            else:
-                arrays.append(np.ascontiguousarray(np.asarray(t, dtype=np.float32)).reshape(-1))
-        n = len(arrays)
-        ptrs = (ctypes.c_void_p * n)(*[a.ctypes.data if a.size else None for a in arrays])
-        counts = (ctypes.c_int64 * n)(*[a.size for a in arrays])
         wd = nat.WeightDims(**{k: int(v) for k, v in dims.items()})
         handle = ctypes.c_void_p()
-        device.check(device.lib.lf_weights_create(device.handle, kind, ctypes.byref(wd), ptrs, counts, n,
-                                                   ctypes.byref(handle)))
+        if any(isinstance(t, EncodedTensor) for t in tensors):
+            n = len(tensors)
+            descs = (nat.EncodedTensorDesc * n)()
+            keep = []
+            for d, t in zip(descs, tensors):
+                if isinstance(t, EncodedTensor):
+                    raw = np.frombuffer(t.payload, np.uint8)
+                    keep.append(raw)
+                    d.dtype, d.block, d.data, d.count = nat.TENSOR_INT5, t.block, raw.ctypes.data, t.count
+                    d.payload_bytes, d.scale_offset, d.zero_offset = raw.size, t.scale_offset, t.zero_offset
+                else:
+                    a = np.zeros(0, np.float32) if t is None else np.ascontiguousarray(np.asarray(t, dtype=np.float32)).reshape(-1)
+                    keep.append(a)
+                    d.dtype, d.block, d.data, d.count = nat.TENSOR_F32, 0, (a.ctypes.data if a.size else None), a.size
+            device.check(device.lib.lf_weights_create_encoded(device.handle, kind, ctypes.byref(wd), descs, n, ctypes.byref(handle)))
+        else:
+            arrays = []
+            for t in tensors:
+                if t is None:
+                    arrays.append(np.zeros(0, np.float32))
+                else:
+                    arrays.append(np.ascontiguousarray(np.asarray(t, dtype=np.float32)).reshape(-1))
+            n = len(arrays)
+            ptrs = (ctypes.c_void_p * n)(*[a.ctypes.data if a.size else None for a in arrays])
+            counts = (ctypes.c_int64 * n)(*[a.size for a in arrays])
+            device.check(device.lib.lf_weights_create(device.handle, kind, ctypes.byref(wd), ptrs, counts, n,
+                                                       ctypes.byref(handle)))
         self.handle = handle
         self._finalizer = weakref.finalize(self, device.lib.lf_weights_destroy, handle)
 

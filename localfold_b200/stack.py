@@ -35,7 +35,7 @@ class PreparedPairBlock:
             self.att_end = prepare_grid_attention_weights(device, w["pairAttention2"], c_z)
             self.heads = int(w["pairAttention1"]["heads"])
             t = w["pairTransition"]
-            self.transition_hidden = np.asarray(t["transition2"]).shape[0]
+            self.transition_hidden = int(t["transition2"].shape[0])
             self.transition = PreparedWeights(device, nat.WEIGHTS_TRANSITION_AF3,
                                               {"channels": c_z, "hidden": self.transition_hidden},
                                               [t[k] for k in TRANSITION_AF3_ORDER])
@@ -82,7 +82,9 @@ class PairStackGpu:
 
     def run(self, pair, mask, options=None, first_block=0, n_blocks=None, dialect=None, inplace=False):
         """Updates ``pair`` (device tensor: in place; numpy: returns a new array, or
-        updates the given float32 array when ``inplace``)."""
+        updates the given float32 array when ``inplace``).  ``options["order"] = "template"`` runs each block
+        in the template pair stack's order (attention start, end, triangle out, in, transition:
+        ``encodeTemplatePairBlock``, ``webgpu/af2/evoformer/block.js:1746-1781``)."""
         opts = options or {}
         dev = self.device
         c_z, c_hidden = self.shape
@@ -113,7 +115,8 @@ class PairStackGpu:
                                  _variance(opts, "fast" if af3 else "two-pass"), _precision(opts), swap,
                                  float(opts.get("epsilon") or 1e-5),
                                  nat.SPACE_DEVICE if p.is_device else nat.SPACE_HOST, target.dtype,
-                                 target.ptr, m.ptr, self._table, len(self.blocks), first_block, count)
+                                 target.ptr, m.ptr, self._table, len(self.blocks), first_block, count,
+                                 nat.ORDER_TEMPLATE if opts.get("order") == "template" else nat.ORDER_EVOFORMER)
         res = nat.Result()
         dev.check(dev.lib.lf_pair_stack_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
         return {"pair": output, "elapsedMilliseconds": float(res.elapsed_ms),
@@ -227,7 +230,7 @@ class Af3PairformerStackGpu:
                     t = blocks[b]["singleTransition"]
                     single_w.append((prepare_single_attention_weights(dev, blocks[b], cs, cz),
                                      PreparedWeights(dev, nat.WEIGHTS_TRANSITION_AF3,
-                                                     {"channels": cs, "hidden": int(np.asarray(t["transition2"]).shape[0])},
+                                                     {"channels": cs, "hidden": int(t["transition2"].shape[0])},
                                                      [t[k] for k in TRANSITION_AF3_ORDER])))
             launches = 0
             sub = {"precision": opts.get("precision", "f32"), "residual": True}

@@ -308,6 +308,21 @@ def af2_pair_block(pair, pair_mask, w, c_hidden, eps=1e-5, stages=None):
     return pair
 
 
+def af2_template_pair_block(pair, pair_mask, w, c_hidden, eps=1e-5):
+    """The template pair stack's block: the same five updates with the attentions first
+    (``encodeTemplatePairBlock``: ``webgpu/af2/evoformer/block.js:1746-1781``)."""
+    pair = np.array(pair, np.float32, copy=True)
+    n, _, cz = pair.shape
+    for key, transpose in (("triangleAttentionStarting", False), ("triangleAttentionEnding", True)):
+        t = w[key]
+        pair = pair + attention_af2(pair, pair_mask, n, n, cz, t["heads"], t["attention"], transpose,
+                                    dict(t["pairBias"], source="normalized-input"), eps).reshape(pair.shape)
+    pair = pair + trimul_af2(pair, pair_mask, w["triangleMultiplicationOutgoing"], c_hidden, eps, False)
+    pair = pair + trimul_af2(pair, pair_mask, w["triangleMultiplicationIncoming"], c_hidden, eps, True)
+    t = w["pairTransition"]
+    return pair + transition_af2(pair, t, t["firstBias"].shape[0], eps)
+
+
 def af2_evoformer_block(msa, pair, msa_mask, pair_mask, w, c_outer, c_hidden, eps=1e-5):
     """Whole AF2 Evoformer block (``webgpu/af2/evoformer/block.js:1546-1612``)."""
     msa = np.array(msa, np.float32, copy=True)

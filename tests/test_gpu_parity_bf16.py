@@ -51,15 +51,38 @@ def test_triangle_bf16_af3_channels_64(dev):
         assert oracle.relative_l2(got, want) <= OP_TOL
 
 
-def test_af2_pair_block_bf16(dev):
+@pytest.mark.parametrize("n", [64, 300])
+def test_af2_pair_block_bf16(dev, n):
     import localfold_b200 as lf
-    n = 64
-    pair, mask, weights = syn.af2_pair_block(0, n, masked_tail=0.05)
+    from parity_report import record
+    pair, mask, weights = syn.af2_pair_block(n - 64, n, masked_tail=0.05)
     want = oracle.af2_pair_block(pair, mask, weights[0], 128)
     stack = lf.PairStackGpu(dev).prepare(weights, 128, 128)
     got = stack.run(pair, mask, {"precision": "bf16", "variance": "two-pass"})
     stack.close()
-    assert oracle.relative_l2(got["pair"], want) <= BLOCK_TOL
+    err = oracle.relative_l2(got["pair"], want)
+    record("af2_pair_block", f"n={n}", err, BLOCK_TOL)
+    assert err <= BLOCK_TOL
+
+
+def test_af2_pair_block_bf16_at_the_metric_length(dev):
+    """N = 384, the shorter of the two lengths the metric names: the whole block against the float64
+    formulation (the scalar oracle takes tens of seconds there), at the per-block bound."""
+    import localfold_b200 as lf
+    from oracle import tier2_torch as t2
+    from parity_report import record
+    n = 384
+    pair, mask, weights = syn.af2_pair_block(384, n, masked_tail=0.05)
+    want = t2.af2_pair_block(pair, mask, weights[0])
+    stack = lf.PairStackGpu(dev).prepare(weights, 128, 128)
+    got = stack.run(pair, mask, {"precision": "bf16", "variance": "two-pass"})
+    f32 = stack.run(pair, mask, {"precision": "f32", "variance": "two-pass"})
+    stack.close()
+    err = oracle.relative_l2(got["pair"], want)
+    record("af2_pair_block", "n=384 vs float64", err, BLOCK_TOL)
+    record("af2_pair_block", "n=384 f32 mode vs float64", oracle.relative_l2(f32["pair"], want), 1e-5)
+    assert err <= BLOCK_TOL
+    assert oracle.relative_l2(f32["pair"], want) <= 1e-5
 
 
 @pytest.mark.parametrize("n", [64, 77, 260])
@@ -205,3 +228,15 @@ def test_af3_blocks_from_an_int5_bundle_on_disk(dev, tmp_path):
                                              "tokens": n}, on_device, {"swapTransposedBias": True}, {"precision": "bf16"})
     assert oracle.relative_l2(got["pair"], wp) <= 2 * BLOCK_TOL
     assert oracle.relative_l2(got["single"], ws) <= 2 * BLOCK_TOL
+    # and with the int5 tensors left encoded: the codes go to the device and are decoded there, straight into the
+    # operators' weight layout - the same weights, so the same result
+    encoded = bundle.pairformer_stack_weights(bundle.FileTensorStore(path), encoded=True)
+    assert isinstance(encoded[0]["pairTransition"]["transition1"], lf.EncodedTensor)
+    assert isinstance(encoded[0]["pairTransition"]["inputLayerNormScale"], np.ndarray)       # kept float32 by the exporter
+    again = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
+                                               "tokens": n}, encoded, {"swapTransposedBias": True}, {"precision": "bf16"})
+    np.testing.assert_array_equal(again["pair"], got["pair"])
+    np.testing.assert_array_equal(again["single"], got["single"])
+    f32 = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
+                                             "tokens": n}, encoded, {"swapTransposedBias": True}, {"precision": "f32"})
+    assert oracle.relative_l2(f32["pair"], wp) <= 2e-5

@@ -255,3 +255,21 @@ def test_shape_errors_name_the_tensor(dev):
                                                        "z": pair, "mask": mask, "weights": bad})
     with pytest.raises(ValueError, match="swapTransposedBias"):
         lf.Af3GridSelfAttentionGpu(dev).run(pair, mask, {"n": 8, "channels": 128}, {}, {})
+
+
+@pytest.mark.parametrize("precision,tol", [("f32", 1e-5), ("bf16", 2e-3)])
+def test_template_pair_stack_order_and_width(dev, precision, tol):
+    """The template pair stack: the same block at 64 channels with the attentions first
+    (``webgpu/af2/evoformer/block.js:1746-1781``; widths: ``shared/bundles/alphafold-fixture.js:418-451``)."""
+    import localfold_b200 as lf
+    n, cz = 40, 64
+    pair, mask, weights = syn.af2_pair_block(90, n, cz, cz, 4, blocks=2, masked_tail=0.1)
+    want = pair
+    for w in weights:
+        want = oracle.af2_template_pair_block(want, mask, w, cz)
+    other = oracle.af2_pair_block(pair, mask, weights[0], cz)
+    stack = lf.PairStackGpu(dev).prepare(weights, cz, cz)
+    got = stack.run(pair, mask, {"precision": precision, "variance": "two-pass", "order": "template"})
+    stack.close()
+    assert oracle.relative_l2(got["pair"], want) <= tol
+    assert oracle.relative_l2(want, oracle.af2_pair_block(other, mask, weights[1], cz)) > 1e-3      # the order matters
