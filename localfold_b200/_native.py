@@ -7,7 +7,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "liblocalfold_pairstack.so")
+# the in-tree build; LOCALFOLD_PAIRSTACK_LIB points at another build of the same ABI (e.g. a variant being measured)
+LIB_PATH = os.environ.get("LOCALFOLD_PAIRSTACK_LIB") or os.path.join(HERE, "lib", "liblocalfold_pairstack.so")
 
 LF_OK, LF_ERR_SHAPE, LF_ERR_ARGUMENT, LF_ERR_CUDA, LF_ERR_MEMORY, LF_ERR_UNSUPPORTED, LF_ERR_TIMEOUT = range(7)
 SPACE_HOST, SPACE_DEVICE = 0, 1

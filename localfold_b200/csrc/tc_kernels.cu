@@ -83,6 +83,21 @@ lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base,
   return LF_OK;
 }
 
+// float32 rows of 128 channels as a 2-d map (channel, row) with boxes of 16 channels x 32 rows (64-byte rows,
+// 64-byte swizzle): the staging tiles of the transition's output
+lf_status make_map_f32_rows16(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t rows) {
+  if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {128, rows};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {16, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled (float32 rows, 16 channels) failed with code %d", (int)r);
+  return LF_OK;
+}
+
 lf_status check_status(lf_context* ctx) {
   if (!ctx->tc_status) return LF_OK;
   Status st;

@@ -520,17 +520,23 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
                 float4* cell = reinterpret_cast<float4*>(stage + ((uint32_t)((half * 4 + k4) ^ (lane & 7)) << 4));
-                const float* bias = sBias + c0 + k4 * 4;
+                // per-channel vectors are the same for every lane: 16-byte broadcasts, not scalar reads
+                const float4 b0v = *reinterpret_cast<const float4*>(sBias + c0 + k4 * 4);
+                const float b0[4] = {b0v.x, b0v.y, b0v.z, b0v.w};
                 float e4[4];
+                if (EPI == LG_EPI_TRI_OUT) {
+                  const float4 b1v = *reinterpret_cast<const float4*>(sBias + 128 + c0 + k4 * 4);
+                  const float4 b2v = *reinterpret_cast<const float4*>(sBias + 256 + c0 + k4 * 4);
+                  const float b1[4] = {b1v.x, b1v.y, b1v.z, b1v.w}, b2[4] = {b2v.x, b2v.y, b2v.z, b2v.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  if (EPI == LG_EPI_TRI_OUT) {
+                  for (int e = 0; e < 4; ++e) {
                     // (x - mean) * inv folded: inv * acc - inv*mean * s1[c] + t[c], gated
-                    const float lin = fmaf(rs, __uint_as_float(v1[k4 * 4 + e]), fmaf(-rm, bias[e], bias[128 + e]));
-                    e4[e] = lin * sigmoid_fast(__uint_as_float(v2[k4 * 4 + e]) + bias[256 + e]);
-                  } else {
-                    e4[e] = __uint_as_float(v1[k4 * 4 + e]) + bias[e];
+                    const float lin = fmaf(rs, __uint_as_float(v1[k4 * 4 + e]), fmaf(-rm, b0[e], b1[e]));
+                    e4[e] = lin * sigmoid_fast(__uint_as_float(v2[k4 * 4 + e]) + b2[e]);
                   }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) e4[e] = __uint_as_float(v1[k4 * 4 + e]) + b0[e];
                 }
                 float4 o = make_float4(e4[0], e4[1], e4[2], e4[3]);
                 if (p.resid) { const float4 rr = *cell; o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
@@ -562,16 +568,25 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
             tmem_ld_wait();
             if (valid) {
               float o[16];
+              float b0[16];
+#pragma unroll
+              for (int e4 = 0; e4 < 4; ++e4) *reinterpret_cast<float4*>(b0 + e4 * 4) = *reinterpret_cast<const float4*>(sBias + c0 + e4 * 4);
               if (EPI == LG_EPI_TRI_OUT) {
+                float b1[16], b2[16];
+#pragma unroll
+                for (int e4 = 0; e4 < 4; ++e4) {
+                  *reinterpret_cast<float4*>(b1 + e4 * 4) = *reinterpret_cast<const float4*>(sBias + 128 + c0 + e4 * 4);
+                  *reinterpret_cast<float4*>(b2 + e4 * 4) = *reinterpret_cast<const float4*>(sBias + 256 + c0 + e4 * 4);
+                }
                 // (x - mean) * inv folded: inv * acc - inv*mean * s1[c] + t[c], gated
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                  const float lin = fmaf(rs, __uint_as_float(v1[e]), fmaf(-rm, sBias[c0 + e], sBias[128 + c0 + e]));
-                  o[e] = lin * sigmoid_fast(__uint_as_float(v2[e]) + sBias[256 + c0 + e]);
+                  const float lin = fmaf(rs, __uint_as_float(v1[e]), fmaf(-rm, b0[e], b1[e]));
+                  o[e] = lin * sigmoid_fast(__uint_as_float(v2[e]) + b2[e]);
                 }
               } else {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v1[e]) + sBias[c0 + e];
+                for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v1[e]) + b0[e];
               }
               if (p.out_bf16) {
                 bf16* op = reinterpret_cast<bf16*>(p.out) + dst * 128 + c0;

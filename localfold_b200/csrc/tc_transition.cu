@@ -24,6 +24,7 @@ constexpr int TR_ROWS = 128;
 constexpr int TR_TILE_BYTES = TR_ROWS * 128 * 2;   // 32 KiB: 128 rows x 128 fp16, two k-atoms
 constexpr int TR_W_STAGE = 2 * TR_TILE_BYTES;      // AF2: W1 slice (32 KiB) + W2 slice (32 KiB); AF3: 32 KiB + 16 KiB
 constexpr int TR_SMEM = 2 * TR_W_STAGE + 2 * TR_TILE_BYTES + (1024 + 128 + 256) * 4 + 256 + 1024;
+constexpr int TR_OUT_STAGE = 32 * 64;              // per epilogue warp: 32 rows x 16 float32 channels of the pair
 
 struct TransitionParams {
   const void* act;
@@ -36,6 +37,7 @@ struct TransitionParams {
   const float* b2;          // [128]
   const void* resid;
   void* out;
+  int tma_out;              // float32 pair updated in place (or no residual): the pair tile travels by TMA through staging rows
   Status* status;
 };
 
@@ -52,7 +54,7 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 
 template <bool SWIGLU>
-__global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const TransitionParams p) {
+__global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_constant__ CUtensorMap mapO, const TransitionParams p) {
   constexpr int TR_CHUNKS = SWIGLU ? 8 : 4;                 // hidden chunks per tile
   constexpr int HK = SWIGLU ? 64 : 128;                     // hidden channels per chunk = K of the second GEMM
   constexpr uint32_t W_BYTES = SWIGLU ? 3 * TR_TILE_BYTES / 2 : 2 * TR_TILE_BYTES;   // bytes streamed per chunk
@@ -76,7 +78,8 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
   uint64_t* h_empty = bars + 11;      // MMA commit: GEMM 2 has read the hidden tile
   uint64_t* out_full = bars + 12;     // MMA commit
   uint64_t* out_empty = bars + 13;    // count 16
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* stage_free = bars + 14;   // count 16: every warp's output copy has finished reading the staging rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,6 +89,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
     mbar_init(a_full, 8); mbar_init(a_empty, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); mbar_init(&hacc_full[s], 1); mbar_init(&hacc_empty[s], 16); }
     mbar_init(h_full, 16); mbar_init(h_empty, 1); mbar_init(out_full, 1); mbar_init(out_empty, 16);
+    mbar_init(stage_free, 16);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -117,7 +121,14 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
     const int pw = warp - 16;
     const int sub = lane >> 3, j = lane & 7;
     int it = 0;
+    const uint32_t row_bytes = p.act_bf16 ? 256u : 512u;
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
+      if (pw == 0 && lane == 0 && t + gridDim.x < tiles) {
+        // ask for the next tile's rows now: they arrive in L2 while this tile is normalised and multiplied
+        const int64_t r0 = (t + gridDim.x) * TR_ROWS;
+        const int64_t nrows = p.rows - r0 < TR_ROWS ? p.rows - r0 : TR_ROWS;
+        bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.act) + r0 * row_bytes, (uint32_t)nrows * row_bytes);
+      }
       if (!mbar_wait(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
 #pragma unroll 1
       for (int grp = 0; grp < 2; ++grp) {
@@ -229,7 +240,6 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
       };
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
         if (!mbar_wait(a_full, it & 1, abort_flag, p.status, 52)) break;
-        if (!mbar_wait(out_empty, (it & 1) ^ 1, abort_flag, p.status, 53)) break;
         tc_fence_after();
         for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
           const int s = g & 1;
@@ -251,6 +261,8 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
           if (c >= 1) {
             // second GEMM of the previous chunk, once its hidden tile is in shared memory
             if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 56)) { ok = false; break; }
+            // the tile's first write of the output accumulator: the previous tile's must have been read
+            if (c == 1 && !mbar_wait(out_empty, (it & 1) ^ 1, abort_flag, p.status, 53)) { ok = false; break; }
             tc_fence_after();
             if (elect_one()) {
               gemm2(g - 1, c - 1);
@@ -295,8 +307,13 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
           tmem_ld16(tmem_base + lane_addr + s * 128 + part * 16, gt);
           tmem_ld16(tmem_base + lane_addr + s * 128 + 64 + part * 16, vl);
           tmem_ld_wait();
-          const float* bg = sB1 + c * 64 + part * 16;
-          const float* bv = sB1 + 512 + c * 64 + part * 16;
+          // the biases are the same for every lane: read as four 16-byte broadcasts, not sixteen scalars
+          float bg[16], bv[16];
+#pragma unroll
+          for (int e4 = 0; e4 < 4; ++e4) {
+            *reinterpret_cast<float4*>(bg + e4 * 4) = *reinterpret_cast<const float4*>(sB1 + c * 64 + part * 16 + e4 * 4);
+            *reinterpret_cast<float4*>(bv + e4 * 4) = *reinterpret_cast<const float4*>(sB1 + 512 + c * 64 + part * 16 + e4 * 4);
+          }
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float g0 = __uint_as_float(gt[2 * e]) + bg[2 * e], g1 = __uint_as_float(gt[2 * e + 1]) + bg[2 * e + 1];
@@ -309,7 +326,10 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
             uint32_t v[16];
             tmem_ld16(tmem_base + lane_addr + s * 128 + part * 32 + half16 * 16, v);
             tmem_ld_wait();
-            const float* b1 = sB1 + c * 128 + part * 32 + half16 * 16;
+            float b1[16];
+#pragma unroll
+            for (int e4 = 0; e4 < 4; ++e4)
+              *reinterpret_cast<float4*>(b1 + e4 * 4) = *reinterpret_cast<const float4*>(sB1 + c * 128 + part * 32 + half16 * 16 + e4 * 4);
 #pragma unroll
             for (int e = 0; e < 8; ++e)
               pk[half16 * 8 + e] = pack_half2(fmaxf(__uint_as_float(v[2 * e]) + b1[2 * e], 0.f),
@@ -321,6 +341,8 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
         if (lane == 0) mbar_arrive(&hacc_empty[s]);
         // the hidden tile is single-buffered: the previous chunk's second GEMM must have read it
         if (!mbar_wait(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
+        // ... and it doubles as the staging rows of the previous tile's output: those stores must have read it
+        if (p.tma_out && c == 0 && it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status, 61)) { ok = false; break; }
         if (SWIGLU) {
           // 16 hidden channels = chunks 2*part, 2*part+1 of the row's single 64-wide k-atom
 #pragma unroll
@@ -342,6 +364,49 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
       if (!ok) break;
       if (!mbar_wait(out_full, it & 1, abort_flag, p.status, 60)) break;
       tc_fence_after();
+      if (p.tma_out) {
+        // The pair tile leaves by TMA from this warp's staging rows (32 rows x 16 channels, twice), which live in
+        // the hidden tile's shared memory: it is free once the tile's last second GEMM has completed (out_full).
+        // An update in place is a reduce-add of (accumulator + bias) into the rows, so the residual is not read
+        // here at all.  A thread owning a row would otherwise touch 32 lines per 32-byte access.
+        uint8_t* stage = sH + warp * TR_OUT_STAGE;
+        const int64_t row0 = t * TR_ROWS + q * 32;
+        const bool any_row = row0 < p.rows;
+        uint32_t v[2][16];
+        tmem_ld16(tmem_base + lane_addr + 256 + part * 32, v[0]);
+        tmem_ld16(tmem_base + lane_addr + 256 + part * 32 + 16, v[1]);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_empty);     // the accumulator is in registers: the next tile may overwrite it
+        if (any_row) {
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            const int c0 = part * 32 + pass * 16;
+            if (pass == 1) {                        // the first pass's copy has finished reading the rows
+              if (lane == 0) bulk_wait_read();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const float4 bb = *reinterpret_cast<const float4*>(sB2 + c0 + k4 * 4);
+              *reinterpret_cast<float4*>(stage + lane * 64 + ((uint32_t)(k4 ^ ((lane >> 1) & 3)) << 4)) =
+                  make_float4(__uint_as_float(v[pass][k4 * 4]) + bb.x, __uint_as_float(v[pass][k4 * 4 + 1]) + bb.y,
+                              __uint_as_float(v[pass][k4 * 4 + 2]) + bb.z, __uint_as_float(v[pass][k4 * 4 + 3]) + bb.w);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (p.resid) tma_reduce_add_2d(&mapO, stage, c0, (int)row0);
+              else tma_store_2d(&mapO, stage, c0, (int)row0);
+              bulk_commit();
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) { bulk_wait_read(); mbar_arrive(stage_free); }
+        continue;
+      } else
 #pragma unroll 1
       for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
         uint32_t v[16];
@@ -350,7 +415,11 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
         if (valid) {
           float o[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] = __uint_as_float(v[e]) + sB2[c0 + e];
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const float4 bb = *reinterpret_cast<const float4*>(sB2 + c0 + e4 * 4);
+            o[e4 * 4] = __uint_as_float(v[e4 * 4]) + bb.x; o[e4 * 4 + 1] = __uint_as_float(v[e4 * 4 + 1]) + bb.y;
+            o[e4 * 4 + 2] = __uint_as_float(v[e4 * 4 + 2]) + bb.z; o[e4 * 4 + 3] = __uint_as_float(v[e4 * 4 + 3]) + bb.w;
+          }
           if (out_bf16) {
             if (p.resid) {
               uint32_t words[8];
@@ -396,11 +465,14 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const Transit
     }
   }
 
+  if (p.tma_out && warp < 16 && lane == 0) bulk_wait_all();     // this thread's stores have landed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) drain_after_abort();
   if (warp == 24) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
+
+lf_status make_map_f32_rows16(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t rows);
 
 void configure_transition() {
   cudaFuncSetAttribute(transition_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TR_SMEM);
@@ -418,13 +490,17 @@ lf_status transition_run(lf_context* ctx, ArenaCursor& cur, const void* act, int
   p.gamma = w->f[TRN_LN_G]; p.beta = w->f[TRN_LN_B]; p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[0]; p.b1 = w->f[TRN_B1]; p.b2 = w->f[TRN_B2];
   p.resid = resid; p.out = out; p.status = (Status*)ctx->tc_status;
+  // float32 rows updated in place (or written without a residual): the pair tile travels by TMA
+  CUtensorMap mo{};
+  p.tma_out = (!p.act_bf16 && (resid == nullptr || resid == out) && rows < ((int64_t)1 << 31)) ? 1 : 0;
+  if (p.tma_out) LF_TRY(make_map_f32_rows16(ctx, &mo, out, (uint64_t)rows));
   const int64_t tiles = (rows + TR_ROWS - 1) / TR_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_TRANSITION);
   if (w->kind == LF_WEIGHTS_TRANSITION_AF3)
-    transition_kernel<true><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
+    transition_kernel<true><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(mo, p);
   else
-    transition_kernel<false><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(p);
+    transition_kernel<false><<<grid, TR_THREADS, TR_SMEM, ctx->stream>>>(mo, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
