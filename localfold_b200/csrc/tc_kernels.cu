@@ -98,6 +98,22 @@ lf_status make_map_f32_rows16(lf_context* ctx, CUtensorMap* map, const void* bas
   return LF_OK;
 }
 
+// fp16 operand planes [planes][plane_rows][ld] seen as (k, i, plane); boxes of 64 k (128 bytes, 128-byte swizzle) x 1 x box_h
+// planes: what four epilogue warps of the triangle projection store per pass
+lf_status make_map_plane_runs(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t n, uint64_t plane_rows, uint64_t planes,
+                              uint64_t ld, uint32_t box_h) {
+  if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {n, plane_rows, planes};
+  cuuint64_t strides[2] = {ld * 2, plane_rows * ld * 2};
+  cuuint32_t box[3] = {64, 1, box_h};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled (operand planes) failed with code %d", (int)r);
+  return LF_OK;
+}
+
 lf_status check_status(lf_context* ctx) {
   if (!ctx->tc_status) return LF_OK;
   Status st;

@@ -54,6 +54,8 @@ struct LnGemmParams {
   // its [ch_per_rank][peer_plane_rows][ld] buffer, at rows peer_row0 + local row; stores go to the peers' memory
   int peer_ranks, ch_per_rank, peer_plane_rows, peer_row0;
   PeerPtrs peer_a, peer_b;
+  int plane_tma;            // the planes are written by TMA from staging rows (maps in PlaneMaps), plane_box_h planes per copy
+  int plane_box_h;
   // attention projection epilogue
   op16* out_q; op16* out_k; op16* out_v; op16* out_g;   // logical rows, stored in 8 x 8 pieces (see ldq)
   op16* out_bias;           // fp16 [heads][batch rows][ldb] (head, query, key)
@@ -76,6 +78,11 @@ struct LnGemmParams {
   float x_eps;              // epsilon of the centre LayerNorm in the units x is stored in
   Status* status;
 };
+
+// Tensor maps of the triangle projection's destinations: entry 2 * owner + (0 for a, 1 for b) covers that rank's
+// [ch_per_rank][plane rows][ld] buffer (one owner = this device's whole planes).
+constexpr int LG_MAX_PLANE_OWNERS = 8;
+struct PlaneMaps { CUtensorMap m[2 * LG_MAX_PLANE_OWNERS]; };
 
 enum { LG_EPI_TRIANGLE = 0, LG_EPI_ATTENTION = 1, LG_EPI_OUTPUT = 2, LG_EPI_TRI_OUT = 3 };
 
@@ -104,9 +111,21 @@ __device__ __forceinline__ void tile_rows(const LnGemmParams& p, int64_t t, int6
 }
 
 
+#ifdef LF_RELAX_EPI
+#define LF_WAIT_EPI mbar_wait_relaxed
+#else
+#define LF_WAIT_EPI mbar_wait
+#endif
+#ifdef LF_RELAX_PROD
+#define LF_WAIT_PROD mbar_wait_relaxed
+#else
+#define LF_WAIT_PROD mbar_wait
+#endif
+
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1)
-ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const __grid_constant__ LnGemmParams p) {
+ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const __grid_constant__ PlaneMaps planes,
+               const __grid_constant__ LnGemmParams p) {
   // operand stages: the triangle output keeps one (its shared memory goes to the staging rows of the pair tile instead);
   // the producers of tile t+1 then start when the MMAs of tile t have completed, i.e. beside the epilogue of tile t
   constexpr int NS = EPI == LG_EPI_TRI_OUT ? 1 : 2;
@@ -117,7 +136,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
   uint8_t* sX = sA + NS * LG_A_BYTES;                 // triangle output only: the raw x tile
   uint8_t* sStage = sX + (EPI == LG_EPI_TRI_OUT ? LG_A_BYTES : 0);   // output kernels: per epilogue warp 32 rows x 128 B of the pair
-  float* sBias = reinterpret_cast<float*>(sStage + ((EPI == LG_EPI_TRI_OUT || EPI == LG_EPI_OUTPUT) ? LG_EPI_WARPS * 4096 : 0));
+  // (triangle projection: per group of four epilogue warps 32 channels x 128 B of an operand plane)
+  float* sBias = reinterpret_cast<float*>(sStage + ((EPI == LG_EPI_TRI_OUT || EPI == LG_EPI_OUTPUT) ? LG_EPI_WARPS * 4096
+                                                    : EPI == LG_EPI_TRIANGLE ? 4 * 4096 : 0));
   float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
   float* sGamma = sBias + 544;      // [128]
   float* sBeta = sGamma + 128;      // [128]
@@ -144,7 +165,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], LG_EPI_WARPS);
     }
-    for (int i = 0; i < LG_EPI_WARPS; ++i) mbar_init(&stage_bar[i], 1);
+    for (int i = 0; i < LG_EPI_WARPS; ++i) mbar_init(&stage_bar[i], (EPI == LG_EPI_TRIANGLE && i < 4) ? 4 : 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -176,7 +197,15 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
     for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
       const int s = it % NS;
       const uint32_t ph = (uint32_t)(it / NS) & 1u;
-      if (!mbar_wait(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
+      if (pw == 0 && lane == 0 && !p.a_is_op16 && !p.transpose && t + gridDim.x < tiles) {
+        // rows of a tile are contiguous: ask for this CTA's next tile now, so that its loads find the rows in L2
+        int64_t nb;
+        int nc;
+        tile_rows(p, t + gridDim.x, nb, nc);
+        const uint32_t row_bytes = p.act_bf16 ? LG_K * 2u : LG_K * 4u;
+        bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.act) + nb * row_bytes, (uint32_t)nc * row_bytes);
+      }
+      if (!LF_WAIT_PROD(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
       uint8_t* tile = sA + s * LG_A_BYTES;
       int64_t row_base;
       int row_count;
@@ -438,7 +467,7 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
       }
       for (int j = 0; j < p.n_chunks; ++j, ++g) {
         const int b = g & 1;
-        if (!mbar_wait(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
+        if (!LF_WAIT_EPI(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + lane_addr + b * 256;
         if (EPI == LG_EPI_TRIANGLE) {
@@ -459,6 +488,64 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
           // rows of this warp's quarter: r0 .. r0+31, as (i, k) with 32-bit arithmetic
           const uint32_t r0 = (uint32_t)(t * LG_ROWS) + part * 32;
           uint32_t ii = r0 / un, kk0 = r0 % un;
+          if (p.plane_tma) {
+            // The four warps that share this warp's 32 channels fill staging rows of 64 k (128 bytes, 128-byte swizzle),
+            // 16 k each, twice per chunk; one of them sends the rows off as one copy per owner.  A request to the L2
+            // then carries 128 bytes: with a thread's own 32-byte stores (one line in each of 32 planes per
+            // instruction) the request rate, not the bytes, bounded this kernel.
+            uint8_t* stage = sStage + q * 4096;
+            uint64_t* grp_full = &stage_bar[q];        // count 4: the warps' slices are written
+            uint64_t* grp_free = &stage_bar[4 + q];    // count 1: the copy has finished reading the rows
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {
+              const int c0 = pass * 64 + part * 16;
+              uint32_t pv[16], gv[16];
+              tmem_ld16(acc + c0, pv);
+              tmem_ld16(acc + 128 + c0, gv);
+              tmem_ld_wait();
+              const int64_t r64 = t * LG_ROWS + pass * 64;     // n is a multiple of 64: a run lies inside one pair row and
+              if (r64 >= p.rows) break;                        // is in range or out of it as a whole, for all four warps alike
+              const float4* m4 = reinterpret_cast<const float4*>(p.mask + r64 + part * 16);
+              uint32_t pk[8];
+#pragma unroll
+              for (int g4 = 0; g4 < 4; ++g4) {
+                const float4 m = __ldg(m4 + g4);
+                const float mm[4] = {m.x, m.y, m.z, m.w};
+                float val[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  val[e] = mm[e] * (__uint_as_float(pv[g4 * 4 + e]) + bias_p) * sigmoid_fast(__uint_as_float(gv[g4 * 4 + e]) + bias_g);
+                pk[g4 * 2] = pack_half2(val[0], val[1]);
+                pk[g4 * 2 + 1] = pack_half2(val[2], val[3]);
+              }
+              if (part == 0 && staged > 0) {
+                if (lane == 0) { bulk_wait_read(); mbar_arrive(grp_free); }
+                __syncwarp();
+              }
+              if (!mbar_wait(grp_free, (staged & 1u) ^ 1u, abort_flag, p.status, 19)) { ok = false; break; }
+              const uint32_t sw = (uint32_t)lane & 7u;
+              *reinterpret_cast<uint4*>(stage + lane * 128 + (((uint32_t)(part * 2) ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              *reinterpret_cast<uint4*>(stage + lane * 128 + (((uint32_t)(part * 2 + 1) ^ sw) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(grp_full);
+              if (part == 0) {
+                if (!mbar_wait(grp_full, staged & 1u, abort_flag, p.status, 20)) { ok = false; break; }
+                if (lane == 0) {
+                  const uint32_t u64 = (uint32_t)r64;
+                  const int ti = (int)(u64 / un), tk = (int)(u64 % un);
+                  for (int h0 = 0; h0 < 32; h0 += p.plane_box_h) {
+                    const int hh = q * 32 + h0, owner = hh / p.ch_per_rank;
+                    tma_store_3d(&planes.m[2 * owner + j], stage + h0 * 128, tk, p.peer_row0 + ti, hh - owner * p.ch_per_rank);
+                  }
+                  bulk_commit();
+                }
+                __syncwarp();
+              }
+              ++staged;
+            }
+            if (!ok) break;
+          } else
 #pragma unroll 1
           for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
             uint32_t pv[16], gv[16];
@@ -705,7 +792,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
     }
   }
 
-  if ((EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out && warp < LG_EPI_WARPS && lane == 0) bulk_wait_all();   // this thread's stores have landed
+  if ((((EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out) || (EPI == LG_EPI_TRIANGLE && p.plane_tma)) && warp < LG_EPI_WARPS &&
+      lane == 0)
+    bulk_wait_all();   // this thread's stores have landed
   tc_fence_before();
   __syncthreads();
   if (*abort_flag) drain_after_abort();
@@ -733,16 +822,38 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                             uint64_t stride2_bytes, uint32_t b1, uint32_t b2);
 
-static int ln_gemm_smem(int n_pad, bool tri_out = false, bool staged_out = false) {
-  return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (staged_out ? LG_EPI_WARPS * 4096 : 0) + (544 + 256 + 512) * 4 + 512 + 1024;
+static int ln_gemm_smem(int n_pad, bool tri_out = false, bool staged_out = false, bool plane_stage = false) {
+  return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (staged_out ? LG_EPI_WARPS * 4096 : 0) + (plane_stage ? 4 * 4096 : 0) +
+         (544 + 256 + 512) * 4 + 512 + 1024;
 }
 
 void configure_ln_gemm() {
-  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512, false, false, true));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_ATTENTION>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(528));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128, false, true));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, false, true));
   cudaGetLastError();
+}
+
+lf_status make_map_plane_runs(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t n, uint64_t plane_rows, uint64_t planes,
+                              uint64_t ld, uint32_t box_h);
+
+// Destinations of the triangle projection as tensor maps, when the shape allows the staged copies (runs of 64 k,
+// at most LG_MAX_PLANE_OWNERS owners); otherwise the kernel stores with its own threads.
+static lf_status plane_maps(lf_context* ctx, LnGemmParams& p, PlaneMaps& pm, const PeerPtrs& a, const PeerPtrs& b, int owners,
+                            int plane_rows) {
+  p.plane_tma = 0;
+  if ((p.n & 63) != 0 || owners > LG_MAX_PLANE_OWNERS || 128 % owners != 0) return LF_OK;
+  p.ch_per_rank = 128 / owners;
+  p.plane_box_h = p.ch_per_rank < 32 ? p.ch_per_rank : 32;
+  for (int o = 0; o < owners; ++o) {
+    LF_TRY(make_map_plane_runs(ctx, &pm.m[2 * o], a.p[o], (uint64_t)p.n, (uint64_t)plane_rows, (uint64_t)p.ch_per_rank, (uint64_t)p.ld,
+                               (uint32_t)p.plane_box_h));
+    LF_TRY(make_map_plane_runs(ctx, &pm.m[2 * o + 1], b.p[o], (uint64_t)p.n, (uint64_t)plane_rows, (uint64_t)p.ch_per_rank, (uint64_t)p.ld,
+                               (uint32_t)p.plane_box_h));
+  }
+  p.plane_tma = 1;
+  return LF_OK;
 }
 
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
@@ -755,10 +866,14 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
   p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
   p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
   p.mask = mask; p.out_a = a; p.out_b = b; p.n = n; p.ld = ld; p.status = (Status*)ctx->tc_status;
+  PlaneMaps pm{};
+  PeerPtrs pa{}, pb{};
+  pa.p[0] = a; pb.p[0] = b;
+  LF_TRY(plane_maps(ctx, p, pm, pa, pb, 1, rows));
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
+  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512, false, false, true), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, pm, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -778,10 +893,12 @@ lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void
   p.peer_ranks = ranks; p.ch_per_rank = 128 / ranks; p.peer_plane_rows = n; p.peer_row0 = row0;
   p.peer_a = a_peers; p.peer_b = b_peers;
   p.out_a = (op16*)a_peers.p[0]; p.out_b = (op16*)b_peers.p[0];      // ranks == 1: plain form
+  PlaneMaps pm{};
+  LF_TRY(plane_maps(ctx, p, pm, a_peers, b_peers, ranks, n));
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
+  ln_gemm_kernel<LG_EPI_TRIANGLE><<<grid, LG_THREADS, ln_gemm_smem(512, false, false, true), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, pm, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -828,7 +945,7 @@ static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const
   const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
-  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, p);
+  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(528), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, PlaneMaps{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -862,7 +979,7 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
   // the fp16 rows are in logical order; the transposed scatter happens in the epilogue (or in the tensor map)
-  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128, false, true), ctx->stream>>>(CUtensorMap{}, mo, p);
+  ln_gemm_kernel<LG_EPI_OUTPUT><<<grid, LG_THREADS, ln_gemm_smem(128, false, true), ctx->stream>>>(CUtensorMap{}, mo, PlaneMaps{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
@@ -893,7 +1010,7 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
   p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out)) ? 1 : 0;
   if (p.tma_out) LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)n, (uint64_t)rows, 512, (uint64_t)n * 512, 32, 1));
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_OUTPUT);
-  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, false, true), ctx->stream>>>(mapX, mo, p);
+  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, false, true), ctx->stream>>>(mapX, mo, PlaneMaps{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
