@@ -87,9 +87,6 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // and the caller leaves its loop; the kernel then tears down normally.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-#ifndef LF_RELAX_NS
-#define LF_RELAX_NS 40
-#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* status,
                                           unsigned int where) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -97,28 +94,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 2047u) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = global_timer_ns();
-      if (start == 0) start = now;
-      else if (now - start > kWaitLimitNs) {
-        *abort_flag = 1;
-        if (status && atomicCAS(&status->code, 0u, 1u) == 0u) { status->where = where; status->block = blockIdx.x; }
-        return false;
-      }
-    }
-  }
-}
-
-// For warps off the critical path: sleeps between tries, so that a waiting warp leaves the issue slots
-// of its scheduler to the warps that have work (a few tens of nanoseconds added to the hand-over).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* status,
-                                                  unsigned int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t start = 0;
-  for (uint32_t it = 1;; ++it) {
-    __nanosleep(LF_RELAX_NS);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 0) {
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (start == 0) start = now;
@@ -198,6 +173,12 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
                "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 // asks for [src, src + bytes) to be brought into L2; bytes a multiple of 16, src 16-byte aligned

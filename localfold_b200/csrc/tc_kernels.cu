@@ -83,6 +83,21 @@ lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base,
   return LF_OK;
 }
 
+// the same with boxes of 16 channels (64-byte rows, 64-byte swizzle): the staging tiles of the triangle output
+lf_status make_map_f32_rows_half(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                                 uint64_t stride2_bytes, uint32_t b1, uint32_t b2) {
+  if (!g_encode) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {128, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {16, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return lf_fail(ctx, LF_ERR_CUDA, "cuTensorMapEncodeTiled (float32 rows, 16 channels, 3-d) failed with code %d", (int)r);
+  return LF_OK;
+}
+
 // float32 rows of 128 channels as a 2-d map (channel, row) with boxes of 16 channels x 32 rows (64-byte rows,
 // 64-byte swizzle): the staging tiles of the transition's output
 lf_status make_map_f32_rows16(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t rows) {

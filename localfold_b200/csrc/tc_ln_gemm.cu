@@ -111,33 +111,22 @@ __device__ __forceinline__ void tile_rows(const LnGemmParams& p, int64_t t, int6
 }
 
 
-#ifdef LF_RELAX_EPI
-#define LF_WAIT_EPI mbar_wait_relaxed
-#else
-#define LF_WAIT_EPI mbar_wait
-#endif
-#ifdef LF_RELAX_PROD
-#define LF_WAIT_PROD mbar_wait_relaxed
-#else
-#define LF_WAIT_PROD mbar_wait
-#endif
-
 template <int EPI>
 __global__ void __launch_bounds__(LG_THREADS, 1)
 ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapO, const __grid_constant__ PlaneMaps planes,
                const __grid_constant__ LnGemmParams p) {
-  // operand stages: the triangle output keeps one (its shared memory goes to the staging rows of the pair tile instead);
-  // the producers of tile t+1 then start when the MMAs of tile t have completed, i.e. beside the epilogue of tile t
-  constexpr int NS = EPI == LG_EPI_TRI_OUT ? 1 : 2;
+  // two operand stages everywhere; the triangle output also keeps two raw x tiles, and the epilogue of a tile stages its
+  // output rows in that tile's x buffer, which its MMAs have finished with by then
+  constexpr int NS = 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int w_bytes = p.n_pad * 256;
   uint8_t* sW = smem;
   uint8_t* sA = smem + w_bytes;                       // 2 stages (w_bytes is a multiple of 1024: n_pad % 8 == 0... x256)
   uint8_t* sX = sA + NS * LG_A_BYTES;                 // triangle output only: the raw x tile
-  uint8_t* sStage = sX + (EPI == LG_EPI_TRI_OUT ? LG_A_BYTES : 0);   // output kernels: per epilogue warp 32 rows x 128 B of the pair
+  uint8_t* sStage = sX + (EPI == LG_EPI_TRI_OUT ? NS * LG_A_BYTES : 0);   // attention output: per epilogue warp 32 rows x 128 B of the pair
   // (triangle projection: per group of four epilogue warps 32 channels x 128 B of an operand plane)
-  float* sBias = reinterpret_cast<float*>(sStage + ((EPI == LG_EPI_TRI_OUT || EPI == LG_EPI_OUTPUT) ? LG_EPI_WARPS * 4096
+  float* sBias = reinterpret_cast<float*>(sStage + (EPI == LG_EPI_OUTPUT ? LG_EPI_WARPS * 4096
                                                     : EPI == LG_EPI_TRIANGLE ? 4 * 4096 : 0));
   float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
   float* sGamma = sBias + 544;      // [128]
@@ -149,7 +138,8 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
   uint64_t* acc_empty = bars + 6;   // [2]
   uint64_t* x_full = bars + 8;      // [2] TMA bytes of the x tile
   uint64_t* stat_full = bars + 10;  // [2] row statistics of the x tile written
-  uint64_t* stage_bar = bars + 12;  // [epilogue warp] TMA bytes of the warp's residual tile
+  uint64_t* stage_bar = bars + 12;  // [16] hand-over of staging rows: triangle projection 0..3 slices written (count 4), 4..7 rows read;
+                                    // triangle output 8..9: the epilogue warps (count 16) are done with the x buffer of that stage
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12 + LG_EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -159,13 +149,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(&x_full[s], 1);
-      mbar_init(&stat_full[s], 4);
+      mbar_init(&stat_full[s], LG_PROD_WARPS);
       mbar_init(&a_full[s], LG_PROD_WARPS);
       mbar_init(&a_empty[s], 1);
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], LG_EPI_WARPS);
     }
-    for (int i = 0; i < LG_EPI_WARPS; ++i) mbar_init(&stage_bar[i], (EPI == LG_EPI_TRIANGLE && i < 4) ? 4 : 1);
+    for (int i = 0; i < LG_EPI_WARPS; ++i)
+      mbar_init(&stage_bar[i], (EPI == LG_EPI_TRIANGLE && i < 4) ? 4 : (EPI == LG_EPI_TRI_OUT && (i == 8 || i == 9)) ? LG_EPI_WARPS : 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -205,17 +196,21 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
         const uint32_t row_bytes = p.act_bf16 ? LG_K * 2u : LG_K * 4u;
         bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.act) + nb * row_bytes, (uint32_t)nc * row_bytes);
       }
-      if (!LF_WAIT_PROD(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
+      if (!mbar_wait(&a_empty[s], ph ^ 1, abort_flag, p.status, 10)) break;
       uint8_t* tile = sA + s * LG_A_BYTES;
       int64_t row_base;
       int row_count;
       tile_rows(p, t, row_base, row_count);
-      if (EPI == LG_EPI_TRI_OUT && pw == 0 && lane == 0) {
-        // x[h][i][k0 .. k0+127] for all 128 channels: two boxes of 64 pairs x 128 channels
-        const int i = (int)(t / p.tile_per_row), k0 = (int)(t % p.tile_per_row) * LG_ROWS;
-        mbar_expect_tx(&x_full[s], LG_A_BYTES);
-        tma_load_3d(sX + s * LG_A_BYTES, &mapX, &x_full[s], k0, i, 0);
-        tma_load_3d(sX + s * LG_A_BYTES + LG_A_BYTES / 2, &mapX, &x_full[s], k0 + 64, i, 0);
+      if (EPI == LG_EPI_TRI_OUT && pw == 0) {
+        // the x buffer of this stage doubled as the staging rows of the tile two back: its copies must have read them
+        if (!mbar_wait(&stage_bar[8 + s], ph ^ 1, abort_flag, p.status, 21)) break;
+        if (lane == 0) {
+          // x[h][i][k0 .. k0+127] for all 128 channels: two boxes of 64 pairs x 128 channels
+          const int i = (int)(t / p.tile_per_row), k0 = (int)(t % p.tile_per_row) * LG_ROWS;
+          mbar_expect_tx(&x_full[s], LG_A_BYTES);
+          tma_load_3d(sX + s * LG_A_BYTES, &mapX, &x_full[s], k0, i, 0);
+          tma_load_3d(sX + s * LG_A_BYTES + LG_A_BYTES / 2, &mapX, &x_full[s], k0 + 64, i, 0);
+        }
       }
 #pragma unroll 1
       for (int grp = 0; grp < 2; ++grp) {
@@ -327,27 +322,55 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[s]);
-      if (EPI == LG_EPI_TRI_OUT && pw < 4) {
-        // statistics of the centre LayerNorm: one thread per pair reads its 128 channels from the
-        // raw x tile (row h of the tile = 128 bytes of 64 pairs, 128-byte swizzled)
+      if (EPI == LG_EPI_TRI_OUT) {
+        // Statistics of the centre LayerNorm over the raw x tile (row h of a box = 128 bytes of 64 pairs, 128-byte
+        // swizzled).  A warp owns 16 pairs; a lane reads 8 pairs (one 16-byte piece) of 8 channel rows, so the tile is
+        // read once with 16-byte loads, and the 16 lanes that share a piece add up by a halving exchange: after four
+        // steps lane group v holds value v of (8 sums, 8 sums of squares).
         if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, 14)) break;
-        const int pr = pw * 32 + lane;
-        const uint8_t* xt = sX + s * LG_A_BYTES + (pr >> 6) * (LG_A_BYTES / 2);
-        const uint32_t chunk = (uint32_t)((pr & 63) >> 3), within = (uint32_t)(pr & 7) * 2u;
-        float sum = 0.f, sq = 0.f;
-#pragma unroll 8
-        for (int h = 0; h < 128; ++h) {
-          const float xv = __half2float(*reinterpret_cast<const __half*>(xt + swizzle128_offset((uint32_t)h, chunk) + within));
-          sum += xv;
-          sq = fmaf(xv, xv, sq);
+        const int cg = pw * 2 + (lane & 1);          // pairs 8 cg .. 8 cg + 7 of the tile
+        const int hgl = lane >> 1;                   // channel rows 8 hgl .. 8 hgl + 7
+        const uint8_t* xb = sX + s * LG_A_BYTES + (cg >> 3) * (LG_A_BYTES / 2);
+        const uint32_t piece = (uint32_t)cg & 7u;
+        float acc[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int hh = 0; hh < 8; ++hh) {
+          // the rows are taken in an order that differs from lane to lane, so that a warp's loads spread over the banks
+          const uint32_t h = (uint32_t)hgl * 8u + (((uint32_t)hh + 2u * (uint32_t)hgl) & 7u);
+          const uint4 raw = *reinterpret_cast<const uint4*>(xb + h * 128u + ((piece ^ (h & 7u)) << 4));
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&words[e]));
+            acc[2 * e] += f2.x; acc[2 * e + 1] += f2.y;
+            acc[8 + 2 * e] = fmaf(f2.x, f2.x, acc[8 + 2 * e]); acc[8 + 2 * e + 1] = fmaf(f2.y, f2.y, acc[8 + 2 * e + 1]);
+          }
         }
-        const float mean = sum * (1.0f / 128.0f);
-        float var = sq * (1.0f / 128.0f) - mean * mean;
-        if (p.variance != 2) var = fmaxf(var, 0.f);
-        float inv = rsqrtf(var + p.x_eps);
-        inv = inv * (1.5f - 0.5f * (var + p.x_eps) * inv * inv);
-        sStat[(it & 1) * 256 + pr] = inv;            // two sets: the epilogue of the previous tile may still read its own
-        sStat[(it & 1) * 256 + 128 + pr] = inv * mean;
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+          const int width = 8 >> step;               // values kept after this step
+          const uint32_t bit = 16u >> step;          // lane bit that picks the half
+          const bool upper = ((uint32_t)lane & bit) != 0u;
+#pragma unroll
+          for (int e = 0; e < width; ++e) {
+            const float keep = upper ? acc[e + width] : acc[e];
+            const float send = upper ? acc[e] : acc[e + width];
+            acc[e] = keep + __shfl_xor_sync(0xffffffffu, send, (int)bit);
+          }
+        }
+        const float sq = __shfl_down_sync(0xffffffffu, acc[0], 16);
+        if (lane < 16) {
+          const int pr = cg * 8 + hgl;
+          const float mean = acc[0] * (1.0f / 128.0f);
+          float var = sq * (1.0f / 128.0f) - mean * mean;
+          if (p.variance != 2) var = fmaxf(var, 0.f);
+          float inv = rsqrtf(var + p.x_eps);
+          inv = inv * (1.5f - 0.5f * (var + p.x_eps) * inv * inv);
+          sStat[(it & 1) * 256 + pr] = inv;            // two sets: the epilogue of the previous tile may still read its own
+          sStat[(it & 1) * 256 + 128 + pr] = inv * mean;
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&stat_full[s]);
       }
@@ -444,30 +467,24 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
       // attention output through the tensor map: this warp's 32 rows x 32 channels of the pair
       const bool tma_tile = (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out && q * 32 < row_count;
       int tx = 0, ty = 0, tz = 0;
-      uint32_t stage_phase = 0;
       if (tma_tile) {
-        stage_phase = staged & 1u;       // a warp skips tiles of which it owns no row, so it counts its own residual loads
-        if (p.resid) ++staged;
         const int64_t r0 = row_base + q * 32;
         tx = part * 32;
         if (EPI == LG_EPI_TRI_OUT) {
+          // (its staging rows hold 16 channels at a time: see below)
           // tiles lie inside one pair row i: the map is (channel, k, i), so a ragged last tile of a row is clipped at k = n
           tz = (int)(t / p.tile_per_row);
           ty = (int)(t % p.tile_per_row) * LG_ROWS + q * 32;
         } else if (p.transpose) { const uint32_t u0 = (uint32_t)r0, uq = (uint32_t)p.Q; ty = (int)(u0 / uq); tz = (int)(u0 % uq); }
         else ty = (int)r0;
-        if (lane == 0) {
-          bulk_wait_read();      // the previous tile's store has finished reading the staging rows
-          if (p.resid) {
-            mbar_expect_tx(&stage_bar[warp], 4096);
-            tma_load_3d(sStage + warp * 4096, &mapO, &stage_bar[warp], tx, ty, tz);
-          }
+        if (EPI == LG_EPI_OUTPUT) {
+          if (lane == 0) bulk_wait_read();      // the previous tile's copy has finished reading the staging rows
+          __syncwarp();
         }
-        __syncwarp();
       }
       for (int j = 0; j < p.n_chunks; ++j, ++g) {
         const int b = g & 1;
-        if (!LF_WAIT_EPI(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
+        if (!mbar_wait(&acc_full[b], (g >> 1) & 1, abort_flag, p.status, 13)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + lane_addr + b * 256;
         if (EPI == LG_EPI_TRIANGLE) {
@@ -585,12 +602,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
             if (kk0 >= un) { kk0 -= un; ++ii; }
           }
         } else if ((EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) && p.tma_out) {
-          // thread = pair row; the warp's 32 rows x 32 channels are finished in its staging rows (128 B each,
+          // thread = pair row; the warp's 32 rows x 32 channels are written to its staging rows (128 B each,
           // 16-byte pieces swizzled by row so that the row-per-thread accesses spread over the banks) and leave
-          // as one TMA store: no global load or store instruction touches the pair here
+          // as one TMA copy (a reduce-add when the pair is updated in place): no global load or store
+          // instruction touches the pair here
           if (tma_tile) {
-            uint8_t* stage = sStage + warp * 4096 + lane * 128;
-            if (p.resid && !mbar_wait(&stage_bar[warp], stage_phase, abort_flag, p.status, 18)) { ok = false; break; }
+            // attention output: 32 channels per row (128 B, 128-byte swizzle), one copy per tile; triangle output: 16
+            // channels per row (64 B, 64-byte swizzle) in this tile's x buffer, one copy per half
+            uint8_t* stage = EPI == LG_EPI_TRI_OUT ? sX + (it % NS) * LG_A_BYTES + warp * 2048 + lane * 64 : sStage + warp * 4096 + lane * 128;
             float rs = 0.f, rm = 0.f;
             if (EPI == LG_EPI_TRI_OUT) {
               if (!mbar_wait(&stat_full[it % NS], (uint32_t)(it / NS) & 1u, abort_flag, p.status, 17)) { ok = false; break; }
@@ -604,9 +623,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
               tmem_ld16(acc + c0, v1);
               if (EPI == LG_EPI_TRI_OUT) tmem_ld16(acc + 128 + c0, v2);
               tmem_ld_wait();
+              if (EPI == LG_EPI_TRI_OUT && half == 1) {     // the first half's copy has finished reading the rows
+                if (lane == 0) bulk_wait_read();
+                __syncwarp();
+              }
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
-                float4* cell = reinterpret_cast<float4*>(stage + ((uint32_t)((half * 4 + k4) ^ (lane & 7)) << 4));
+                float4* cell = reinterpret_cast<float4*>(
+                    stage + (EPI == LG_EPI_TRI_OUT ? ((uint32_t)(k4 ^ ((lane >> 1) & 3)) << 4) : ((uint32_t)((half * 4 + k4) ^ (lane & 7)) << 4)));
                 // per-channel vectors are the same for every lane: 16-byte broadcasts, not scalar reads
                 const float4 b0v = *reinterpret_cast<const float4*>(sBias + c0 + k4 * 4);
                 const float b0[4] = {b0v.x, b0v.y, b0v.z, b0v.w};
@@ -625,14 +649,29 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
 #pragma unroll
                   for (int e = 0; e < 4; ++e) e4[e] = __uint_as_float(v1[k4 * 4 + e]) + b0[e];
                 }
-                float4 o = make_float4(e4[0], e4[1], e4[2], e4[3]);
-                if (p.resid) { const float4 rr = *cell; o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w; }
-                *cell = o;
+                *cell = make_float4(e4[0], e4[1], e4[2], e4[3]);
+              }
+              if (EPI == LG_EPI_TRI_OUT) {
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  const uint8_t* rows = sX + (it % NS) * LG_A_BYTES + warp * 2048;
+                  if (p.resid) tma_reduce_add_3d(&mapO, rows, c0, ty, tz);
+                  else tma_store_3d(&mapO, rows, c0, ty, tz);
+                  bulk_commit();
+                }
               }
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) { tma_store_3d(&mapO, sStage + warp * 4096, tx, ty, tz); bulk_commit(); }
+            if (EPI == LG_EPI_OUTPUT) {
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                // in place: the update is added to the rows where they live, so the residual is never read here
+                if (p.resid) tma_reduce_add_3d(&mapO, sStage + warp * 4096, tx, ty, tz);
+                else tma_store_3d(&mapO, sStage + warp * 4096, tx, ty, tz);
+                bulk_commit();
+              }
+            }
           }
         } else if (EPI == LG_EPI_OUTPUT || EPI == LG_EPI_TRI_OUT) {
           // thread = pair row; this warp's quarter = 32 output channels, two runs of 16
@@ -789,6 +828,11 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[b]);
       }
+      if (EPI == LG_EPI_TRI_OUT && ok) {
+        // this warp is done with the stage's x buffer once its copies have read their rows
+        if (lane == 0) { bulk_wait_read(); mbar_arrive(&stage_bar[8 + it % NS]); }
+        __syncwarp();
+      }
     }
   }
 
@@ -822,6 +866,9 @@ void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_
 lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                             uint64_t stride2_bytes, uint32_t b1, uint32_t b2);
 
+lf_status make_map_f32_rows_half(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                                 uint64_t stride2_bytes, uint32_t b1, uint32_t b2);
+
 static int ln_gemm_smem(int n_pad, bool tri_out = false, bool staged_out = false, bool plane_stage = false) {
   return n_pad * 256 + (tri_out ? 4 : 2) * LG_A_BYTES + (staged_out ? LG_EPI_WARPS * 4096 : 0) + (plane_stage ? 4 * 4096 : 0) +
          (544 + 256 + 512) * 4 + 512 + 1024;
@@ -831,7 +878,7 @@ void configure_ln_gemm() {
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRIANGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(512, false, false, true));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_ATTENTION>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(528));
   cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_OUTPUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(128, false, true));
-  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, false, true));
+  cudaFuncSetAttribute(ln_gemm_kernel<LG_EPI_TRI_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ln_gemm_smem(256, true, false));
   cudaGetLastError();
 }
 
@@ -1008,9 +1055,9 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
   // (channel, k, i) so that the last tile of a pair row is clipped at k = n
   CUtensorMap mo{};
   p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out)) ? 1 : 0;
-  if (p.tma_out) LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)n, (uint64_t)rows, 512, (uint64_t)n * 512, 32, 1));
+  if (p.tma_out) LF_TRY(make_map_f32_rows_half(ctx, &mo, out, (uint64_t)n, (uint64_t)rows, 512, (uint64_t)n * 512, 32, 1));
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_OUTPUT);
-  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, false, true), ctx->stream>>>(mapX, mo, PlaneMaps{}, p);
+  ln_gemm_kernel<LG_EPI_TRI_OUT><<<grid, LG_THREADS, ln_gemm_smem(256, true, false), ctx->stream>>>(mapX, mo, PlaneMaps{}, p);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;

@@ -53,17 +53,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
-#ifdef LF_RELAX_EPI
-#define LF_WAIT_EPI mbar_wait_relaxed
-#else
-#define LF_WAIT_EPI mbar_wait
-#endif
-#ifdef LF_RELAX_PROD
-#define LF_WAIT_PROD mbar_wait_relaxed
-#else
-#define LF_WAIT_PROD mbar_wait
-#endif
-
 template <bool SWIGLU>
 __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_constant__ CUtensorMap mapO, const TransitionParams p) {
   constexpr int TR_CHUNKS = SWIGLU ? 8 : 4;                 // hidden chunks per tile
@@ -140,7 +129,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         const int64_t nrows = p.rows - r0 < TR_ROWS ? p.rows - r0 : TR_ROWS;
         bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.act) + r0 * row_bytes, (uint32_t)nrows * row_bytes);
       }
-      if (!LF_WAIT_PROD(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
+      if (!mbar_wait(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
 #pragma unroll 1
       for (int grp = 0; grp < 2; ++grp) {
         float v[2][16];
@@ -309,7 +298,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
       const bool valid = r < p.rows;
       for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
         const int s = g & 1;
-        if (!LF_WAIT_EPI(&hacc_full[s], (g >> 1) & 1, abort_flag, p.status, 58)) { ok = false; break; }
+        if (!mbar_wait(&hacc_full[s], (g >> 1) & 1, abort_flag, p.status, 58)) { ok = false; break; }
         tc_fence_after();
         uint32_t pk[16];
         if (SWIGLU) {
@@ -351,7 +340,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         __syncwarp();
         if (lane == 0) mbar_arrive(&hacc_empty[s]);
         // the hidden tile is single-buffered: the previous chunk's second GEMM must have read it
-        if (!LF_WAIT_EPI(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
+        if (!mbar_wait(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
         // ... and it doubles as the staging rows of the previous tile's output: those stores must have read it
         if (p.tma_out && c == 0 && it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status, 61)) { ok = false; break; }
         if (SWIGLU) {
@@ -373,7 +362,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         if (lane == 0) mbar_arrive(h_full);
       }
       if (!ok) break;
-      if (!LF_WAIT_EPI(out_full, it & 1, abort_flag, p.status, 60)) break;
+      if (!mbar_wait(out_full, it & 1, abort_flag, p.status, 60)) break;
       tc_fence_after();
       if (p.tma_out) {
         // The pair tile leaves by TMA from this warp's staging rows (32 rows x 16 channels, twice), which live in
