@@ -548,13 +548,6 @@ lf_status derive_maps(lf_context* ctx, int kind, const lf_weight_dims& dims, con
 
 }  // namespace
 
-// Host copy of a tensor of the operator being created (valid inside lf_weights_create only).
-const float* lf_weights_staged_host(int slot) {
-  for (auto& it : g_pending.items)
-    if (it.slot == slot) return it.data.data();
-  return nullptr;
-}
-
 extern "C" {
 
 lf_status lf_weights_create(lf_context* ctx, lf_weight_kind kind, const lf_weight_dims* dims,

@@ -122,7 +122,5 @@ struct ArenaCursor {
 lf_status lf_arena_ensure(lf_context* ctx, size_t bytes);
 // The pair stack with the pair left in host memory (pair_spill.cu).
 lf_status lf_pair_stack_spilled(lf_context* ctx, const lf_pair_stack_desc* d, lf_result* r);
-// Host copy of a tensor (slot of lf_weights::f) of the operator being created; null outside lf_weights_create.
-const float* lf_weights_staged_host(int slot);
 
 static inline int lf_ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }

@@ -144,21 +144,22 @@ lf_status check_status(lf_context* ctx) {
 bool ln_gemm_supported(const lf_weights* w) { return w && !w->h.empty() && w->h[0] != nullptr; }
 
 // The centre LayerNorm folded into the output projection: W' = diag(gain) Wz, s1[c] = sum_h fp16(W'[h][c]) (what the
-// tensor core will multiply the mean by), t[c] = bz[c] + sum_h offset[h] Wz[h][c]; fold = (s1 | t | bg).
+// tensor core will multiply the mean by), t[c] = bz[c] + sum_h offset[h] Wz[h][c]; fold = (s1 | t | bg + input offset through Wg).
 __global__ void triangle_fold_kernel(const float* __restrict__ wz, const float* __restrict__ gain, const float* __restrict__ offset,
-                                     const float* __restrict__ bz, const float* __restrict__ bg, float* __restrict__ wfold,
-                                     float* __restrict__ fold) {
+                                     const float* __restrict__ bz, const float* __restrict__ bg, const float* __restrict__ wg,
+                                     const float* __restrict__ in_offset, float* __restrict__ wfold, float* __restrict__ fold) {
   const int c = threadIdx.x;
-  double s1 = 0.0, t = bz[c];
+  double s1 = 0.0, t = bz[c], g = bg[c];
   for (int h = 0; h < 128; ++h) {
     const float wf = gain[h] * wz[h * 128 + c];
     wfold[h * 128 + c] = wf;
     s1 += (double)__half2float(__float2half_rn(wf));
     t += (double)offset[h] * wz[h * 128 + c];
+    g += (double)in_offset[h] * wg[h * 128 + c];      // the input LayerNorm's offset through the output gate
   }
   fold[c] = (float)s1;
   fold[128 + c] = (float)t;
-  fold[256 + c] = bg[c];
+  fold[256 + c] = (float)g;
 }
 
 // bf16/fp16 repacks for the tensor-core kernels: h[0] = swizzled fp16 image of the fused
@@ -171,17 +172,24 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     LF_CUDA(ctx, cudaMalloc(&img, 512 * 256));
     w->owned.push_back(img);
     LF_CUDA(ctx, cudaMemsetAsync(img, 0, 512 * 256, ctx->stream));
-    pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0, 1.0f);
+    // the input LayerNorm's gain goes into the rows of the images, its offset into the biases: the kernels' producers
+    // hand the tensor core (x - mean) / std
+    pack_weight_image(ctx, w->f[TRI_W4], 128, 512, 512, 0, 512, img, 0, 1.0f, w->f[TRI_LN_G]);
+    float* b4 = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&b4, 512 * sizeof(float))); w->owned.push_back(b4);
+    fold_bias(ctx, w->f[TRI_W4], 128, 512, 0, 512, w->f[TRI_LN_B], w->f[TRI_B4], 1.0f, b4);
     w->h.assign(4, nullptr);
     w->h[0] = img;
+    w->h[1] = b4;
     // output kernel: rows 0..127 = (diag(gain) Wz)^T, rows 128..255 = Wg^T, plus the folded vectors
     float* dfold = nullptr; float* dw = nullptr; op16* img2 = nullptr;
     LF_CUDA(ctx, cudaMalloc(&dfold, 384 * 4)); w->owned.push_back(dfold);
     LF_CUDA(ctx, cudaMalloc(&dw, 128 * 128 * 4)); w->owned.push_back(dw);
     LF_CUDA(ctx, cudaMalloc(&img2, 256 * 256)); w->owned.push_back(img2);
-    triangle_fold_kernel<<<1, 128, 0, ctx->stream>>>(w->f[TRI_WZ], w->f[TRI_LNO_G], w->f[TRI_LNO_B], w->f[TRI_BZ], w->f[TRI_BG], dw, dfold);
+    triangle_fold_kernel<<<1, 128, 0, ctx->stream>>>(w->f[TRI_WZ], w->f[TRI_LNO_G], w->f[TRI_LNO_B], w->f[TRI_BZ], w->f[TRI_BG], w->f[TRI_WG],
+                                                     w->f[TRI_LN_B], dw, dfold);
     pack_weight_image(ctx, dw, 128, 128, 256, 0, 128, img2, 0, 1.0f);
-    pack_weight_image(ctx, w->f[TRI_WG], 128, 128, 256, 0, 128, img2, 128, 1.0f);
+    pack_weight_image(ctx, w->f[TRI_WG], 128, 128, 256, 0, 128, img2, 128, 1.0f, w->f[TRI_LN_G]);
     LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     w->h[2] = img2;
     w->h[3] = dfold;
@@ -197,25 +205,24 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     LF_CUDA(ctx, cudaMemsetAsync(bias, 0, 528 * sizeof(float), ctx->stream));
     // the query columns carry the head_dim^-1/2 logit scale
     const float qs = 1.0f / sqrtf((float)w->dims.head_dim);
-    pack_weight_image(ctx, w->f[ATT_W4], 128, 128, 528, 0, 512, img, 0, qs);
-    pack_weight_image(ctx, w->f[ATT_W4], 128, 384, 528, 128, 512, img, 128, 1.0f);
-    if (w->has_pair_proj) pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512, 1.0f);
+    // the LayerNorm's gain goes into the rows of the image, its offset into the bias vector
+    pack_weight_image(ctx, w->f[ATT_W4], 128, 128, 528, 0, 512, img, 0, qs, w->f[ATT_LN_G]);
+    pack_weight_image(ctx, w->f[ATT_W4], 128, 384, 528, 128, 512, img, 128, 1.0f, w->f[ATT_LN_G]);
+    fold_bias(ctx, w->f[ATT_W4], 128, 128, 0, 512, w->f[ATT_LN_B], w->f[ATT_B4], qs, bias);
+    fold_bias(ctx, w->f[ATT_W4], 128, 384, 128, 512, w->f[ATT_LN_B], w->f[ATT_B4] + 128, 1.0f, bias + 128);
+    if (w->has_pair_proj) {
+      pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 528, 0, w->dims.heads, img, 512, 1.0f, w->f[ATT_LN_G]);
+      fold_bias(ctx, w->f[ATT_WB], 128, w->dims.heads, 0, w->dims.heads, w->f[ATT_LN_B], nullptr, 1.0f, bias + 512);
+    }
     {
-      // the fused projection's bias vector: from the host copy staged while the operator is created, or (weights
-      // decoded on the device) read back - 2 KiB of values that bundles keep in float32 anyway
+      // which 128-column groups have a bias at all (the epilogue skips the others): 2 KiB read back once
       std::vector<float> hb(512);
-      if (const float* staged = lf_weights_staged_host(ATT_B4)) std::copy(staged, staged + 512, hb.begin());
-      else {
-        LF_CUDA(ctx, cudaMemcpyAsync(hb.data(), w->f[ATT_B4], 512 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
-        LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-      }
-      for (int i = 0; i < 128; ++i) hb[i] *= qs;
+      LF_CUDA(ctx, cudaMemcpyAsync(hb.data(), bias, 512 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
       w->bias_flags = 0;
       for (int grp = 0; grp < 4; ++grp)
         for (int i = 0; i < 128; ++i)
           if (hb[grp * 128 + i] != 0.f) { w->bias_flags |= 1 << grp; break; }
-      LF_CUDA(ctx, cudaMemcpyAsync(bias, hb.data(), 512 * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
-      LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     }
     w->h.assign(4, nullptr);
     w->h[0] = img;
@@ -232,11 +239,15 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     LF_CUDA(ctx, cudaMalloc(&img, 4 * 65536));
     w->owned.push_back(img);
     for (int cidx = 0; cidx < 4; ++cidx) {
-      pack_weight_image(ctx, w->f[TRN_W1], 128, 128, 128, cidx * 128, 512, img + cidx * 32768, 0, 1.0f);
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 128, 128, cidx * 128, 512, img + cidx * 32768, 0, 1.0f, w->f[TRN_LN_G]);
       pack_weight_image(ctx, w->f[TRN_W2] + (size_t)cidx * 128 * 128, 128, 128, 128, 0, 128, img + cidx * 32768 + 16384, 0, 1.0f);
     }
-    w->h.assign(1, nullptr);
+    float* b1 = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&b1, 512 * sizeof(float))); w->owned.push_back(b1);
+    fold_bias(ctx, w->f[TRN_W1], 128, 512, 0, 512, w->f[TRN_LN_B], w->f[TRN_B1], 1.0f, b1);
+    w->h.assign(2, nullptr);
     w->h[0] = img;
+    w->h[1] = b1;
   }
   if (w->kind == LF_WEIGHTS_TRANSITION_AF3 && w->dims.channels == 128 && w->dims.hidden == 512) {
     // per 64-wide hidden chunk: W1 slice image of 128 rows (64 gate columns, then the matching 64 value
@@ -246,12 +257,16 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->owned.push_back(img);
     for (int cidx = 0; cidx < 8; ++cidx) {
       op16* base = img + (size_t)cidx * 24576;
-      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, cidx * 64, 1024, base, 0, 1.0f);
-      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, 512 + cidx * 64, 1024, base, 64, 1.0f);
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, cidx * 64, 1024, base, 0, 1.0f, w->f[TRN_LN_G]);
+      pack_weight_image(ctx, w->f[TRN_W1], 128, 64, 128, 512 + cidx * 64, 1024, base, 64, 1.0f, w->f[TRN_LN_G]);
       pack_weight_image(ctx, w->f[TRN_W2] + (size_t)cidx * 64 * 128, 64, 128, 128, 0, 128, base + 16384, 0, 1.0f);
     }
-    w->h.assign(1, nullptr);
+    float* b1 = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&b1, 1024 * sizeof(float))); w->owned.push_back(b1);
+    fold_bias(ctx, w->f[TRN_W1], 128, 1024, 0, 1024, w->f[TRN_LN_B], w->f[TRN_B1], 1.0f, b1);
+    w->h.assign(2, nullptr);
     w->h[0] = img;
+    w->h[1] = b1;
   }
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return LF_OK;

@@ -40,7 +40,9 @@ lf_status contract_scatter(lf_context* ctx, ArenaCursor& cur, const op16* a, con
 bool ln_gemm_supported(const lf_weights* w);
 void configure_ln_gemm();
 void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0,
-                       float scale);
+                       float scale, const float* kscale = nullptr);
+void fold_bias(lf_context* ctx, const float* w, int K, int n_out, int col0, int ld, const float* offset, const float* b_in, float scale,
+               float* b_out);
 // a, b [c][n][ld] fp16 = mask * (LN(z) Wp + bp) * sigmoid(LN(z) Wg + bg)
 // `rows` pair rows of length n (rows = n for the whole pair, fewer for a row shard)
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,

@@ -33,9 +33,7 @@ struct LnGemmParams {
   int act_bf16;
   int64_t rows;             // logical rows
   int transpose, batch, Q;  // logical row (b, i) reads memory row i*batch + b when transpose
-  const float* gamma;
-  const float* beta;
-  float eps;
+  float eps;                // (the LayerNorm's gain and offset are folded into wimg and bias when the weights are prepared)
   int variance;             // 1 two-pass, 2 fast
   const uint8_t* wimg;      // swizzled fp16 image of W^T: [2 atoms][n_pad rows][128 B]
   int n_pad;
@@ -129,8 +127,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
   float* sBias = reinterpret_cast<float*>(sStage + (EPI == LG_EPI_OUTPUT ? LG_EPI_WARPS * 4096
                                                     : EPI == LG_EPI_TRIANGLE ? 4 * 4096 : 0));
   float* sStat = sBias + 544 + 256;                   // [2 stages][2][128]: inverse std, inverse std * mean
-  float* sGamma = sBias + 544;      // [128]
-  float* sBeta = sGamma + 128;      // [128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 512);
   uint64_t* a_full = bars;          // [2]
   uint64_t* a_empty = bars + 2;     // [2]
@@ -166,7 +162,6 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
     uint4* dst = reinterpret_cast<uint4*>(sW);
     for (int i = threadIdx.x; i < w_bytes / 16; i += LG_THREADS) dst[i] = src[i];
     for (int i = threadIdx.x; i < p.n_bias; i += LG_THREADS) sBias[i] = p.bias[i];
-    if (threadIdx.x < 128) { sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
     fence_async_smem();
   }
   if (warp == LG_MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -273,35 +268,34 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
 #pragma unroll
             for (int e = 0; e < 8; ++e) packed[e] = pack_half2(v[u][2 * e], v[u][2 * e + 1]);
           } else {
-          float sum = 0.f;
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};      // four chains instead of one of 16 dependent additions
 #pragma unroll
-          for (int e = 0; e < 16; ++e) sum += v[u][e];
+          for (int e = 0; e < 16; ++e) s4[e & 3] += v[u][e];
+          float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
           sum += __shfl_xor_sync(0xffffffffu, sum, 1);
           sum += __shfl_xor_sync(0xffffffffu, sum, 2);
           sum += __shfl_xor_sync(0xffffffffu, sum, 4);
           const float mean = sum * (1.0f / LG_K);
-          float sq = 0.f;
+          float q4[4] = {0.f, 0.f, 0.f, 0.f};
           if (p.variance == 2) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) sq = fmaf(v[u][e], v[u][e], sq);
+            for (int e = 0; e < 16; ++e) q4[e & 3] = fmaf(v[u][e], v[u][e], q4[e & 3]);
           } else {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; sq = fmaf(d, d, sq); }
+            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; q4[e & 3] = fmaf(d, d, q4[e & 3]); }
           }
+          float sq = (q4[0] + q4[1]) + (q4[2] + q4[3]);
           sq += __shfl_xor_sync(0xffffffffu, sq, 1);
           sq += __shfl_xor_sync(0xffffffffu, sq, 2);
           sq += __shfl_xor_sync(0xffffffffu, sq, 4);
           const float var = p.variance == 2 ? sq * (1.0f / LG_K) - mean * mean : sq * (1.0f / LG_K);
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
-          // element e sits at channel ch(e): 16-bit input 64 (e / 8) + 8 j + e % 8, else 32 (e / 4) + 4 j + e % 4
+          // the gain and offset of the LayerNorm live in the weight image and the bias: the operand is (x - mean) / std
+          const float shift = -mean * inv;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int ch = p.act_bf16 ? 64 * (e >> 2) + 8 * j + 2 * (e & 3) : 32 * (e >> 1) + 4 * j + 2 * (e & 1);
-            const float2 gm = *reinterpret_cast<const float2*>(sGamma + ch);
-            const float2 bt = *reinterpret_cast<const float2*>(sBeta + ch);
-            packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
-          }
+          for (int e = 0; e < 8; ++e)
+            packed[e] = valid ? pack_half2(fmaf(v[u][2 * e], inv, shift), fmaf(v[u][2 * e + 1], inv, shift)) : 0u;
           }
           if (p.a_is_op16 || p.act_bf16) {
             // channels 64 w + 8 j .. + 7: k-atom w, 16-byte chunk j of the row
@@ -814,12 +808,12 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
                   op16* ob = reinterpret_cast<op16*>(p.peer_bias.p[g2]);
 #pragma unroll
                   for (int h = 0; h < 16; ++h)
-                    if (h < p.heads) ob[h * pq + pdst] = __float2half_rn(__uint_as_float(v[h]));
+                    if (h < p.heads) ob[h * pq + pdst] = __float2half_rn(__uint_as_float(v[h]) + sBias[512 + h]);
                 }
               } else {
 #pragma unroll
                 for (int h = 0; h < 16; ++h)
-                  if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]));
+                  if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]) + sBias[512 + h]);
               }
             }
           }
@@ -848,19 +842,35 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
 // W (in,out) float32 [K][n_out] -> fp16 image of W^T in the swizzled K-major layout
 // ([K/64 atoms][n_pad rows][128 B]); rows >= n_out are zero.
 __global__ void pack_weight_image_kernel(const float* __restrict__ w, int K, int n_out, int n_pad, int col0, int ld,
-                                         op16* __restrict__ img, int row0, float scale) {
+                                         op16* __restrict__ img, int row0, float scale, const float* __restrict__ kscale) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_out * K) return;
   int n = idx / K, k = idx % K;
   int row = row0 + n;
   size_t off = (size_t)(k >> 6) * ((size_t)n_pad * 128) + (size_t)row * 128 + ((((k & 63) >> 3) ^ (row & 7)) << 4) + (k & 7) * 2;
-  img[off / 2] = __float2half_rn(w[(size_t)k * ld + col0 + n] * scale);
+  img[off / 2] = __float2half_rn(w[(size_t)k * ld + col0 + n] * scale * (kscale ? kscale[k] : 1.0f));
 }
 
+// kscale (optional, [K]): a LayerNorm gain folded into the rows of W, so that the kernel's producers only standardise
 void pack_weight_image(lf_context* ctx, const float* w, int K, int n_out, int n_pad, int col0, int ld, op16* img, int row0,
-                       float scale) {
+                       float scale, const float* kscale) {
   int total = n_out * K;
-  pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0, scale);
+  pack_weight_image_kernel<<<(total + 255) / 256, 256, 0, ctx->stream>>>(w, K, n_out, n_pad, col0, ld, img, row0, scale, kscale);
+}
+
+// The LayerNorm offset folded into a bias: b_out[c] = scale * (b_in[c] + sum_k offset[k] W[k][col0 + c]) (b_in optional)
+__global__ void fold_bias_kernel(const float* __restrict__ w, int K, int n_out, int col0, int ld, const float* __restrict__ offset,
+                                 const float* __restrict__ b_in, float scale, float* __restrict__ b_out) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n_out) return;
+  double acc = b_in ? (double)b_in[c] : 0.0;
+  for (int k = 0; k < K; ++k) acc += (double)offset[k] * (double)w[(size_t)k * ld + col0 + c];
+  b_out[c] = (float)(acc * scale);
+}
+
+void fold_bias(lf_context* ctx, const float* w, int K, int n_out, int col0, int ld, const float* offset, const float* b_in, float scale,
+               float* b_out) {
+  fold_bias_kernel<<<(n_out + 127) / 128, 128, 0, ctx->stream>>>(w, K, n_out, col0, ld, offset, b_in, scale, b_out);
 }
 
 lf_status make_map_f32_rows(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
@@ -909,8 +919,8 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
   LnGemmParams p{};
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;
-  p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
-  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
+  p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = (const float*)w->h[1]; p.n_bias = 512;
   p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
   p.mask = mask; p.out_a = a; p.out_b = b; p.n = n; p.ld = ld; p.status = (Status*)ctx->tc_status;
   PlaneMaps pm{};
@@ -933,8 +943,8 @@ lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void
   LnGemmParams p{};
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;
-  p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
-  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = w->f[TRI_B4]; p.n_bias = 512;
+  p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 512; p.bias = (const float*)w->h[1]; p.n_bias = 512;
   p.n_chunks = 2; p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_row0[0] = 0; p.chunk_row0[1] = 256;
   p.mask = mask; p.n = n; p.ld = ld; p.status = (Status*)ctx->tc_status;
   p.peer_ranks = ranks; p.ch_per_rank = 128 / ranks; p.peer_plane_rows = n; p.peer_row0 = row0;
@@ -980,7 +990,7 @@ static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const
   LnGemmParams p{};
   if (bias_peers) { p.bias_ranks = ranks; p.bias_rows = bias_rows; p.bias_row0 = row0; p.peer_bias = *bias_peers; }
   p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
-  p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = eps; p.variance = variance;
+  p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 528; p.bias = (const float*)w->h[1]; p.n_bias = 528;
   p.n_chunks = bias ? 3 : 2;
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
@@ -1008,7 +1018,7 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   LnGemmParams p{};
   p.act = o; p.a_is_op16 = 1; p.rows = (int64_t)batch * Q; p.transpose = transpose; p.batch = batch; p.Q = Q;
   p.ldq = (Q + 15) / 16 * 16;
-  p.gamma = w->f[ATT_LN_G]; p.beta = w->f[ATT_LN_B]; p.eps = 1e-5f; p.variance = 1;
+  p.eps = 1e-5f; p.variance = 1;
   p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 128; p.bias = w->f[ATT_BO]; p.n_bias = 128;
   p.n_chunks = 1; p.chunk_n[0] = 128; p.chunk_row0[0] = 0;
   p.resid = resid; p.out = out; p.out_bf16 = act_dtype == LF_DTYPE_BF16;
@@ -1043,7 +1053,7 @@ lf_status triangle_output(lf_context* ctx, ArenaCursor& cur, const op16* x, int 
   LnGemmParams p{};
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;
-  p.gamma = w->f[TRI_LN_G]; p.beta = w->f[TRI_LN_B]; p.eps = eps; p.variance = variance;
+  p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[2]; p.n_pad = 256; p.bias = (const float*)w->h[3]; p.n_bias = 384;
   p.n_chunks = 1; p.chunk_n[0] = 256; p.chunk_row0[0] = 0;
   p.n = n; p.ld = ld; p.tile_per_row = (n + LG_ROWS - 1) / LG_ROWS; p.x_eps = x_eps;

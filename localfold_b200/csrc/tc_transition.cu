@@ -30,7 +30,6 @@ struct TransitionParams {
   const void* act;
   int act_bf16;
   int64_t rows;
-  const float* gamma; const float* beta;
   float eps; int variance;
   const uint8_t* wimg;      // per chunk: W1 slice image, then W2 slice image
   const float* b1;          // [512] (AF2) or [1024] = gate half | value half (AF3)
@@ -65,9 +64,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
   uint8_t* sH = sA + TR_TILE_BYTES;                // hidden chunk (A of GEMM 2)
   float* sB1 = reinterpret_cast<float*>(sH + TR_TILE_BYTES);   // [512]
   float* sB2 = sB1 + 1024;                         // [128]
-  float* sGamma = sB2 + 128;                       // [128]
-  float* sBeta = sGamma + 128;                     // [128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sBeta + 128);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB2 + 128 + 256);
   uint64_t* a_full = bars;            // count 8 producer warps
   uint64_t* a_empty = bars + 1;       // MMA commit
   uint64_t* w_full = bars + 2;        // [2] bulk bytes
@@ -94,7 +91,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
     fence_barrier_init();
   }
   for (int i = threadIdx.x; i < (SWIGLU ? 1024 : 512); i += TR_THREADS) sB1[i] = p.b1[i];
-  if (threadIdx.x < 128) { sB2[threadIdx.x] = p.b2[threadIdx.x]; sGamma[threadIdx.x] = p.gamma[threadIdx.x]; sBeta[threadIdx.x] = p.beta[threadIdx.x]; }
+  if (threadIdx.x < 128) sB2[threadIdx.x] = p.b2[threadIdx.x];
   if (warp == 24) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -170,35 +167,35 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         for (int u = 0; u < 2; ++u) {
           const int row = pw * 16 + (grp * 2 + u) * 4 + sub;
           const bool valid = t * TR_ROWS + row < p.rows;
-          float sum = 0.f;
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};      // four chains instead of one of 16 dependent additions
 #pragma unroll
-          for (int e = 0; e < 16; ++e) sum += v[u][e];
+          for (int e = 0; e < 16; ++e) s4[e & 3] += v[u][e];
+          float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
           sum += __shfl_xor_sync(0xffffffffu, sum, 1);
           sum += __shfl_xor_sync(0xffffffffu, sum, 2);
           sum += __shfl_xor_sync(0xffffffffu, sum, 4);
           const float mean = sum * (1.0f / 128.0f);
-          float sq = 0.f;
+          float q4[4] = {0.f, 0.f, 0.f, 0.f};
           if (p.variance == 2) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) sq = fmaf(v[u][e], v[u][e], sq);
+            for (int e = 0; e < 16; ++e) q4[e & 3] = fmaf(v[u][e], v[u][e], q4[e & 3]);
           } else {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; sq = fmaf(d, d, sq); }
+            for (int e = 0; e < 16; ++e) { const float d = v[u][e] - mean; q4[e & 3] = fmaf(d, d, q4[e & 3]); }
           }
+          float sq = (q4[0] + q4[1]) + (q4[2] + q4[3]);
           sq += __shfl_xor_sync(0xffffffffu, sq, 1);
           sq += __shfl_xor_sync(0xffffffffu, sq, 2);
           sq += __shfl_xor_sync(0xffffffffu, sq, 4);
           const float var = p.variance == 2 ? sq * (1.0f / 128.0f) - mean * mean : sq * (1.0f / 128.0f);
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
+          // the LayerNorm's gain and offset live in the first weight image and its bias: the operand is (x - mean) / std
           uint32_t packed[8];
+          const float shift = -mean * inv;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int ch = p.act_bf16 ? 64 * (e >> 2) + 8 * j + 2 * (e & 3) : 32 * (e >> 1) + 4 * j + 2 * (e & 1);
-            const float2 gm = *reinterpret_cast<const float2*>(sGamma + ch);
-            const float2 bt = *reinterpret_cast<const float2*>(sBeta + ch);
-            packed[e] = valid ? pack_half2((v[u][2 * e] - mean) * inv * gm.x + bt.x, (v[u][2 * e + 1] - mean) * inv * gm.y + bt.y) : 0u;
-          }
+          for (int e = 0; e < 8; ++e)
+            packed[e] = valid ? pack_half2(fmaf(v[u][2 * e], inv, shift), fmaf(v[u][2 * e + 1], inv, shift)) : 0u;
           if (p.act_bf16) {
             // channels 64 w + 8 j .. + 7: k-atom w, 16-byte chunk j of the row
 #pragma unroll
@@ -487,8 +484,8 @@ lf_status transition_run(lf_context* ctx, ArenaCursor& cur, const void* act, int
   if (cur.dry) return LF_OK;
   TransitionParams p{};
   p.act = act; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = rows;
-  p.gamma = w->f[TRN_LN_G]; p.beta = w->f[TRN_LN_B]; p.eps = eps; p.variance = variance;
-  p.wimg = (const uint8_t*)w->h[0]; p.b1 = w->f[TRN_B1]; p.b2 = w->f[TRN_B2];
+  p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[0]; p.b1 = (const float*)w->h[1]; p.b2 = w->f[TRN_B2];
   p.resid = resid; p.out = out; p.status = (Status*)ctx->tc_status;
   // float32 rows updated in place (or written without a residual): the pair tile travels by TMA
   CUtensorMap mo{};

@@ -25,7 +25,7 @@ BLOCK_TOL_BF16_STREAM = 6e-3
 @pytest.fixture(scope="module")
 def dev():
     import localfold_b200 as lf
-    d = lf.Device(0)
+    d = lf.Device(0, stream=torch.cuda.current_stream().cuda_stream)   # the inputs are made by torch on that stream
     yield d
     d.close()
 

@@ -38,6 +38,58 @@ def test_triangle_bf16(dev, n, incoming):
     assert oracle.relative_l2(got, want) <= OP_TOL
 
 
+@pytest.mark.parametrize("incoming", [False, True])
+def test_triangle_bf16_layer_norm_gains_and_offsets(dev, incoming):
+    """The tensor-core path keeps the LayerNorm gains and offsets inside its weight images and biases: a case
+    where they are far from (1, 0), for the input norm (projection and output gate) and the centre norm."""
+    import localfold_b200 as lf
+    from parity_report import record
+    n = 128
+    d = syn.draw(4242)
+    z = d.normal(n, n, 128) + 0.5          # a mean that the offsets' path has to carry
+    mask = syn.residue_pair_mask(n, 0.05)
+    w = syn.af2_triangle_weights(d, 128, 128)
+    w["layerNormInWeight"] = 1 + d.normal(128, std=0.3)
+    w["layerNormInBias"] = d.normal(128, std=0.3)
+    w["layerNormOutWeight"] = 1 + d.normal(128, std=0.3)
+    w["layerNormOutBias"] = d.normal(128, std=0.3)
+    for role in ("AP", "AG", "BP", "BG", "Z", "G"):
+        w[f"linear{role}Bias"] = w[f"linear{role}Bias"] + d.normal(128, std=0.2)
+    cls = lf.TriangleMultiplicationIncomingGpu if incoming else lf.TriangleMultiplicationOutgoingGpu
+    got = cls(dev).run({"shape": {"length": n, "cZ": 128, "cHidden": 128}, "z": z, "mask": mask, "weights": w},
+                       {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.trimul_af2(z, mask, w, 128, 1e-5, incoming)
+    err = oracle.relative_l2(got, want)
+    record("triangle_bf16", f"n={n} incoming={incoming} random LayerNorm gains and offsets", err, OP_TOL)
+    assert np.isfinite(got).all()
+    assert err <= OP_TOL
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_triangle_attention_bf16_layer_norm_gains_and_offsets(dev, transpose):
+    """As above for the attention: the norm's offset reaches q, k, v, the gate and the pair-bias logits."""
+    import localfold_b200 as lf
+    from parity_report import record
+    n = 96
+    d = syn.draw(4343)
+    z = d.normal(n, n, 128) + 0.5
+    mask = syn.residue_pair_mask(n, 0.1)
+    t = syn.af2_attention_weights(d, 128, 4, 128)
+    t["attention"]["queryNormScale"] = 1 + d.normal(128, std=0.3)
+    t["attention"]["queryNormOffset"] = d.normal(128, std=0.3)
+    t["attention"]["gatingBias"] = t["attention"]["gatingBias"] + d.normal(128, std=0.2)
+    t["attention"]["outputBias"] = d.normal(128, std=0.2)
+    pb = dict(t["pairBias"], source="normalized-input")
+    inp = {"activations": z, "mask": mask, "batch": n, "queryLength": n, "channels": 128, "heads": 4,
+           "transpose": transpose, "weights": t["attention"], "pairBias": pb}
+    got = lf.AttentionGpu(dev).run(inp, {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.attention_af2(z, mask, n, n, 128, 4, t["attention"], transpose, pb)
+    err = oracle.relative_l2(got, want)
+    record("attention_bf16", f"n={n} transpose={transpose} random LayerNorm gains and offsets", err, OP_TOL)
+    assert np.isfinite(got).all()
+    assert err <= OP_TOL
+
+
 def test_triangle_bf16_af3_channels_64(dev):
     import localfold_b200 as lf
     n, c = 96, 64
