@@ -67,8 +67,10 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
   uint64_t* bars = reinterpret_cast<uint64_t*>(sB2 + 128 + 256);
   uint64_t* a_full = bars;            // count 8 producer warps
   uint64_t* a_empty = bars + 1;       // MMA commit
-  uint64_t* w_full = bars + 2;        // [2] bulk bytes
-  uint64_t* w_empty = bars + 4;       // [2] MMA commit
+  // the two weight slices of a chunk travel through rings of their own: a first-GEMM slice is released when its GEMM
+  // has completed, two chunks before the second-GEMM slice beside it, and is refilled at once
+  uint64_t* w1_full = bars + 2;       // [2] bulk bytes
+  uint64_t* w1_empty = bars + 4;      // [2] MMA commit
   uint64_t* hacc_full = bars + 6;     // [2] MMA commit
   uint64_t* hacc_empty = bars + 8;    // [2] count 16
   uint64_t* h_full = bars + 10;       // count 16: hidden tile written
@@ -76,7 +78,9 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
   uint64_t* out_full = bars + 12;     // MMA commit
   uint64_t* out_empty = bars + 13;    // count 16
   uint64_t* stage_free = bars + 14;   // count 16: every warp's output copy has finished reading the staging rows
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* w2_full = bars + 15;      // [2] bulk bytes
+  uint64_t* w2_empty = bars + 17;     // [2] MMA commit
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,7 +88,10 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(a_full, 8); mbar_init(a_empty, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); mbar_init(&hacc_full[s], 1); mbar_init(&hacc_empty[s], 16); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&w1_full[s], 1); mbar_init(&w1_empty[s], 1); mbar_init(&w2_full[s], 1); mbar_init(&w2_empty[s], 1);
+      mbar_init(&hacc_full[s], 1); mbar_init(&hacc_empty[s], 16);
+    }
     mbar_init(h_full, 16); mbar_init(h_empty, 1); mbar_init(out_full, 1); mbar_init(out_empty, 16);
     mbar_init(stage_free, 16);
     *abort_flag = 0;
@@ -101,15 +108,20 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
 
   if (warp == 25) {
     // ---------------- weight streamer ----------------
-    if (lane == 0) {
+    // lane 0 feeds the first-GEMM slices, lane 1 the second-GEMM slices
+    if (lane < 2) {
+      uint64_t* full = lane == 0 ? w1_full : w2_full;
+      uint64_t* empty = lane == 0 ? w1_empty : w2_empty;
+      const uint32_t offset = lane == 0 ? 0u : (uint32_t)TR_TILE_BYTES;
+      const uint32_t bytes = lane == 0 ? (uint32_t)TR_TILE_BYTES : W_BYTES - (uint32_t)TR_TILE_BYTES;
       uint32_t g = 0;
       bool ok = true;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
         for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
           const int s = g & 1;
-          if (!mbar_wait(&w_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 50)) { ok = false; break; }
-          mbar_expect_tx(&w_full[s], W_BYTES);
-          bulk_load(sW + s * TR_W_STAGE, p.wimg + (size_t)c * W_BYTES, W_BYTES, &w_full[s]);
+          if (!mbar_wait(&empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 50)) { ok = false; break; }
+          mbar_expect_tx(&full[s], bytes);
+          bulk_load(sW + s * TR_W_STAGE + offset, p.wimg + (size_t)c * W_BYTES + offset, bytes, &full[s]);
         }
       }
     }
@@ -126,8 +138,10 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         const int64_t nrows = p.rows - r0 < TR_ROWS ? p.rows - r0 : TR_ROWS;
         bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.act) + r0 * row_bytes, (uint32_t)nrows * row_bytes);
       }
-      if (!mbar_wait(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
-#pragma unroll 1
+      // The single operand stage is still being read by the previous tile's first GEMMs while this tile is loaded and
+      // normalised into registers (both halves): only the stores wait for it.
+      uint32_t packed[4][8];
+#pragma unroll
       for (int grp = 0; grp < 2; ++grp) {
         float v[2][16];
 #pragma unroll
@@ -191,24 +205,30 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
           float inv = rsqrtf(var + p.eps);
           inv = inv * (1.5f - 0.5f * (var + p.eps) * inv * inv);
           // the LayerNorm's gain and offset live in the first weight image and its bias: the operand is (x - mean) / std
-          uint32_t packed[8];
           const float shift = -mean * inv;
 #pragma unroll
           for (int e = 0; e < 8; ++e)
-            packed[e] = valid ? pack_half2(fmaf(v[u][2 * e], inv, shift), fmaf(v[u][2 * e + 1], inv, shift)) : 0u;
+            packed[grp * 2 + u][e] = valid ? pack_half2(fmaf(v[u][2 * e], inv, shift), fmaf(v[u][2 * e + 1], inv, shift)) : 0u;
+        }
+      }
+      if (!mbar_wait(a_empty, (it & 1) ^ 1, abort_flag, p.status, 51)) break;
+      {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int row = pw * 16 + u * 4 + sub;
           if (p.act_bf16) {
             // channels 64 w + 8 j .. + 7: k-atom w, 16-byte chunk j of the row
 #pragma unroll
             for (int w2 = 0; w2 < 2; ++w2)
               *reinterpret_cast<uint4*>(sA + (uint32_t)w2 * (TR_ROWS * 128) + swizzle128_offset((uint32_t)row, (uint32_t)j)) =
-                  make_uint4(packed[w2 * 4], packed[w2 * 4 + 1], packed[w2 * 4 + 2], packed[w2 * 4 + 3]);
+                  make_uint4(packed[u][w2 * 4], packed[u][w2 * 4 + 1], packed[u][w2 * 4 + 2], packed[u][w2 * 4 + 3]);
           } else {
             // channels 32 w + 4 j .. + 3: k-atom w / 2, 16-byte chunk 4 (w % 2) + j / 2, its half j % 2
 #pragma unroll
             for (int w4 = 0; w4 < 4; ++w4)
               *reinterpret_cast<uint2*>(sA + (uint32_t)(w4 >> 1) * (TR_ROWS * 128) +
                                         swizzle128_offset((uint32_t)row, (uint32_t)((w4 & 1) * 4 + (j >> 1))) + (j & 1) * 8) =
-                  make_uint2(packed[w4 * 2], packed[w4 * 2 + 1]);
+                  make_uint2(packed[u][w4 * 2], packed[u][w4 * 2 + 1]);
           }
         }
       }
@@ -240,7 +260,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         tc_fence_after();
         for (int c = 0; c < TR_CHUNKS; ++c, ++g) {
           const int s = g & 1;
-          if (!mbar_wait(&w_full[s], (g >> 1) & 1, abort_flag, p.status, 54) ||
+          if (!mbar_wait(&w1_full[s], (g >> 1) & 1, abort_flag, p.status, 54) ||
               !mbar_wait(&hacc_empty[s], ((g >> 1) & 1) ^ 1, abort_flag, p.status, 55)) { ok = false; break; }
           tc_fence_after();
           const uint32_t w1 = smem_u32(sW + s * TR_W_STAGE);
@@ -252,6 +272,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
               umma_f16(tmem_base + s * 128, adesc, bdesc, idesc, kk != 0 ? 1u : 0u);
             }
             umma_commit(&hacc_full[s]);
+            umma_commit(&w1_empty[s]);
             if (c == TR_CHUNKS - 1) umma_commit(a_empty);
           }
           __syncwarp();
@@ -260,22 +281,24 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
             if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 56)) { ok = false; break; }
             // the tile's first write of the output accumulator: the previous tile's must have been read
             if (c == 1 && !mbar_wait(out_empty, (it & 1) ^ 1, abort_flag, p.status, 53)) { ok = false; break; }
+            if (!mbar_wait(&w2_full[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, p.status, 63)) { ok = false; break; }
             tc_fence_after();
             if (elect_one()) {
               gemm2(g - 1, c - 1);
               umma_commit(h_empty);
-              umma_commit(&w_empty[(g - 1) & 1]);
+              umma_commit(&w2_empty[(g - 1) & 1]);
             }
             __syncwarp();
           }
         }
         if (!ok) break;
         if (!mbar_wait(h_full, (g - 1) & 1, abort_flag, p.status, 57)) break;
+        if (!mbar_wait(&w2_full[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag, p.status, 64)) break;
         tc_fence_after();
         if (elect_one()) {
           gemm2(g - 1, TR_CHUNKS - 1);
           umma_commit(h_empty);
-          umma_commit(&w_empty[(g - 1) & 1]);
+          umma_commit(&w2_empty[(g - 1) & 1]);
           umma_commit(out_full);
         }
         __syncwarp();
@@ -339,7 +362,12 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
         // the hidden tile is single-buffered: the previous chunk's second GEMM must have read it
         if (!mbar_wait(h_empty, (g & 1) ^ 1, abort_flag, p.status, 59)) { ok = false; break; }
         // ... and it doubles as the staging rows of the previous tile's output: those stores must have read it
-        if (p.tma_out && c == 0 && it > 0 && !mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status, 61)) { ok = false; break; }
+        if (p.tma_out && c == 0 && it > 0) {
+          // this warp's output copies of the previous tile have had a whole hidden chunk's time to read their rows
+          if (lane == 0) { bulk_wait_read(); mbar_arrive(stage_free); }
+          __syncwarp();
+          if (!mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status, 61)) { ok = false; break; }
+        }
         if (SWIGLU) {
           // 16 hidden channels = chunks 2*part, 2*part+1 of the row's single 64-wide k-atom
 #pragma unroll
@@ -401,8 +429,7 @@ __global__ void __launch_bounds__(TR_THREADS, 1) transition_kernel(const __grid_
           }
         }
         __syncwarp();
-        if (lane == 0) { bulk_wait_read(); mbar_arrive(stage_free); }
-        continue;
+        continue;      // (the staging rows are handed back before the next tile's first hidden write, below)
       } else
 #pragma unroll 1
       for (int c0 = part * 32; c0 < part * 32 + 32; c0 += 16) {
