@@ -66,7 +66,9 @@ class Device:
         """``stream``: None - the context makes a stream of its own; an integer - that ``cudaStream_t``
         (0 is CUDA's default stream).  Every call enqueues on that stream and returns without waiting, so
         a device-tensor ``output`` is ready only after ``synchronize()`` or for work enqueued on the
-        same stream (``stream`` gives its handle); work on other streams is not ordered with it."""
+        same stream (``stream`` gives its handle).  Inputs: a context with a stream of its own waits, on
+        the device, for what torch has enqueued on its current stream when a device tensor is handed to a
+        call (``wait_for_torch``); nothing orders torch's later work after the call's results."""
         self.lib = nat.load()
         handle = ctypes.c_void_p()
         if stream is None:
@@ -79,6 +81,20 @@ class Device:
         self.ordinal = ordinal
         self.stream = int(self.lib.lf_context_stream(handle) or 0)
         self._finalizer = weakref.finalize(self, self.lib.lf_context_destroy, handle)
+        self._torch_stream = None
+        if stream is None:
+            _own_stream_devices.setdefault(int(ordinal), weakref.WeakSet()).add(self)
+
+    def wait_for_torch(self):
+        """Makes the context's own stream wait (on the device, no host wait) for the work torch has enqueued so
+        far on its current stream of this GPU: device tensors handed to a call are usually produced there."""
+        import torch
+        current = torch.cuda.current_stream(self.ordinal)
+        if int(current.cuda_stream) == self.stream:
+            return
+        if self._torch_stream is None:
+            self._torch_stream = torch.cuda.ExternalStream(self.stream, device=self.ordinal)
+        self._torch_stream.wait_event(current.record_event())
 
     def require_current_stream(self, what):
         """Raises unless torch's current stream on this device is the context's stream: collectives and
@@ -128,6 +144,7 @@ class Device:
 
 
 _default_device = None
+_own_stream_devices = {}      # GPU ordinal -> contexts that run on a stream of their own
 
 
 def create_device(ordinal: int = 0) -> Device:
@@ -220,6 +237,9 @@ class _Buffer:
         if self.is_device:
             if not value.is_contiguous():
                 raise ValueError("device tensors must be contiguous")
+            # a context with a stream of its own reads this tensor after torch's pending work on it
+            for ctx in tuple(_own_stream_devices.get(value.device.index, ())):
+                ctx.wait_for_torch()
             self.keep = value
             self.ptr = value.data_ptr()
             self.count = value.numel()

@@ -143,3 +143,27 @@ def test_pair_block_relabelling_fullsize(dev, pair):
     stack.close()
     assert bool(torch.isfinite(base).all())
     assert rel_l2(moved, relabel(base, perm)) <= 2e-3
+
+
+def test_context_with_its_own_stream_waits_for_torch_inputs(dev, pair):
+    """A context that runs on a stream of its own is handed a tensor that torch is still producing (a 2 GB gather
+    enqueued just before the call): the library orders its stream after torch's, so the result is the one computed
+    from the finished tensor."""
+    import localfold_b200 as lf
+    z, _, perm = pair
+    w = syn.af2_transition_weights(syn.draw(82), 128, 4)
+    own = lf.Device(0)                       # a stream of its own
+    try:
+        moved = relabel(z, perm)             # torch's stream, not waited for here
+        got = torch.empty((N * N, 128), device="cuda")
+        lf.TransitionGpu(own).run({"activations": moved.reshape(N * N, 128), "rows": N * N, "channels": 128,
+                                   "hiddenChannels": 512, "weights": w}, OPTS, out=got)
+        own.synchronize()
+        torch.cuda.synchronize()
+        want = torch.empty_like(got)
+        lf.TransitionGpu(dev).run({"activations": moved.reshape(N * N, 128), "rows": N * N, "channels": 128,
+                                   "hiddenChannels": 512, "weights": w}, OPTS, out=want)
+        dev.synchronize()
+        assert torch.equal(got, want)
+    finally:
+        own.close()
