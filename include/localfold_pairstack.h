@@ -161,7 +161,13 @@ typedef enum lf_weight_kind {
    * gatingQuery, outputProjection (H*d,c), then the block's
    * singlePairLogitsNormScale, singlePairLogitsNormOffset,
    * singlePairLogitsProjection (cz,H). */
-  LF_WEIGHTS_SINGLE_ATTENTION_AF3 = 8
+  LF_WEIGHTS_SINGLE_ATTENTION_AF3 = 8,
+  /* msaAttention1 of shared/af3/weights/weights.js:670-680: actNormScale,
+   * actNormOffset, pairNormScale, pairNormOffset, pairLogits (cz,H),
+   * vProjection (cm,H*d), gatingQuery (cm,H*d), outputProjection (H*d,cm).
+   * dims: channels = cm, heads, head_dim (not tied to cm / heads),
+   * pair_channels = cz. */
+  LF_WEIGHTS_MSA_ATTENTION_AF3 = 9
 } lf_weight_kind;
 
 /* Shape of the operator the weights belong to; unused fields are 0. */
@@ -329,6 +335,39 @@ typedef struct lf_single_attention_desc {
   const lf_weights* weights;
 } lf_single_attention_desc;
 LF_API lf_status lf_single_attention_run(lf_context* ctx, const lf_single_attention_desc* d, lf_result* r);
+
+/* Af3MsaAttentionGpu.run (webgpu/af3/trunk/msa-attention.js:501-520; CPU form
+ * cpu/af3/trunk/msa.js:164-224): MSA pair-weighted averaging.  The attention
+ * weights come from the pair alone - softmax over keys of LN(pair).pairLogits
+ * with one key mask for every sequence, the maximum of msa_mask over the
+ * depth - and average the values v = LN(msa).vProjection of each sequence;
+ * the result is gated by sigmoid(LN(msa).gatingQuery) and projected back to
+ * the MSA channels.  Float32 arithmetic in either precision mode. */
+typedef struct lf_msa_attention_desc {
+  int32_t sequences, tokens, channels, heads, head_dim, pair_channels;
+  int32_t precision, residual; /* residual: out = msa + update */
+  int32_t space, pair_dtype;   /* lf_dtype of pair in device space */
+  const float* msa;            /* [sequences, tokens, channels] float32 */
+  const float* msa_mask;       /* [sequences, tokens] float32 */
+  const void* pair;            /* [tokens, tokens, pair_channels] */
+  float* out;                  /* [sequences, tokens, channels] float32 */
+  const lf_weights* weights;   /* MSA_ATTENTION_AF3 */
+} lf_msa_attention_desc;
+LF_API lf_status lf_msa_attention_run(lf_context* ctx, const lf_msa_attention_desc* d, lf_result* r);
+
+/* The logits of distogramHead (cpu/af3/trunk/trunk.js:47-60): half =
+ * pair.half_logits (+ bias), logits[i,j] = half[i,j] + half[j,i] - a sum, not a
+ * mean.  `half_logits` (channels, bins) and the optional `bias` (bins) live in
+ * the same space as the pair; the logits are float32. */
+typedef struct lf_distogram_desc {
+  int32_t tokens, channels, bins;
+  int32_t space, pair_dtype;
+  const void* pair;            /* [tokens, tokens, channels] */
+  const float* half_logits;    /* [channels, bins] */
+  const float* bias;           /* [bins] or null */
+  float* out;                  /* [tokens, tokens, bins] */
+} lf_distogram_desc;
+LF_API lf_status lf_distogram_logits_run(lf_context* ctx, const lf_distogram_desc* d, lf_result* r);
 
 /* One block's worth of pair updates on a caller-owned pair, in the
  * reference's order with each update added into the running pair:

@@ -5,9 +5,9 @@ The CUDA library (``lib/liblocalfold_pairstack.so``, C ABI in
 eager fallback - a missing library raises on first use.
 """
 from .operators import (  # noqa: F401
-    Af3GridSelfAttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, AttentionGpu, Device,
+    Af3GridSelfAttentionGpu, Af3MsaAttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, AttentionGpu, Device,
     EncodedTensor, OuterProductMeanGpu, PreparedWeights, RangeError, TransitionGpu,
     TriangleMultiplicationIncomingGpu, TriangleMultiplicationOutgoingGpu,
-    af3_triangle_multiplication, create_device, error_metrics, int5_decode, validate_triangle_input,
+    af3_triangle_multiplication, create_device, distogram_logits, error_metrics, int5_decode, validate_triangle_input,
 )
-from .stack import Af3PairformerStackGpu, EvoformerBlockGpu, PairStackGpu, PreparedPairBlock  # noqa: F401
+from .stack import Af3MsaBlockGpu, Af3PairformerStackGpu, EvoformerBlockGpu, PairStackGpu, PreparedPairBlock  # noqa: F401

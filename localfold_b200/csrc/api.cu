@@ -399,6 +399,22 @@ lf_status build_single_attention_af3(lf_context* ctx, lf_weights* w, const float
   return finish_attention(ctx, w, t[0], t[1], w4, b4, t[7], nullptr, t[8], t[9], t[10], pc);
 }
 
+// AF3 MSA pair-weighted averaging as the gated attention engine sees it: no query and no key (zero
+// columns, so every logit is the pair bias alone), values and gate from the normalised MSA, the pair
+// bias from a pair tensor with a LayerNorm of its own.
+lf_status build_msa_attention_af3(lf_context* ctx, lf_weights* w, const float* const* t, const int64_t* n, int nt) {
+  const int c = w->dims.channels, H = w->dims.heads, d = w->dims.head_dim, HD = H * d, pc = w->dims.pair_channels;
+  if (H <= 0 || d <= 0 || pc <= 0) return lf_fail(ctx, LF_ERR_ARGUMENT, "MSA attention needs heads, head_dim and pair_channels");
+  const Expect e[8] = {{"actNormScale", c}, {"actNormOffset", c}, {"pairNormScale", pc}, {"pairNormOffset", pc},
+                       {"pairLogits", (int64_t)pc * H}, {"vProjection", (int64_t)c * HD}, {"gatingQuery", (int64_t)c * HD},
+                       {"outputProjection", (int64_t)HD * c}};
+  LF_TRY(check_counts(ctx, e, 8, n, nt, t));
+  hvec w4((size_t)c * 4 * HD, 0.f), b4((size_t)4 * HD, 0.f);
+  put_columns(w4, 4 * HD, 2 * HD, t[5], c, HD, HD, 0, 1);
+  put_columns(w4, 4 * HD, 3 * HD, t[6], c, HD, HD, 0, 1);
+  return finish_attention(ctx, w, t[0], t[1], w4, b4, t[7], nullptr, t[2], t[3], t[4], pc);
+}
+
 lf_status build_transition(lf_context* ctx, lf_weights* w, const float* const* t, const int64_t* n, int nt, bool af3) {
   const int c = w->dims.channels, hdn = w->dims.hidden;
   if (hdn <= 0) return lf_fail(ctx, LF_ERR_ARGUMENT, "transition needs hidden channels");
@@ -456,6 +472,7 @@ static lf_status build_weights(lf_context* ctx, lf_weights* w, const float* cons
     case LF_WEIGHTS_ATTENTION_AF2: return build_attention_af2(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_GRID_ATTENTION_AF3: return build_grid_attention_af3(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_SINGLE_ATTENTION_AF3: return build_single_attention_af3(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_MSA_ATTENTION_AF3: return build_msa_attention_af3(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_TRANSITION_AF2: return build_transition(ctx, w, tensors, counts, n_tensors, false);
     case LF_WEIGHTS_TRANSITION_AF3: return build_transition(ctx, w, tensors, counts, n_tensors, true);
     case LF_WEIGHTS_OPM_AF2: return build_opm_af2(ctx, w, tensors, counts, n_tensors);
@@ -1189,6 +1206,64 @@ lf_status lf_single_attention_run(lf_context* ctx, const lf_single_attention_des
     a.pair = st.in(d->pair, (size_t)n * n * d->pair_channels * dtype_size(a.pair_dtype));
     a.out = st.out(d->out, (size_t)n * d->channels * 4);
     att_f32<float>(ctx, cur, a);
+    st.flush();
+    return LF_OK;
+  });
+}
+
+lf_status lf_msa_attention_run(lf_context* ctx, const lf_msa_attention_desc* d, lf_result* r) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!d || !d->msa || !d->msa_mask || !d->pair || !d->out || !d->weights) return lf_fail(ctx, LF_ERR_ARGUMENT, "MSA attention: null argument");
+  if (d->sequences <= 0 || d->tokens <= 0 || d->channels <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "MSA attention dimensions must be positive safe integers");
+  const lf_weights* w = d->weights;
+  if (w->kind != LF_WEIGHTS_MSA_ATTENTION_AF3) return lf_fail(ctx, LF_ERR_ARGUMENT, "weights are not MSA attention weights");
+  if (w->dims.channels != d->channels || w->dims.heads != d->heads || w->dims.head_dim != d->head_dim || w->dims.pair_channels != d->pair_channels)
+    return lf_fail(ctx, LF_ERR_SHAPE, "weights were packed for %d channels, %d heads x %d, %d pair channels", w->dims.channels, w->dims.heads, w->dims.head_dim, w->dims.pair_channels);
+  LF_TRY(check_common(ctx, LF_VARIANCE_FAST, d->precision, d->space, d->space == LF_SPACE_HOST ? LF_DTYPE_F32 : d->pair_dtype, 1e-5f));
+  if (d->head_dim > 64) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "head dimension %d exceeds 64", d->head_dim);
+  const bool host = d->space == LF_SPACE_HOST;
+  const int S = d->sequences, n = d->tokens;
+  const size_t R = (size_t)S * n;
+  return run_with_arena(ctx, r, host, [&](ArenaCursor& cur) -> lf_status {
+    Staging st{ctx, &cur, host};
+    AttArgs a{};
+    a.batch = S; a.Q = n; a.ch = d->channels; a.heads = d->heads; a.d = d->head_dim; a.transpose = 0;
+    a.variance = LF_VARIANCE_FAST; a.residual = d->residual ? 1 : 0; a.bias_mode = 1; a.bias_swap = 0;
+    a.pair_ch = d->pair_channels; a.pair_dtype = host ? LF_DTYPE_F32 : d->pair_dtype; a.pair_variance = LF_VARIANCE_FAST;
+    a.mask_mode = 0; a.clamp = 0; a.eps = 1e-5f; a.pair_eps = 1e-5f; a.act_dtype = LF_DTYPE_F32; a.w = w;
+    a.act = st.in(d->msa, R * d->channels * 4);
+    const float* msa_mask = (const float*)st.in(d->msa_mask, R * 4);
+    float* key_mask = cur.take<float>(R);
+    LAUNCH(ctx, cur, simt::msa_key_mask_kernel, lf_ceil_div(n, 128), 128, 0, msa_mask, S, n, key_mask);
+    a.mask = key_mask;
+    a.pair = st.in(d->pair, (size_t)n * n * d->pair_channels * dtype_size(a.pair_dtype));
+    a.out = st.out(d->out, R * d->channels * 4);
+    att_f32<float>(ctx, cur, a);
+    st.flush();
+    return LF_OK;
+  });
+}
+
+lf_status lf_distogram_logits_run(lf_context* ctx, const lf_distogram_desc* d, lf_result* r) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!d || !d->pair || !d->half_logits || !d->out) return lf_fail(ctx, LF_ERR_ARGUMENT, "distogram: null argument");
+  if (d->tokens <= 0 || d->channels <= 0 || d->bins <= 0) return lf_fail(ctx, LF_ERR_SHAPE, "distogram dimensions must be positive safe integers");
+  LF_TRY(check_common(ctx, LF_VARIANCE_FAST, LF_PRECISION_F32, d->space, d->space == LF_SPACE_HOST ? LF_DTYPE_F32 : d->pair_dtype, 1e-5f));
+  const bool host = d->space == LF_SPACE_HOST;
+  const int n = d->tokens, c = d->channels, bins = d->bins;
+  const size_t P = (size_t)n * n;
+  const int dt = host ? LF_DTYPE_F32 : d->pair_dtype;
+  if (dt != LF_DTYPE_F32) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "distogram logits take a float32 pair");
+  return run_with_arena(ctx, r, host, [&](ArenaCursor& cur) -> lf_status {
+    Staging st{ctx, &cur, host};
+    const void* pair = st.in(d->pair, P * c * dtype_size(dt));
+    const float* w = (const float*)st.in(d->half_logits, (size_t)c * bins * 4);
+    const float* bias = d->bias ? (const float*)st.in(d->bias, (size_t)bins * 4) : nullptr;
+    float* out = (float*)st.out(d->out, P * bins * 4);
+    const float* x = (const float*)pair;
+    float* half = cur.take<float>(P * bins);
+    sgemm(ctx, cur, false, false, 0, (int)P, bins, c, x, c, 0, w, bins, 0, half, bins, 0, bias, 0, 1);
+    LAUNCH(ctx, cur, simt::symmetrise_sum_kernel, lf_ceil_div((int64_t)P * bins, 256), 256, 0, half, n, bins, out);
     st.flush();
     return LF_OK;
   });

@@ -294,6 +294,27 @@ __global__ void pair_bias_kernel(const TIn* __restrict__ pair, int Q, int ch, in
   }
 }
 
+// One key mask for every sequence of an MSA: out[s][t] = max over s' of mask[s'][t] (AF3 pair-weighted
+// averaging: a token any sequence covers is a key for all of them).
+__global__ void msa_key_mask_kernel(const float* __restrict__ mask, int sequences, int tokens, float* __restrict__ out) {
+  int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float largest = 0.f;
+  for (int s = 0; s < sequences; ++s) largest = fmaxf(largest, mask[(int64_t)s * tokens + t]);
+  for (int s = 0; s < sequences; ++s) out[(int64_t)s * tokens + t] = largest;
+}
+
+// out[i][j][b] = half[i][j][b] + half[j][i][b]: a sum over the two token orders, not a mean.
+__global__ void symmetrise_sum_kernel(const float* __restrict__ half, int tokens, int bins, float* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)tokens * tokens * bins;
+  if (idx >= total) return;
+  int b = (int)(idx % bins);
+  int64_t p = idx / bins;
+  int i = (int)(p / tokens), j = (int)(p % tokens);
+  out[idx] = half[idx] + half[((int64_t)j * tokens + i) * bins + b];
+}
+
 // ---------------------------------------------------------------------------
 // Gated attention core, float32, online softmax.  One warp per query, 8 queries
 // per block, key/value tiles of 32 rows staged in shared memory.

@@ -699,6 +699,86 @@ class Af3SingleAttentionGpu:
                 owned.close()
 
 
+MSA_ATTENTION_AF3_ORDER = ("actNormScale", "actNormOffset", "pairNormScale", "pairNormOffset", "pairLogits",
+                           "vProjection", "gatingQuery", "outputProjection")
+
+
+def prepare_msa_attention_weights(device, weights, channels, pair_channels):
+    """Resident weights of ``msaAttention1`` (``shared/af3/weights/weights.js:670-680``); the head width is
+    ``weights["dimension"]``, not ``channels / heads``."""
+    return PreparedWeights(device, nat.WEIGHTS_MSA_ATTENTION_AF3,
+                           {"channels": channels, "heads": int(weights["heads"]), "head_dim": int(weights["dimension"]),
+                            "pair_channels": pair_channels}, [weights[k] for k in MSA_ATTENTION_AF3_ORDER])
+
+
+class Af3MsaAttentionGpu:
+    """``Af3MsaAttentionGpu`` (``webgpu/af3/trunk/msa-attention.js:501``; CPU form
+    ``cpu/af3/trunk/msa.js:164-224``): ``run(msa, msaMask, pair, {sequences, tokens, msaChannels,
+    pairChannels}, weights, options)`` - MSA pair-weighted averaging, float32 arithmetic."""
+
+    def __init__(self, device: Device | None = None):
+        self.device = _device(device)
+
+    def run(self, msa, msa_mask, pair, shape, weights, options=None, out=None):
+        S, n = int(shape["sequences"]), int(shape["tokens"])
+        cm, cz = int(shape["msaChannels"]), int(shape["pairChannels"])
+        dev = self.device
+        owned = None
+        if not isinstance(weights, PreparedWeights):
+            if not isinstance(weights.get("heads"), (int, np.integer)) or not isinstance(weights.get("dimension"), (int, np.integer)):
+                raise ValueError("weights.heads and weights.dimension must be integers")
+            owned = weights = prepare_msa_attention_weights(dev, weights, cm, cz)
+        try:
+            a = _Buffer(msa)
+            m = _Buffer(msa_mask)
+            p = _Buffer(pair)
+            _expect_length("msa", a, S * n * cm)
+            _expect_length("msaMask", m, S * n)
+            _expect_length("pair", p, n * n * cz)
+            obuf, output = _out_like(a, (S, n, cm), out)
+            opts = options or {}
+            desc = nat.MsaAttentionDesc(S, n, cm, weights.dims["heads"], weights.dims["head_dim"], cz, _precision(opts),
+                                        1 if opts.get("residual") else 0,
+                                        nat.SPACE_DEVICE if a.is_device else nat.SPACE_HOST, p.dtype,
+                                        a.ptr, m.ptr, p.ptr, obuf.ptr, weights.handle)
+            res = nat.Result()
+            dev.check(dev.lib.lf_msa_attention_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
+            return _result(dev, res, output)
+        finally:
+            if owned is not None:
+                dev.synchronize()
+                owned.close()
+
+
+def distogram_logits(device, pair, tokens, channels, half_logits, bias=None):
+    """The logits of ``distogramHead`` (``cpu/af3/trunk/trunk.js:47-60``): ``pair . halfLogits`` plus its
+    transpose over the token axes (a sum).  ``pair`` and the weights are host arrays or float32 device tensors."""
+    dev = _device(device)
+    p = _Buffer(pair)
+    _expect_length("pair", p, tokens * tokens * channels)
+    if p.is_device:
+        import torch
+        w = half_logits if getattr(half_logits, "is_cuda", False) else torch.as_tensor(np.asarray(half_logits, np.float32)).to(pair.device)
+        b = None if bias is None else (bias if getattr(bias, "is_cuda", False) else torch.as_tensor(np.asarray(bias, np.float32)).to(pair.device))
+    else:
+        w, b = half_logits, bias
+    wb = _Buffer(w)
+    bins = wb.count // channels
+    _expect_length("halfLogits", wb, channels * bins)
+    bb = None if b is None else _Buffer(b)
+    if p.is_device:
+        output = pair.new_empty((tokens, tokens, bins), dtype=w.dtype)
+        obuf = _Buffer(output)
+    else:
+        output = np.empty((tokens, tokens, bins), np.float32)
+        obuf = _Buffer(output)
+    desc = nat.DistogramDesc(tokens, channels, bins, nat.SPACE_DEVICE if p.is_device else nat.SPACE_HOST, p.dtype,
+                             p.ptr, wb.ptr, None if bb is None else bb.ptr, obuf.ptr)
+    res = nat.Result()
+    dev.check(dev.lib.lf_distogram_logits_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
+    return _result(dev, res, output)
+
+
 # ---------------------------------------------------------------------------
 # int5
 

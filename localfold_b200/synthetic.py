@@ -183,5 +183,48 @@ def af3_pairformer(seed, n=384, cz=128, cs=384, blocks=1, pair_heads=4, single_h
     return pair, single, np.ones((n, n), np.float32), np.ones(n, np.float32), weights
 
 
+def af3_opm_weights(d: _Draw, cm, co, cz):
+    """``outerProductMean`` of an AF3 MSA block (``cpu/af3/trunk/msa.js:72-155``): no left/right biases."""
+    return {"outerChannels": co, "layerNormInputScale": 1 + d.normal(cm, std=0.1), "layerNormInputOffset": d.normal(cm, std=0.1),
+            "leftProjection": d.linear(cm, cm, co), "rightProjection": d.linear(cm, cm, co),
+            "outputW": d.linear(co * co, co * co, cz), "outputB": d.normal(cz, std=0.1)}
+
+
+def af3_msa_attention_weights(d: _Draw, cm, cz, heads, dim):
+    """``msaAttention1`` (``shared/af3/weights/weights.js:670-680``); ``heads * dim`` need not equal ``cm``."""
+    hd = heads * dim
+    return {"heads": heads, "dimension": dim, "actNormScale": 1 + d.normal(cm, std=0.1), "actNormOffset": d.normal(cm, std=0.1),
+            "pairNormScale": 1 + d.normal(cz, std=0.1), "pairNormOffset": d.normal(cz, std=0.1),
+            "pairLogits": d.linear(cz, cz, heads), "vProjection": d.linear(cm, cm, hd),
+            "gatingQuery": d.linear(cm, cm, hd), "outputProjection": d.linear(hd, hd, cm)}
+
+
+def af3_msa_block_weights(d: _Draw, cm=64, cz=128, co=32, msa_heads=8, msa_dim=8, pair_heads=4):
+    """``msaBlockWeights`` (``shared/af3/weights/weights.js:640-700``)."""
+    return {
+        "msaChannels": cm, "pairChannels": cz,
+        "outerProductMean": af3_opm_weights(d, cm, co, cz),
+        "msaAttention1": af3_msa_attention_weights(d, cm, cz, msa_heads, msa_dim),
+        "msaTransition": af3_transition_weights(d, cm),
+        "triangleMultiplicationOutgoing": af3_triangle_weights(d, cz),
+        "triangleMultiplicationIncoming": af3_triangle_weights(d, cz),
+        "pairAttention1": af3_grid_attention_weights(d, cz, pair_heads, cz // pair_heads),
+        "pairAttention2": af3_grid_attention_weights(d, cz, pair_heads, cz // pair_heads),
+        "pairTransition": af3_transition_weights(d, cz),
+    }
+
+
+def af3_msa_block(seed, S=16, n=64, cm=64, cz=128, co=32, msa_heads=8, msa_dim=8, pair_heads=4, gaps=0.2):
+    """One AF3 MSA block: msa, pair ~ N(0,1); a random ``gaps`` fraction of the MSA entries below the first
+    row masked out (so the coverage count and the key mask both matter); pair mask ones."""
+    d = _Draw(seed)
+    msa = d.normal(S, n, cm)
+    pair = d.normal(n, n, cz)
+    msa_mask = (d.rng.random((S, n)) >= gaps).astype(np.float32)
+    msa_mask[0] = 1
+    pair_mask = np.ones((n, n), np.float32)
+    return msa, pair, msa_mask, pair_mask, af3_msa_block_weights(d, cm, cz, co, msa_heads, msa_dim, pair_heads)
+
+
 def draw(seed):
     return _Draw(seed)

@@ -361,6 +361,69 @@ def af3_pairformer_block(pair, single, pair_mask, seq_mask, w, swap_transposed_b
     return pair, single
 
 
+def msa_attention_af3(msa, msa_mask, pair, weights):
+    """``msaAttention`` (``cpu/af3/trunk/msa.js:164-224``): MSA pair-weighted averaging."""
+    a, pa = _f(msa)
+    S, n, cm = a.shape
+    m, pm = _f(msa_mask)
+    z, pz = _f(pair)
+    cz = z.shape[-1]
+    heads, dim = int(weights["heads"]), int(weights["dimension"])
+    names = ("actNormScale", "actNormOffset", "pairNormScale", "pairNormOffset", "pairLogits", "vProjection",
+             "gatingQuery", "outputProjection")
+    keep = [_f(weights[k]) for k in names]
+    out = np.empty((S, n, cm), np.float32)
+    lib().orc_msa_attention_af3(pa, pm, pz, _i(S), _i(n), _i(cm), _i(cz), _i(heads), _i(dim),
+                                *[k[1] for k in keep], out.ctypes.data_as(_FP))
+    return out
+
+
+def msa_block_af3(msa, pair, msa_mask, pair_mask, w, swap_transposed_bias, msa_update_before_outer_product,
+                  bias_after_norm=False):
+    """``msaBlock`` (``cpu/af3/trunk/msa.js:235-287``): the outer product mean and the MSA update in the
+    order the dialect names (it has no default there either), then the five pair updates."""
+    if msa_update_before_outer_product not in (True, False):
+        raise ValueError("dialect.msaUpdateBeforeOuterProduct has no default")
+    msa = np.array(msa, np.float32, copy=True)
+    pair = np.array(pair, np.float32, copy=True)
+    cz = pair.shape[-1]
+
+    def outer_product():
+        nonlocal pair
+        pair = pair + outer_product_mean_af3(msa, msa_mask, w["outerProductMean"], cz, bias_after_norm)
+
+    def update_msa():
+        nonlocal msa
+        msa = msa + msa_attention_af3(msa, msa_mask, pair, w["msaAttention1"])
+        S, n, cm = msa.shape
+        msa = msa + transition_af3(msa.reshape(S * n, cm), w["msaTransition"]).reshape(S, n, cm)
+
+    if msa_update_before_outer_product:
+        update_msa()
+        outer_product()
+    else:
+        outer_product()
+        update_msa()
+    pair = pair + trimul_af3(pair, pair_mask, w["triangleMultiplicationOutgoing"], False)
+    pair = pair + trimul_af3(pair, pair_mask, w["triangleMultiplicationIncoming"], True)
+    pair = pair + grid_attention_af3(pair, pair_mask, w["pairAttention1"], False, swap_transposed_bias)
+    pair = pair + grid_attention_af3(pair, pair_mask, w["pairAttention2"], True, swap_transposed_bias)
+    pair = pair + transition_af3(pair, w["pairTransition"])
+    return msa, pair
+
+
+def distogram_logits(pair, half_logits, bias=None):
+    """The logits of ``distogramHead`` (``cpu/af3/trunk/trunk.js:47-60``): half + half transposed (a sum)."""
+    z, pz = _f(pair)
+    n, _, cz = z.shape
+    w, pw = _f(half_logits)
+    bins = w.size // cz
+    b = _f(bias)
+    out = np.empty((n, n, bins), np.float32)
+    lib().orc_distogram_logits(pz, _i(n), _i(cz), _i(bins), pw, b[1], out.ctypes.data_as(_FP))
+    return out
+
+
 def relative_l2(actual, expected) -> float:
     """``relativeRms`` of the reference's checkers: ||a-b|| / ||b||
     (``tools/gpu/relative-rms.js:63-75``)."""

@@ -665,6 +665,79 @@ ORC_API void orc_pair_logits_af3(const float* pair, int n, int ch, int heads,
 }
 
 /* ------------------------------------------------------------------------- */
+/* AF3 MSA pair-weighted averaging: values from the MSA, weights from the pair only (no query, no key).
+ * cpu/af3/trunk/msa.js:164-224.  All weights (in,out); LayerNorms are the fast-variance form; one key mask
+ * for every sequence, the maximum of the MSA mask over the depth (:179-187); the softmax row is float32
+ * (softmaxRows, msa.js:34-52).  width = heads * dim need not equal the MSA channels.                     */
+ORC_API void orc_msa_attention_af3(const float* msa, const float* msa_mask, const float* pair, int sequences,
+                                   int tokens, int cm, int cz, int heads, int dim, const float* act_scale,
+                                   const float* act_offset, const float* pair_scale, const float* pair_offset,
+                                   const float* pair_logits, const float* wv, const float* wgate, const float* wo,
+                                   float* out) {
+  const int width = heads * dim;
+  const int64_t rows = (int64_t)sequences * tokens, pairs = (int64_t)tokens * tokens;
+  float* nrm = (float*)malloc((size_t)rows * cm * 4);
+  orc_layer_norm(msa, rows, cm, act_scale, act_offset, 1e-5, 1, nrm);
+  float* pnrm = (float*)malloc((size_t)pairs * cz * 4);
+  orc_layer_norm(pair, pairs, cz, pair_scale, pair_offset, 1e-5, 1, pnrm);
+  float* flat = (float*)malloc((size_t)pairs * heads * 4);
+  orc_linear(pnrm, pairs, cz, heads, pair_logits, NULL, 0, flat);
+  float* key_mask = (float*)malloc((size_t)tokens * 4);
+  for (int t = 0; t < tokens; ++t) {
+    float largest = 0;
+    for (int s = 0; s < sequences; ++s) if (msa_mask[(size_t)s * tokens + t] > largest) largest = msa_mask[(size_t)s * tokens + t];
+    key_mask[t] = largest;
+  }
+  float* weights = (float*)malloc((size_t)heads * pairs * 4);
+#pragma omp parallel for schedule(static)
+  for (int h = 0; h < heads; ++h)
+    for (int i = 0; i < tokens; ++i) {
+      float* row = weights + (size_t)h * pairs + (size_t)i * tokens;
+      for (int j = 0; j < tokens; ++j)
+        row[j] = (float)((double)flat[((size_t)i * tokens + j) * heads + h] + 1e9 * ((double)key_mask[j] - 1.0));
+      softmax_row_f32(row, tokens);
+    }
+  float* values = (float*)malloc((size_t)rows * width * 4);
+  orc_linear(nrm, rows, cm, width, wv, NULL, 0, values);
+  float* averaged = (float*)malloc((size_t)rows * width * 4);
+#pragma omp parallel for schedule(static)
+  for (int64_t si = 0; si < rows; ++si) {
+    const int s = (int)(si / tokens), i = (int)(si % tokens);
+    for (int h = 0; h < heads; ++h) {
+      const float* wrow = weights + (size_t)h * pairs + (size_t)i * tokens;
+      for (int d = 0; d < dim; ++d) {
+        double total = 0;
+        for (int j = 0; j < tokens; ++j) total += (double)wrow[j] * (double)values[((size_t)s * tokens + j) * width + h * dim + d];
+        averaged[(size_t)si * width + h * dim + d] = (float)total;
+      }
+    }
+  }
+  float* gate = (float*)malloc((size_t)rows * width * 4);
+  orc_linear(nrm, rows, cm, width, wgate, NULL, 0, gate);
+  for (int64_t i = 0; i < rows * width; ++i) averaged[i] = (float)((double)averaged[i] * sigmoid_d(gate[i]));
+  orc_linear(averaged, rows, width, cm, wo, NULL, 0, out);
+  free(gate); free(averaged); free(values); free(weights); free(key_mask); free(flat); free(pnrm); free(nrm);
+}
+
+/* Distogram logits: one half from a linear over the pair, symmetrised by a SUM with its transpose over the
+ * two token axes (not a mean).  cpu/af3/trunk/trunk.js:47-60.  `bias` may be null (AlphaFold 3 has none).  */
+ORC_API void orc_distogram_logits(const float* pair, int tokens, int cz, int bins, const float* w, const float* bias,
+                                  float* out) {
+  const int64_t pairs = (int64_t)tokens * tokens;
+  float* half = (float*)malloc((size_t)pairs * bins * 4);
+  orc_linear(pair, pairs, cz, bins, w, bias, 0, half);
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < tokens; ++i)
+    for (int j = 0; j < tokens; ++j) {
+      const float* f = half + ((size_t)i * tokens + j) * bins;
+      const float* b = half + ((size_t)j * tokens + i) * bins;
+      float* o = out + ((size_t)i * tokens + j) * bins;
+      for (int k = 0; k < bins; ++k) o[k] = f[k] + b[k];
+    }
+  free(half);
+}
+
+/* ------------------------------------------------------------------------- */
 /* int5 tensor decode: groups of `block` codes, 5 bits each, least significant
  * bit first in a little-endian bit stream (block*5/8 bytes per group), one
  * fp16 scale and one fp16 zero point per group; value = code*scale + zero in
