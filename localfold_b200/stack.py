@@ -268,21 +268,22 @@ class Af3PairformerStackGpu:
         return out
 
 
-class Af3MsaBlockGpu:
-    """One block of the AF3 MSA stack, ``msaBlock`` (``cpu/af3/trunk/msa.js:235-287``; the GPU stack of the
-    reference is ``Af3MsaStackGpu``, ``webgpu/af3/trunk/msa-stack.js:67``): the outer product mean into the
-    pair and the MSA update (pair-weighted averaging, then the MSA transition) in the order
-    ``dialect["msaUpdateBeforeOuterProduct"]`` names - it has no default - followed by the five pair updates.
-    ``run(state, weights, dialect, options)`` with ``state = {msa, pair, msaMask, pairMask, sequences,
-    tokens}``; host arrays are uploaded once, the MSA and the pair stay on the device for the whole block and
-    are read back once (CUDA tensors are updated in place and returned)."""
+class Af3MsaStackGpu:
+    """``Af3MsaStackGpu.run(state, blocks, dialect, options)`` (``webgpu/af3/trunk/msa-stack.js:67-89``): the
+    blocks of the AF3 MSA stack, each ``msaBlock`` (``cpu/af3/trunk/msa.js:235-287``) - the outer product mean
+    into the pair and the MSA update (pair-weighted averaging, then the MSA transition) in the order
+    ``dialect["msaUpdateBeforeOuterProduct"]`` names (it has no default), followed by the five pair updates.
+    ``state = {msa, pair, msaMask, pairMask, sequences, tokens}``; host arrays are uploaded once, the MSA and the
+    pair stay on the device for the whole stack and are read back once; CUDA tensors are updated in place and
+    returned (``options["keepPair"]`` returns the device tensors as ``pairTensor`` / ``msaTensor`` either way, the
+    hand-over to the pairformer stack that follows); ``options["onBlock"]`` is called after each block."""
 
     def __init__(self, device=None):
         self.device = _device(device)
 
-    def run(self, state, weights, dialect, options=None):
+    def run(self, state, blocks, dialect, options=None):
         import torch
-        from .operators import Af3MsaAttentionGpu, OuterProductMeanGpu, prepare_msa_attention_weights, OPM_WEIGHT_ORDER
+        from .operators import Af3MsaAttentionGpu, OPM_WEIGHT_ORDER, prepare_msa_attention_weights
         if dialect is None or dialect.get("swapTransposedBias") not in (True, False):
             raise ValueError("dialect.swapTransposedBias has no default")
         if dialect.get("msaUpdateBeforeOuterProduct") not in (True, False):
@@ -290,17 +291,23 @@ class Af3MsaBlockGpu:
                              "the pre-update MSA and OpenDDE off the updated one")
         if dialect.get("outerProductBiasAfterNorm"):
             raise NotImplementedError("the bias-after-normalisation form of the outer product mean is not built")
+        if len(blocks) == 0:
+            raise nat.RangeError("the MSA stack requires at least one block")
         opts = dict(options or {})
         dev = self.device
         S, n = int(state["sequences"]), int(state["tokens"])
-        cm, cz = int(weights["msaChannels"]), int(weights["pairChannels"])
+        cm, cz = int(blocks[0]["msaChannels"]), int(blocks[0]["pairChannels"])
         where = f"cuda:{dev.ordinal}"
 
         def resident(value, shape):
             if getattr(value, "is_cuda", False):
+                if value.numel() != int(np.prod(shape)):
+                    raise nat.RangeError(f"state tensor has {value.numel()} values; expected {int(np.prod(shape))}")
                 return value.view(shape), True
-            host = np.ascontiguousarray(np.asarray(value, np.float32)).reshape(shape)
-            return torch.from_numpy(host).to(where), False
+            host = np.ascontiguousarray(np.asarray(value, np.float32))
+            if host.size != int(np.prod(shape)):
+                raise nat.RangeError(f"state array has {host.size} values; expected {int(np.prod(shape))}")
+            return torch.from_numpy(host.reshape(shape)).to(where), False
 
         stream = torch.cuda.ExternalStream(dev.stream, device=where) if dev.stream else torch.cuda.default_stream(where)
         with torch.cuda.stream(stream):
@@ -308,57 +315,74 @@ class Af3MsaBlockGpu:
             pair, pair_given = resident(state["pair"], (n, n, cz))
             msa_mask, _ = resident(state["msaMask"], (S, n))
             pair_mask, _ = resident(state["pairMask"], (n, n))
-            opm = weights["outerProductMean"]
-            co = int(opm["outerChannels"])
-            zero = np.zeros(co, np.float32)
-            opm_af2 = {"layerNormScale": opm["layerNormInputScale"], "layerNormOffset": opm["layerNormInputOffset"],
-                       "leftWeight": opm["leftProjection"], "leftBias": opm.get("leftProjectionBias", zero),
-                       "rightWeight": opm["rightProjection"], "rightBias": opm.get("rightProjectionBias", zero),
-                       "outputWeight": opm["outputW"], "outputBias": opm["outputB"]}
-            opm_w = PreparedWeights(dev, nat.WEIGHTS_OPM_AF2, {"channels": cm, "hidden": co, "out_channels": cz},
-                                    [opm_af2[k] for k in OPM_WEIGHT_ORDER])
-            att_w = prepare_msa_attention_weights(dev, weights["msaAttention1"], cm, cz)
-            t = weights["msaTransition"]
-            trn_w = PreparedWeights(dev, nat.WEIGHTS_TRANSITION_AF3,
-                                    {"channels": cm, "hidden": int(np.asarray(t["transition2"]).shape[0])},
-                                    [t[k] for k in TRANSITION_AF3_ORDER])
-            stack = PairStackGpu(dev).prepare([weights], cz, cz)
+            prepared = []
+            for w in blocks:      # resident weights of the MSA track, prepared before the first block runs
+                opm = w["outerProductMean"]
+                co = int(opm["outerChannels"])
+                zero = np.zeros(co, np.float32)
+                opm_af2 = {"layerNormScale": opm["layerNormInputScale"], "layerNormOffset": opm["layerNormInputOffset"],
+                           "leftWeight": opm["leftProjection"], "leftBias": opm.get("leftProjectionBias", zero),
+                           "rightWeight": opm["rightProjection"], "rightBias": opm.get("rightProjectionBias", zero),
+                           "outputWeight": opm["outputW"], "outputBias": opm["outputB"]}
+                t = w["msaTransition"]
+                prepared.append((co,
+                                 PreparedWeights(dev, nat.WEIGHTS_OPM_AF2, {"channels": cm, "hidden": co, "out_channels": cz},
+                                                 [opm_af2[k] for k in OPM_WEIGHT_ORDER]),
+                                 prepare_msa_attention_weights(dev, w["msaAttention1"], cm, cz),
+                                 PreparedWeights(dev, nat.WEIGHTS_TRANSITION_AF3,
+                                                 {"channels": cm, "hidden": int(np.asarray(t["transition2"]).shape[0])},
+                                                 [t[k] for k in TRANSITION_AF3_ORDER])))
+            stack = PairStackGpu(dev).prepare(blocks, cz, cz)
             sub = {"precision": opts.get("precision", "f32"), "residual": True}
             launches = 0
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record(stream)
-
-            def outer_product():
-                r = OuterProductMeanGpu(dev).run({"sequences": S, "length": n, "cM": cm, "cOuter": co, "cZ": cz,
-                                                  "activations": msa, "mask": msa_mask, "weights": opm_w},
-                                                 dict(sub, variance="fast"), out=pair)
-                return r["launches"]
-
-            def update_msa():
-                r1 = Af3MsaAttentionGpu(dev).run(msa, msa_mask, pair, {"sequences": S, "tokens": n, "msaChannels": cm,
-                                                                      "pairChannels": cz}, att_w, sub, out=msa)
-                r2 = Af3TransitionGpu(dev).run(msa.view(S * n, cm), {"rows": S * n, "channels": cm, "factor": 4}, trn_w, sub,
-                                               out=msa.view(S * n, cm))
-                return r1["launches"] + r2["launches"]
-
             try:
-                if dialect["msaUpdateBeforeOuterProduct"]:
-                    launches += update_msa()
-                    launches += outer_product()
-                else:
-                    launches += outer_product()
-                    launches += update_msa()
-                r = stack.run(pair, pair_mask, opts, first_block=0, n_blocks=1, dialect=dialect)
-                launches += r["launches"]
+                for b, (co, opm_w, att_w, trn_w) in enumerate(prepared):
+                    def outer_product():
+                        return OuterProductMeanGpu(dev).run({"sequences": S, "length": n, "cM": cm, "cOuter": co, "cZ": cz,
+                                                             "activations": msa, "mask": msa_mask, "weights": opm_w},
+                                                            dict(sub, variance="fast"), out=pair)["launches"]
+
+                    def update_msa():
+                        r1 = Af3MsaAttentionGpu(dev).run(msa, msa_mask, pair, {"sequences": S, "tokens": n, "msaChannels": cm,
+                                                                              "pairChannels": cz}, att_w, sub, out=msa)
+                        r2 = Af3TransitionGpu(dev).run(msa.view(S * n, cm), {"rows": S * n, "channels": cm, "factor": 4},
+                                                       trn_w, sub, out=msa.view(S * n, cm))
+                        return r1["launches"] + r2["launches"]
+
+                    if dialect["msaUpdateBeforeOuterProduct"]:
+                        launches += update_msa()
+                        launches += outer_product()
+                    else:
+                        launches += outer_product()
+                        launches += update_msa()
+                    launches += stack.run(pair, pair_mask, opts, first_block=b, n_blocks=1, dialect=dialect)["launches"]
+                    if opts.get("onBlock"):
+                        opts["onBlock"](b)
                 stop.record(stream)
                 dev.synchronize()
             finally:
                 dev.synchronize()
                 stack.close()
-                for w in (opm_w, att_w, trn_w):
-                    w.close()
-            out = {"elapsedMilliseconds": float(start.elapsed_time(stop)), "memory": {"peakBytes": 0}, "launches": launches,
-                   "msa": msa if msa_given else msa.cpu().numpy(),
-                   "pair": pair if pair_given else pair.float().cpu().numpy()}
+                for _, opm_w, att_w, trn_w in prepared:
+                    for w in (opm_w, att_w, trn_w):
+                        w.close()
+            out = {"elapsedMilliseconds": float(start.elapsed_time(stop)), "memory": {"peakBytes": 0}, "launches": launches}
+            if opts.get("keepPair"):
+                out.update(msa=None, pair=None, msaTensor=msa, pairTensor=pair)
+            else:
+                out["msa"] = msa if msa_given else msa.cpu().numpy()
+                out["pair"] = pair if pair_given else pair.float().cpu().numpy()
         return out
 
+
+class Af3MsaBlockGpu:
+    """One block of the AF3 MSA stack (``msaBlock``, ``cpu/af3/trunk/msa.js:235-287``):
+    ``run(state, weights, dialect, options)`` is ``Af3MsaStackGpu.run`` over that one block."""
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+
+    def run(self, state, weights, dialect, options=None):
+        return Af3MsaStackGpu(self.device).run(state, [weights], dialect, options)

@@ -111,3 +111,31 @@ def test_distogram_logits(dev, with_bias):
     want = oracle.distogram_logits(pair, w, bias)
     assert oracle.relative_l2(got, want) <= F32_TOL
     assert np.abs(got - got.transpose(1, 0, 2)).max() == 0
+
+
+def test_msa_stack_hands_the_pair_to_the_pairformer(dev):
+    """Two MSA blocks, then one pairformer block on the same resident pair (``keepPair``), against the oracle's
+    composition of the same blocks."""
+    import localfold_b200 as lf
+    S, n = 6, 32
+    d = syn.draw(50)
+    msa, pair = d.normal(S, n, 64), d.normal(n, n, 128)
+    mm = (d.rng.random((S, n)) >= 0.2).astype(np.float32)
+    mm[0] = 1
+    pm = np.ones((n, n), np.float32)
+    blocks = [syn.af3_msa_block_weights(d) for _ in range(2)]
+    pf = syn.af3_pairformer_block_weights(d, 128, 384)
+    dialect = {"swapTransposedBias": False, "msaUpdateBeforeOuterProduct": False}
+    seen = []
+    r = lf.Af3MsaStackGpu(dev).run({"msa": msa, "pair": pair, "msaMask": mm, "pairMask": pm, "sequences": S, "tokens": n},
+                                   blocks, dialect, {"precision": "f32", "keepPair": True, "onBlock": seen.append})
+    assert seen == [0, 1] and r["pair"] is None
+    out = lf.Af3PairformerStackGpu(dev).run({"pair": r["pairTensor"], "single": None, "pairMask": pm, "tokens": n}, [pf],
+                                            {"swapTransposedBias": False}, {"precision": "f32"})
+    want_msa, want_pair = msa, pair
+    for w in blocks:
+        want_msa, want_pair = oracle.msa_block_af3(want_msa, want_pair, mm, pm, w, False, False)
+    want_pair, _ = oracle.af3_pairformer_block(want_pair, None, pm, None, pf, False)
+    got_pair = out["pair"].cpu().numpy() if hasattr(out["pair"], "cpu") else out["pair"]
+    assert oracle.relative_l2(r["msaTensor"].cpu().numpy(), want_msa) <= 2e-5
+    assert oracle.relative_l2(got_pair, want_pair) <= 2e-5
