@@ -167,7 +167,13 @@ typedef enum lf_weight_kind {
    * vProjection (cm,H*d), gatingQuery (cm,H*d), outputProjection (H*d,cm).
    * dims: channels = cm, heads, head_dim (not tied to cm / heads),
    * pair_channels = cz. */
-  LF_WEIGHTS_MSA_ATTENTION_AF3 = 9
+  LF_WEIGHTS_MSA_ATTENTION_AF3 = 9,
+  /* The extra-MSA stack's global column attention
+   * (webgpu/af2/evoformer/block.js:963-966): queryNormScale, queryNormOffset,
+   * queryWeight (c, H*d), keyWeight (c, d), valueWeight (c, d), gatingWeight
+   * (c, H*d), gatingBias (H*d), outputWeight (H*d, c), outputBias.  dims:
+   * channels, heads, head_dim = gatingBias / heads. */
+  LF_WEIGHTS_GLOBAL_ATTENTION_AF2 = 10
 } lf_weight_kind;
 
 /* Shape of the operator the weights belong to; unused fields are 0. */
@@ -354,6 +360,24 @@ typedef struct lf_msa_attention_desc {
   const lf_weights* weights;   /* MSA_ATTENTION_AF3 */
 } lf_msa_attention_desc;
 LF_API lf_status lf_msa_attention_run(lf_context* ctx, const lf_msa_attention_desc* d, lf_result* r);
+
+/* encodeGlobalAttention (webgpu/af2/evoformer/block.js:953-1032, shaders
+ * :100-482): the global column attention of the extra-MSA stack.  Per column
+ * one query - the masked mean over the sequences of the normalised MSA,
+ * projected onto the heads - against one shared key/value head per sequence
+ * (masked sequences at -1e9); the attended vector is gated per sequence and
+ * projected.  Float32 arithmetic in either precision mode; head_dim <= 32. */
+typedef struct lf_global_attention_desc {
+  int32_t sequences, length, channels, heads;
+  int32_t variance, precision, residual;
+  float epsilon;
+  int32_t space, act_dtype;
+  const void* activations;     /* msa [sequences, length, channels] */
+  const float* mask;           /* [sequences, length] float32 */
+  void* out;
+  const lf_weights* weights;   /* GLOBAL_ATTENTION_AF2 */
+} lf_global_attention_desc;
+LF_API lf_status lf_global_column_attention_run(lf_context* ctx, const lf_global_attention_desc* d, lf_result* r);
 
 /* The logits of distogramHead (cpu/af3/trunk/trunk.js:47-60): half =
  * pair.half_logits (+ bias), logits[i,j] = half[i,j] + half[j,i] - a sum, not a

@@ -6,8 +6,8 @@ eager fallback - a missing library raises on first use.
 """
 from .operators import (  # noqa: F401
     Af3GridSelfAttentionGpu, Af3MsaAttentionGpu, Af3SingleAttentionGpu, Af3TransitionGpu, AttentionGpu, Device,
-    EncodedTensor, OuterProductMeanGpu, PreparedWeights, RangeError, TransitionGpu,
+    EncodedTensor, GlobalColumnAttentionGpu, OuterProductMeanGpu, PreparedWeights, RangeError, TransitionGpu,
     TriangleMultiplicationIncomingGpu, TriangleMultiplicationOutgoingGpu,
     af3_triangle_multiplication, create_device, distogram_logits, error_metrics, int5_decode, validate_triangle_input,
 )
-from .stack import Af3MsaBlockGpu, Af3MsaStackGpu, Af3PairformerStackGpu, EvoformerBlockGpu, PairStackGpu, PreparedPairBlock  # noqa: F401
+from .stack import Af3MsaBlockGpu, Af3MsaStackGpu, Af3PairformerStackGpu, EvoformerBlockGpu, ExtraMsaBlockGpu, PairStackGpu, PreparedPairBlock  # noqa: F401

@@ -19,7 +19,7 @@ PAIR_BIAS_NONE, PAIR_BIAS_SEPARATE, PAIR_BIAS_NORMALIZED_INPUT = 0, 1, 2
 ORDER_EVOFORMER, ORDER_TEMPLATE = 0, 1
 (WEIGHTS_TRIANGLE_AF2, WEIGHTS_TRIANGLE_AF3, WEIGHTS_ATTENTION_AF2, WEIGHTS_GRID_ATTENTION_AF3,
  WEIGHTS_TRANSITION_AF2, WEIGHTS_TRANSITION_AF3, WEIGHTS_OPM_AF2, WEIGHTS_SINGLE_ATTENTION_AF3,
- WEIGHTS_MSA_ATTENTION_AF3) = range(1, 10)
+ WEIGHTS_MSA_ATTENTION_AF3, WEIGHTS_GLOBAL_ATTENTION_AF2) = range(1, 11)
 
 KERNEL_FAMILIES = ("simt", "triangle_contract", "ln_gemm", "triangle_output", "attention", "transition",
                    "elementwise")
@@ -89,6 +89,13 @@ class MsaAttentionDesc(ctypes.Structure):
                 ("pair", c_void_p), ("out", c_void_p), ("weights", c_void_p)]
 
 
+class GlobalAttentionDesc(ctypes.Structure):
+    _fields_ = [("sequences", c_int32), ("length", c_int32), ("channels", c_int32), ("heads", c_int32),
+                ("variance", c_int32), ("precision", c_int32), ("residual", c_int32), ("epsilon", c_float),
+                ("space", c_int32), ("act_dtype", c_int32), ("activations", c_void_p), ("mask", c_void_p),
+                ("out", c_void_p), ("weights", c_void_p)]
+
+
 class DistogramDesc(ctypes.Structure):
     _fields_ = [("tokens", c_int32), ("channels", c_int32), ("bins", c_int32), ("space", c_int32),
                 ("pair_dtype", c_int32), ("pair", c_void_p), ("half_logits", c_void_p), ("bias", c_void_p),
@@ -138,7 +145,7 @@ EXPORTS = (
     "lf_weights_destroy", "lf_int5_decode", "lf_triangle_multiplication_run",
     "lf_triangle_multiplication_run_static", "lf_attention_run",
     "lf_transition_run", "lf_outer_product_mean_run", "lf_single_attention_run", "lf_msa_attention_run",
-    "lf_distogram_logits_run", "lf_pair_stack_run",
+    "lf_global_column_attention_run", "lf_distogram_logits_run", "lf_pair_stack_run",
     "lf_pair_shard_step", "lf_pair_shard_exchange_step", "lf_pair_planes_scatter", "lf_peer_buffer_create", "lf_peer_buffer_open", "lf_peer_buffer_close",
     "lf_peer_buffer_destroy", "lf_pair_transpose_scatter",
 )
@@ -186,6 +193,7 @@ def load():
                        ("lf_triangle_multiplication_run_static", TriangleDesc), ("lf_attention_run", AttentionDesc),
                        ("lf_transition_run", TransitionDesc), ("lf_outer_product_mean_run", OpmDesc),
                        ("lf_single_attention_run", SingleAttentionDesc), ("lf_msa_attention_run", MsaAttentionDesc),
+                       ("lf_global_column_attention_run", GlobalAttentionDesc),
                        ("lf_distogram_logits_run", DistogramDesc), ("lf_pair_stack_run", PairStackDesc),
                        ("lf_pair_shard_step", ShardStepDesc)):
         getattr(lib, name).argtypes = [c_void_p, ctypes.POINTER(desc), ctypes.POINTER(Result)]

@@ -415,6 +415,32 @@ lf_status build_msa_attention_af3(lf_context* ctx, lf_weights* w, const float* c
   return finish_attention(ctx, w, t[0], t[1], w4, b4, t[7], nullptr, t[2], t[3], t[4], pc);
 }
 
+lf_status build_global_attention_af2(lf_context* ctx, lf_weights* w, const float* const* t, const int64_t* n, int nt) {
+  const int c = w->dims.channels, H = w->dims.heads;
+  if (H <= 0 || nt != 9 || !n || n[6] <= 0 || n[6] % H != 0) return lf_fail(ctx, LF_ERR_SHAPE, "global attention: gatingBias must hold heads x head_dim values");
+  const int HD = (int)n[6], d = HD / H;
+  w->dims.head_dim = d;
+  const Expect e[9] = {{"queryNormScale", c}, {"queryNormOffset", c}, {"queryWeight", (int64_t)c * HD}, {"keyWeight", (int64_t)c * d},
+                       {"valueWeight", (int64_t)c * d}, {"gatingWeight", (int64_t)c * HD}, {"gatingBias", HD},
+                       {"outputWeight", (int64_t)HD * c}, {"outputBias", c}};
+  LF_TRY(check_counts(ctx, e, 9, n, nt, t));
+  const int wide = 2 * d + HD;
+  hvec w3((size_t)c * wide), b3((size_t)wide, 0.f);
+  put_columns(w3, wide, 0, t[3], c, d, d, 0, 1);
+  put_columns(w3, wide, d, t[4], c, d, d, 0, 1);
+  put_columns(w3, wide, 2 * d, t[5], c, HD, HD, 0, 1);
+  memcpy(&b3[(size_t)2 * d], t[6], sizeof(float) * HD);
+  w->f.assign(GLB_COUNT, nullptr);
+  LF_TRY(upload(ctx, w, GLB_LN_G, hvec(t[0], t[0] + c)));
+  LF_TRY(upload(ctx, w, GLB_LN_B, hvec(t[1], t[1] + c)));
+  LF_TRY(upload(ctx, w, GLB_WQ, hvec(t[2], t[2] + (size_t)c * HD)));
+  LF_TRY(upload(ctx, w, GLB_W3, w3));
+  LF_TRY(upload(ctx, w, GLB_B3, b3));
+  LF_TRY(upload(ctx, w, GLB_WO, hvec(t[7], t[7] + (size_t)HD * c)));
+  LF_TRY(upload(ctx, w, GLB_BO, hvec(t[8], t[8] + c)));
+  return LF_OK;
+}
+
 lf_status build_transition(lf_context* ctx, lf_weights* w, const float* const* t, const int64_t* n, int nt, bool af3) {
   const int c = w->dims.channels, hdn = w->dims.hidden;
   if (hdn <= 0) return lf_fail(ctx, LF_ERR_ARGUMENT, "transition needs hidden channels");
@@ -473,6 +499,7 @@ static lf_status build_weights(lf_context* ctx, lf_weights* w, const float* cons
     case LF_WEIGHTS_GRID_ATTENTION_AF3: return build_grid_attention_af3(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_SINGLE_ATTENTION_AF3: return build_single_attention_af3(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_MSA_ATTENTION_AF3: return build_msa_attention_af3(ctx, w, tensors, counts, n_tensors);
+    case LF_WEIGHTS_GLOBAL_ATTENTION_AF2: return build_global_attention_af2(ctx, w, tensors, counts, n_tensors);
     case LF_WEIGHTS_TRANSITION_AF2: return build_transition(ctx, w, tensors, counts, n_tensors, false);
     case LF_WEIGHTS_TRANSITION_AF3: return build_transition(ctx, w, tensors, counts, n_tensors, true);
     case LF_WEIGHTS_OPM_AF2: return build_opm_af2(ctx, w, tensors, counts, n_tensors);
@@ -1239,6 +1266,63 @@ lf_status lf_msa_attention_run(lf_context* ctx, const lf_msa_attention_desc* d, 
     a.pair = st.in(d->pair, (size_t)n * n * d->pair_channels * dtype_size(a.pair_dtype));
     a.out = st.out(d->out, R * d->channels * 4);
     att_f32<float>(ctx, cur, a);
+    st.flush();
+    return LF_OK;
+  });
+}
+
+}  // extern "C"
+
+namespace {
+template <typename T>
+void global_attention(lf_context* ctx, ArenaCursor& cur, const lf_global_attention_desc* d, const void* act, const float* mask,
+                      void* out) {
+  const lf_weights* w = d->weights;
+  const auto& f = w->f;
+  const int S = d->sequences, n = d->length, c = d->channels, H = d->heads, hd = w->dims.head_dim, HD = H * hd, wide = 2 * hd + HD;
+  const int64_t R = (int64_t)S * n;
+  float* nrm = cur.take<float>(R * c);
+  float* kvg = cur.take<float>(R * wide);
+  float* q = cur.take<float>((int64_t)n * HD);
+  float* attended = cur.take<float>((int64_t)n * HD);
+  float* gated = cur.take<float>(R * HD);
+  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(R, 8), 256, 0, (const T*)act, R, c, f[GLB_LN_G], f[GLB_LN_B],
+         d->epsilon, d->variance, 0, 1, 1, nrm);
+  sgemm(ctx, cur, false, false, simt::EPI_SIGMOID_FROM_COL, (int)R, wide, c, nrm, c, 0, f[GLB_W3], wide, 0, kvg, wide, 0, f[GLB_B3],
+        2 * hd, 1);
+  LAUNCH(ctx, cur, simt::global_query_kernel, n, 128, (size_t)c * sizeof(float), nrm, mask, S, n, c, HD, 1.0f / sqrtf((float)hd),
+         f[GLB_WQ], q);
+  LAUNCH(ctx, cur, simt::global_attend_kernel, dim3(n, H), 64, 0, q, kvg, wide, mask, S, n, H, hd, attended);
+  LAUNCH(ctx, cur, simt::global_gate_kernel, lf_ceil_div(R * HD, 256), 256, 0, kvg, wide, 2 * hd, attended, R, n, HD, gated);
+  float* proj = nrm;   // the normalised input is dead
+  sgemm(ctx, cur, false, false, 0, (int)R, c, HD, gated, HD, 0, f[GLB_WO], c, 0, proj, c, 0, f[GLB_BO], 0, 1);
+  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
+         d->residual ? (const T*)act : (const T*)nullptr, R, c, 0, 1, 1, (T*)out);
+}
+}  // namespace
+
+extern "C" {
+
+lf_status lf_global_column_attention_run(lf_context* ctx, const lf_global_attention_desc* d, lf_result* r) {
+  if (!ctx) return LF_ERR_ARGUMENT;
+  if (!d || !d->activations || !d->mask || !d->out || !d->weights) return lf_fail(ctx, LF_ERR_ARGUMENT, "global attention: null argument");
+  if (d->sequences <= 0 || d->length <= 0 || d->channels <= 0 || d->heads <= 0)
+    return lf_fail(ctx, LF_ERR_SHAPE, "global attention dimensions must be positive safe integers");
+  LF_TRY(check_common(ctx, d->variance, d->precision, d->space, d->act_dtype, d->epsilon));
+  const lf_weights* w = d->weights;
+  if (w->kind != LF_WEIGHTS_GLOBAL_ATTENTION_AF2) return lf_fail(ctx, LF_ERR_ARGUMENT, "weights are not global attention weights");
+  if (w->dims.channels != d->channels || w->dims.heads != d->heads)
+    return lf_fail(ctx, LF_ERR_SHAPE, "weights were packed for %d channels, %d heads; the call has %d, %d", w->dims.channels, w->dims.heads, d->channels, d->heads);
+  if (w->dims.head_dim > 32) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "global attention head dimension %d exceeds 32", w->dims.head_dim);
+  const bool host = d->space == LF_SPACE_HOST;
+  const size_t R = (size_t)d->sequences * d->length, es = dtype_size(d->act_dtype);
+  return run_with_arena(ctx, r, host, [&](ArenaCursor& cur) -> lf_status {
+    Staging st{ctx, &cur, host};
+    const void* act = st.in(d->activations, R * d->channels * es);
+    const float* mask = (const float*)st.in(d->mask, R * sizeof(float));
+    void* out = st.out(d->out, R * d->channels * es);
+    if (d->act_dtype == LF_DTYPE_BF16) global_attention<bf16>(ctx, cur, d, act, mask, out);
+    else global_attention<float>(ctx, cur, d, act, mask, out);
     st.flush();
     return LF_OK;
   });

@@ -61,6 +61,8 @@ enum { TRI_LN_G, TRI_LN_B, TRI_W4, TRI_B4, TRI_LNO_G, TRI_LNO_B, TRI_WZ, TRI_BZ,
 enum { ATT_LN_G, ATT_LN_B, ATT_W4, ATT_B4, ATT_WO, ATT_BO, ATT_PLN_G, ATT_PLN_B, ATT_WB, ATT_COUNT };
 enum { TRN_LN_G, TRN_LN_B, TRN_W1, TRN_B1, TRN_W2, TRN_B2, TRN_COUNT };
 enum { OPM_LN_G, OPM_LN_B, OPM_WL, OPM_BL, OPM_WR, OPM_BR, OPM_WOUT, OPM_BOUT, OPM_COUNT };
+// global column attention: W3 = (key | value | gate) columns, B3 their biases (zero but for the gate)
+enum { GLB_LN_G, GLB_LN_B, GLB_WQ, GLB_W3, GLB_B3, GLB_WO, GLB_BO, GLB_COUNT };
 
 // Canonical device-resident weights.  Every linear is stored (in,out) row-major
 // float32 in `f[...]`; tensor-core kernels keep extra fp16 repacks (swizzled operand images) in `h[...]`.

@@ -294,6 +294,83 @@ __global__ void pair_bias_kernel(const TIn* __restrict__ pair, int Q, int ch, in
   }
 }
 
+// Global column attention (extra-MSA stack).  Query of a column: the masked mean over the sequences of the
+// normalised rows, projected onto heads x d and scaled.  One block per column; shared memory: c floats.
+__global__ void global_query_kernel(const float* __restrict__ nrm, const float* __restrict__ mask, int S, int n, int c,
+                                    int HD, float scale, const float* __restrict__ wq, float* __restrict__ q) {
+  extern __shared__ float means[];
+  __shared__ float red[32];
+  const int col = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  float count = 0.f;
+  for (int s = tid; s < S; s += blockDim.x) count += mask[(int64_t)s * n + col];
+  count = warp_sum(count);
+  if (lane == 0) red[wid] = count;
+  __syncthreads();
+  float total_count = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total_count += red[w];
+  const float denominator = 1e-10f + total_count;
+  for (int ch = tid; ch < c; ch += blockDim.x) {
+    float total = 0.f;
+    for (int s = 0; s < S; ++s) total = fmaf(nrm[((int64_t)s * n + col) * c + ch], mask[(int64_t)s * n + col], total);
+    means[ch] = total / denominator;
+  }
+  __syncthreads();
+  for (int slot = tid; slot < HD; slot += blockDim.x) {
+    float r = 0.f;
+    for (int ch = 0; ch < c; ++ch) r = fmaf(means[ch], wq[(int64_t)ch * HD + slot], r);
+    q[(int64_t)col * HD + slot] = r * scale;
+  }
+}
+
+// Softmax over the sequences of q(column, head) . k(sequence, column) with masked sequences at -1e9, applied to
+// the values: one block of 64 threads per (column, head), each thread an online softmax over its sequences,
+// combined through shared memory.  k at columns 0..d-1 and v at d..2d-1 of rows of `ld` floats; d <= 32.
+__global__ void global_attend_kernel(const float* __restrict__ q, const float* __restrict__ kv, int ld,
+                                     const float* __restrict__ mask, int S, int n, int heads, int d,
+                                     float* __restrict__ attended) {
+  __shared__ float part_max[64], part_den[64], part_acc[64 * 32];
+  const int col = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  float qv[32], acc[32];
+  for (int e = 0; e < d; ++e) { qv[e] = q[((int64_t)col * heads + h) * d + e]; acc[e] = 0.f; }
+  float maximum = -1e30f, den = 0.f;
+  for (int s = tid; s < S; s += 64) {
+    const float* row = kv + ((int64_t)s * n + col) * ld;
+    float logit = 0.f;
+    for (int e = 0; e < d; ++e) logit = fmaf(qv[e], row[e], logit);
+    if (mask[(int64_t)s * n + col] == 0.f) logit = -1e9f;
+    const float next = fmaxf(maximum, logit);
+    const float prev_scale = __expf(maximum - next), weight = __expf(logit - next);
+    den = den * prev_scale + weight;
+    for (int e = 0; e < d; ++e) acc[e] = acc[e] * prev_scale + weight * row[d + e];
+    maximum = next;
+  }
+  part_max[tid] = maximum;
+  part_den[tid] = den;
+  for (int e = 0; e < d; ++e) part_acc[tid * 32 + e] = acc[e];
+  __syncthreads();
+  if (tid < d) {
+    float top = -1e30f;
+    for (int t = 0; t < 64; ++t) top = fmaxf(top, part_max[t]);
+    float dsum = 0.f, num = 0.f;
+    for (int t = 0; t < 64; ++t) {
+      const float w = __expf(part_max[t] - top);
+      dsum += part_den[t] * w;
+      num += part_acc[t * 32 + tid] * w;
+    }
+    attended[((int64_t)col * heads + h) * d + tid] = num / dsum;
+  }
+}
+
+// gated[r][slot] = sigmoid-gate[r][slot] (columns gate0.. of rows of `ld`) * attended[column of r][slot]
+__global__ void global_gate_kernel(const float* __restrict__ kvg, int ld, int gate0, const float* __restrict__ attended,
+                                   int64_t rows, int n, int HD, float* __restrict__ gated) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * HD) return;
+  const int64_t r = idx / HD;
+  const int slot = (int)(idx % HD);
+  gated[idx] = kvg[r * ld + gate0 + slot] * attended[(r % n) * HD + slot];
+}
+
 // One key mask for every sequence of an MSA: out[s][t] = max over s' of mask[s'][t] (AF3 pair-weighted
 // averaging: a token any sequence covers is a key for all of them).
 __global__ void msa_key_mask_kernel(const float* __restrict__ mask, int sequences, int tokens, float* __restrict__ out) {

@@ -699,6 +699,51 @@ class Af3SingleAttentionGpu:
                 owned.close()
 
 
+GLOBAL_ATTENTION_ORDER = ("queryNormScale", "queryNormOffset", "queryWeight", "keyWeight", "valueWeight",
+                          "gatingWeight", "gatingBias", "outputWeight", "outputBias")
+
+
+class GlobalColumnAttentionGpu:
+    """The extra-MSA stack's global column attention (``encodeGlobalAttention``,
+    ``webgpu/af2/evoformer/block.js:953-1032``): ``run({activations, mask, sequences, length, channels, weights})``
+    with ``weights`` the nine tensors of ``GLOBAL_ATTENTION_ORDER`` plus ``heads``; float32 arithmetic."""
+
+    def __init__(self, device: Device | None = None):
+        self.device = _device(device)
+
+    def run(self, input, options=None, out=None):
+        S, n, c = (int(input[k]) for k in ("sequences", "length", "channels"))
+        for name, v in (("sequences", S), ("length", n), ("channels", c)):
+            _positive(name, v)
+        dev = self.device
+        w = input["weights"]
+        owned = None
+        act = _Buffer(input["activations"])
+        mask = _Buffer(input["mask"])
+        _expect_length("activations", act, S * n * c)
+        _expect_length("mask", mask, S * n)
+        if not isinstance(w, PreparedWeights):
+            heads = w.get("heads")
+            if not isinstance(heads, (int, np.integer)) or heads <= 0:
+                raise RangeError("global attention weights.heads must be a positive integer")
+            owned = w = PreparedWeights(dev, nat.WEIGHTS_GLOBAL_ATTENTION_AF2, {"channels": c, "heads": int(heads)},
+                                        [w[k] for k in GLOBAL_ATTENTION_ORDER])
+        try:
+            opts = options or {}
+            obuf, output = _out_like(act, (S, n, c), out)
+            desc = nat.GlobalAttentionDesc(S, n, c, w.dims["heads"], _variance(opts, "two-pass"), _precision(opts),
+                                           1 if opts.get("residual") else 0, float(input.get("epsilon") or 1e-5),
+                                           nat.SPACE_DEVICE if act.is_device else nat.SPACE_HOST, act.dtype,
+                                           act.ptr, mask.ptr, obuf.ptr, w.handle)
+            res = nat.Result()
+            dev.check(dev.lib.lf_global_column_attention_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
+            return _result(dev, res, output)
+        finally:
+            if owned is not None:
+                dev.synchronize()
+                owned.close()
+
+
 MSA_ATTENTION_AF3_ORDER = ("actNormScale", "actNormOffset", "pairNormScale", "pairNormOffset", "pairLogits",
                            "vProjection", "gatingQuery", "outputProjection")
 

@@ -178,6 +178,56 @@ class EvoformerBlockGpu:
                 "launches": launches}
 
 
+class ExtraMsaBlockGpu:
+    """One block of the AF2 extra-MSA stack (``encodeExtraMsaBlock``, ``webgpu/af2/evoformer/block.js:1715-1744``):
+    msa += rowAttention(msa, pair); msa += globalColumnAttention(msa); msa += transition(msa); then the
+    Evoformer pair part (pair += outerProductMean(msa) and the five pair updates).  Same input as
+    ``EvoformerBlockGpu`` with ``weights["msaColumnGlobalAttention"]`` in place of the column attention."""
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+
+    def run(self, input, options=None):
+        from .operators import GlobalColumnAttentionGpu
+        opts = dict(options or {})
+        dev = self.device
+        S, n, cm, cz = (int(input[k]) for k in ("sequences", "length", "cM", "cZ"))
+        co, ch = int(input["cOuter"]), int(input["triangleHidden"])
+        w = input["weights"]
+        msa = np.array(input["msa"], np.float32, copy=True).reshape(S, n, cm)
+        pair = np.array(input["pair"], np.float32, copy=True).reshape(n, n, cz)
+        msa_mask, pair_mask = input["msaMask"], input["pairMask"]
+        elapsed = 0.0
+        launches = 0
+        row = w["msaRowAttention"]
+        sub = dict(opts, residual=True)
+        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": S, "queryLength": n,
+                                   "channels": cm, "heads": row["heads"], "weights": row["attention"],
+                                   "pairBias": dict(row["pairBias"], source="separate", activations=pair,
+                                                    channels=cz)}, sub)
+        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        r = GlobalColumnAttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
+                                               "channels": cm, "weights": w["msaColumnGlobalAttention"]}, sub)
+        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        t = w["msaTransition"]
+        r = TransitionGpu(dev).run({"activations": msa, "rows": S * n, "channels": cm,
+                                    "hiddenChannels": np.asarray(t["firstBias"]).size, "weights": t}, sub)
+        msa = r["output"].reshape(S, n, cm); elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        r = OuterProductMeanGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
+                                          "cM": cm, "cOuter": co, "cZ": cz, "weights": w["outerProductMean"]},
+                                         sub, out=pair)
+        pair = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        stack = PairStackGpu(dev).prepare([w], cz, ch)
+        try:
+            r = stack.run(pair, pair_mask, opts)
+        finally:
+            dev.synchronize()
+            stack.close()
+        elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        return {"msa": msa, "pair": r["pair"], "elapsedMilliseconds": elapsed, "memory": r["memory"],
+                "launches": launches}
+
+
 class Af3PairformerStackGpu:
     """``Af3PairformerStackGpu.run(state, blocks, dialect, options)``
     (``webgpu/af3/trunk/pairformer-block.js:290-343``): per block the five pair

@@ -127,6 +127,33 @@ def af2_evoformer_block(seed, S=128, n=256, cm=256, cz=128, c_outer=32, c=128, m
     return msa, pair, msa_mask, pair_mask, w
 
 
+def af2_global_attention_weights(d: _Draw, c, heads, dim):
+    """The extra-MSA stack's global column attention (``webgpu/af2/evoformer/block.js:963-966``): one shared
+    key/value head of ``dim`` channels, ``heads`` query and gate heads."""
+    hd = heads * dim
+    return {"heads": heads, "queryNormScale": 1 + d.normal(c, std=0.1), "queryNormOffset": d.normal(c, std=0.1),
+            "queryWeight": d.linear(c, c, hd), "keyWeight": d.linear(c, c, dim), "valueWeight": d.linear(c, c, dim),
+            "gatingWeight": d.linear(c, c, hd), "gatingBias": ones(hd), "outputWeight": d.linear(hd, hd, c),
+            "outputBias": d.normal(c, std=0.1)}
+
+
+def af2_extra_msa_block(seed, S=64, n=48, ce=64, cz=128, c_outer=32, c=128, msa_heads=8, pair_heads=4, gaps=0.15):
+    """One block of the extra-MSA stack at its own widths (64 MSA channels, 8 heads of 8): a random ``gaps``
+    fraction of the alignment masked (the first row whole), pair mask ones."""
+    d = _Draw(seed)
+    msa = d.normal(S, n, ce)
+    pair = d.normal(n, n, cz)
+    msa_mask = (d.rng.random((S, n)) >= gaps).astype(np.float32)
+    msa_mask[0] = 1
+    pair_mask = np.ones((n, n), np.float32)
+    w = {"msaRowAttention": af2_attention_weights(d, ce, msa_heads, cz, separate=True),
+         "msaColumnGlobalAttention": af2_global_attention_weights(d, ce, msa_heads, ce // msa_heads),
+         "msaTransition": af2_transition_weights(d, ce),
+         "outerProductMean": af2_opm_weights(d, ce, c_outer, cz)}
+    w.update(af2_pair_block_weights(d, cz, c, pair_heads))
+    return msa, pair, msa_mask, pair_mask, w
+
+
 # ---- AF3 dialect -----------------------------------------------------------
 
 

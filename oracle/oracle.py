@@ -361,6 +361,44 @@ def af3_pairformer_block(pair, single, pair_mask, seq_mask, w, swap_transposed_b
     return pair, single
 
 
+GLOBAL_ATTENTION_ORDER = ("queryNormScale", "queryNormOffset", "queryWeight", "keyWeight", "valueWeight",
+                          "gatingWeight", "gatingBias", "outputWeight", "outputBias")
+
+
+def global_column_attention_af2(msa, mask, weights, eps=1e-5):
+    """The extra-MSA stack's global column attention (``webgpu/af2/evoformer/block.js:100-482,953-1032``);
+    ``weights["heads"]`` heads of ``gatingBias.size / heads`` channels, one shared key/value head."""
+    a, pa = _f(msa)
+    S, n, c = a.shape
+    m, pm = _f(mask)
+    heads = int(weights["heads"])
+    dim = int(np.asarray(weights["gatingBias"]).size // heads)
+    keep = [_f(weights[k]) for k in GLOBAL_ATTENTION_ORDER]
+    out = np.empty((S, n, c), np.float32)
+    lib().orc_global_column_attention_af2(pa, pm, _i(S), _i(n), _i(c), _i(heads), _i(dim), *[k[1] for k in keep],
+                                          _d(eps), out.ctypes.data_as(_FP))
+    return out
+
+
+def af2_extra_msa_block(msa, pair, msa_mask, pair_mask, w, c_outer, c_hidden, eps=1e-5):
+    """One block of the extra-MSA stack (``encodeExtraMsaBlock``, ``webgpu/af2/evoformer/block.js:1715-1744``):
+    row attention with pair bias, global column attention, MSA transition, then the Evoformer pair part
+    (outer product mean and the five pair updates)."""
+    msa = np.array(msa, np.float32, copy=True)
+    pair = np.array(pair, np.float32, copy=True)
+    S, n, cm = msa.shape
+    cz = pair.shape[-1]
+    row = w["msaRowAttention"]
+    pb = dict(row["pairBias"], source="separate", activations=pair, channels=cz)
+    msa = msa + attention_af2(msa, msa_mask, S, n, cm, row["heads"], row["attention"], False, pb, eps)
+    msa = msa + global_column_attention_af2(msa, msa_mask, w["msaColumnGlobalAttention"], eps)
+    t = w["msaTransition"]
+    msa = msa + transition_af2(msa, t, t["firstBias"].shape[0], eps)
+    pair = pair + outer_product_mean_af2(msa, msa_mask, w["outerProductMean"], c_outer, cz, eps)
+    pair = af2_pair_block(pair, pair_mask, w, c_hidden, eps)
+    return msa, pair
+
+
 def msa_attention_af3(msa, msa_mask, pair, weights):
     """``msaAttention`` (``cpu/af3/trunk/msa.js:164-224``): MSA pair-weighted averaging."""
     a, pa = _f(msa)

@@ -738,6 +738,77 @@ ORC_API void orc_distogram_logits(const float* pair, int tokens, int cz, int bin
 }
 
 /* ------------------------------------------------------------------------- */
+/* AF2 global column attention of the extra-MSA stack, as the reference's shaders define it
+ * (webgpu/af2/evoformer/block.js:100-482, encodeGlobalAttention :953-1032): per column, one query - the
+ * masked mean over the sequences of the two-pass-normalised MSA, projected onto the heads and scaled by
+ * head_dim^-1/2 - against one shared key/value head per sequence; masked sequences get the logit -1e9;
+ * the attended vector of the column is gated per sequence by sigmoid(x.Wg + bg) and projected.  Weights
+ * (in,out); float32 is stored where the shaders store it (normalised MSA, means, query, keys, values,
+ * attended, gated).                                                                                       */
+ORC_API void orc_global_column_attention_af2(const float* msa, const float* mask, int S, int n, int c, int heads,
+                                             int dim, const float* norm_scale, const float* norm_offset,
+                                             const float* wq, const float* wk, const float* wv,
+                                             const float* wgate, const float* bgate, const float* wo,
+                                             const float* bo, double eps, float* out) {
+  const int gates = heads * dim;
+  const int64_t rows = (int64_t)S * n;
+  float* nrm = (float*)malloc((size_t)rows * c * 4);
+  orc_layer_norm(msa, rows, c, norm_scale, norm_offset, eps, 0, nrm);
+  float* keys = (float*)malloc((size_t)rows * dim * 4);
+  float* values = (float*)malloc((size_t)rows * dim * 4);
+  orc_linear(nrm, rows, c, dim, wk, NULL, 0, keys);
+  orc_linear(nrm, rows, c, dim, wv, NULL, 0, values);
+  float* attended = (float*)malloc((size_t)n * gates * 4);
+  const double scale = 1.0 / sqrt((double)dim);
+#pragma omp parallel
+  {
+    float* means = (float*)malloc((size_t)c * 4);
+    float* query = (float*)malloc((size_t)gates * 4);
+    float* logits = (float*)malloc((size_t)S * 4);
+#pragma omp for schedule(static)
+    for (int col = 0; col < n; ++col) {
+      double count = 0;
+      for (int s = 0; s < S; ++s) count += (double)mask[(size_t)s * n + col];
+      const double denominator = 1e-10 + count;
+      for (int ch = 0; ch < c; ++ch) {
+        double total = 0;
+        for (int s = 0; s < S; ++s) total += (double)nrm[((size_t)s * n + col) * c + ch] * (double)mask[(size_t)s * n + col];
+        means[ch] = (float)(total / denominator);
+      }
+      for (int slot = 0; slot < gates; ++slot) {
+        double r = 0;
+        for (int ch = 0; ch < c; ++ch) r += (double)means[ch] * (double)wq[(size_t)ch * gates + slot];
+        query[slot] = (float)(r * scale);
+      }
+      for (int h = 0; h < heads; ++h) {
+        for (int s = 0; s < S; ++s) {
+          double l = 0;
+          for (int d = 0; d < dim; ++d) l += (double)query[h * dim + d] * (double)keys[((size_t)s * n + col) * dim + d];
+          logits[s] = mask[(size_t)s * n + col] == 0.0f ? -1e9f : (float)l;
+        }
+        softmax_row_f32(logits, S);
+        for (int d = 0; d < dim; ++d) {
+          double t = 0;
+          for (int s = 0; s < S; ++s) t += (double)logits[s] * (double)values[((size_t)s * n + col) * dim + d];
+          attended[(size_t)col * gates + h * dim + d] = (float)t;
+        }
+      }
+    }
+    free(logits); free(query); free(means);
+  }
+  float* gate = (float*)malloc((size_t)rows * gates * 4);
+  orc_linear(nrm, rows, c, gates, wgate, bgate, 0, gate);
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const int col = (int)(r % n);
+    for (int slot = 0; slot < gates; ++slot)
+      gate[r * gates + slot] = (float)((double)attended[(size_t)col * gates + slot] * sigmoid_d(gate[r * gates + slot]));
+  }
+  orc_linear(gate, rows, gates, c, wo, bo, 0, out);
+  free(gate); free(attended); free(values); free(keys); free(nrm);
+}
+
+/* ------------------------------------------------------------------------- */
 /* int5 tensor decode: groups of `block` codes, 5 bits each, least significant
  * bit first in a little-endian bit stream (block*5/8 bytes per group), one
  * fp16 scale and one fp16 zero point per group; value = code*scale + zero in

@@ -139,3 +139,52 @@ def test_msa_stack_hands_the_pair_to_the_pairformer(dev):
     got_pair = out["pair"].cpu().numpy() if hasattr(out["pair"], "cpu") else out["pair"]
     assert oracle.relative_l2(r["msaTensor"].cpu().numpy(), want_msa) <= 2e-5
     assert oracle.relative_l2(got_pair, want_pair) <= 2e-5
+
+
+@pytest.mark.parametrize("S,n,c,heads,dim", [(64, 48, 64, 8, 8), (5, 33, 64, 8, 8), (300, 17, 32, 4, 16), (1, 8, 64, 8, 8)])
+def test_global_column_attention_f32(dev, S, n, c, heads, dim):
+    import localfold_b200 as lf
+    from parity_report import record
+    d = syn.draw(60 + S)
+    msa = d.normal(S, n, c)
+    mask = (d.rng.random((S, n)) >= 0.2).astype(np.float32)
+    mask[0] = 1
+    w = syn.af2_global_attention_weights(d, c, heads, dim)
+    got = lf.GlobalColumnAttentionGpu(dev).run({"activations": msa, "mask": mask, "sequences": S, "length": n, "channels": c,
+                                                "weights": w}, {"precision": "f32", "variance": "two-pass"})["output"]
+    want = oracle.global_column_attention_af2(msa, mask, w)
+    err = oracle.relative_l2(got, want)
+    record("global_column_attention", f"S={S} n={n} c={c} heads={heads}x{dim}", err, F32_TOL)
+    assert np.isfinite(got).all()
+    assert err <= F32_TOL
+
+
+def test_global_column_attention_column_with_no_sequence(dev):
+    """A column no sequence covers: every logit is -1e9, the softmax is uniform, the query is 0 / 1e-10 = 0."""
+    import localfold_b200 as lf
+    d = syn.draw(70)
+    S, n, c = 6, 12, 64
+    msa = d.normal(S, n, c)
+    mask = np.ones((S, n), np.float32)
+    mask[:, 5] = 0
+    w = syn.af2_global_attention_weights(d, c, 8, 8)
+    got = lf.GlobalColumnAttentionGpu(dev).run({"activations": msa, "mask": mask, "sequences": S, "length": n, "channels": c,
+                                                "weights": w}, {"precision": "f32", "variance": "two-pass"})["output"]
+    want = oracle.global_column_attention_af2(msa, mask, w)
+    assert np.isfinite(got).all()
+    assert oracle.relative_l2(got, want) <= F32_TOL
+
+
+def test_extra_msa_block_f32(dev):
+    import localfold_b200 as lf
+    from parity_report import record
+    S, n = 24, 40
+    msa, pair, mm, pm, w = syn.af2_extra_msa_block(80, S=S, n=n)
+    got = lf.ExtraMsaBlockGpu(dev).run({"msa": msa, "pair": pair, "msaMask": mm, "pairMask": pm, "sequences": S, "length": n,
+                                        "cM": 64, "cZ": 128, "cOuter": 32, "triangleHidden": 128, "weights": w},
+                                       {"precision": "f32", "variance": "two-pass"})
+    want_msa, want_pair = oracle.af2_extra_msa_block(msa, pair, mm, pm, w, 32, 128)
+    e_msa, e_pair = oracle.relative_l2(got["msa"], want_msa), oracle.relative_l2(got["pair"], want_pair)
+    record("extra_msa_block", f"S={S} n={n} f32 msa", e_msa, F32_TOL)
+    record("extra_msa_block", f"S={S} n={n} f32 pair", e_pair, F32_TOL)
+    assert e_msa <= F32_TOL and e_pair <= F32_TOL

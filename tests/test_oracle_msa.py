@@ -102,3 +102,32 @@ def test_distogram_logits_are_a_sum_with_the_transpose():
     half = pair.astype(np.float64) @ w + bias
     assert np.abs(got - (half + half.transpose(1, 0, 2))).max() < 1e-5
     assert np.abs(got - got.transpose(1, 0, 2)).max() == 0
+
+
+def test_global_column_attention_against_float64():
+    """The extra-MSA global column attention (defined by the reference's shaders only) against an independent
+    float64 formulation of the same sums."""
+    d = syn.draw(21)
+    S, n, c, H, D = 9, 11, 32, 4, 8
+    msa = d.normal(S, n, c)
+    mask = (d.rng.random((S, n)) >= 0.3).astype(np.float32)
+    mask[0] = 1
+    w = syn.af2_global_attention_weights(d, c, H, D)
+    got = oracle.global_column_attention_af2(msa, mask, w)
+    x = msa.astype(np.float64)
+    m = x.mean(-1, keepdims=True)
+    v = ((x - m) ** 2).mean(-1, keepdims=True)
+    nx = (x - m) / np.sqrt(v + 1e-5) * w["queryNormScale"] + w["queryNormOffset"]
+    mk = mask.astype(np.float64)
+    q_avg = (nx * mk[..., None]).sum(0) / (1e-10 + mk.sum(0))[:, None]
+    q = (q_avg @ w["queryWeight"].astype(np.float64)).reshape(n, H, D) * D ** -0.5
+    k = nx @ w["keyWeight"].astype(np.float64)
+    val = nx @ w["valueWeight"].astype(np.float64)
+    logits = np.where(mk.T[:, None, :] == 0, -1e9, np.einsum("nhd,snd->nhs", q, k))
+    logits -= logits.max(-1, keepdims=True)
+    p = np.exp(logits)
+    p /= p.sum(-1, keepdims=True)
+    att = np.einsum("nhs,snd->nhd", p, val).reshape(n, H * D)
+    gate = 1 / (1 + np.exp(-(nx @ w["gatingWeight"].astype(np.float64) + w["gatingBias"])))
+    want = (gate * att[None]) @ w["outputWeight"].astype(np.float64) + w["outputBias"]
+    assert oracle.relative_l2(got, want) <= 1e-6
