@@ -450,6 +450,25 @@ def main():
         extra["n384_ms_per_block"] = float(np.mean(times))
         extra["n384_note"] = "AF2 pair block at N=384 on one GPU, mean of 10 blocks, 256 MiB written between blocks to flush L2"
         extra["n384_tflops_block"] = block_flops(384) / (extra["n384_ms_per_block"] * 1e-3) / 1e12
+        # the same length in the AF3 dialect (the five pair updates of a pairformer block: fast-variance LayerNorm,
+        # SwiGLU transition, no biases), the shape of the 48-block pairformer stack
+        d3 = syn.draw(2)
+        af3_blocks = [syn.af3_pairformer_block_weights(d3, C_Z, 384, 4, 16) for _ in range(2)]
+        stack3 = lf.PairStackGpu(dev).prepare(af3_blocks, C_Z, C_Z)
+        opts3 = dict(opts, variance="fast")
+        times = []
+        for i in range(3 + 10):
+            flush.fill_(i & 0xff)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            stack3.run(z384, k384, opts3, first_block=i % 2, n_blocks=1, dialect={"swapTransposedBias": False})
+            b.record(stream)
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        stack3.close()
+        extra["n384_af3_ms_per_block"] = float(np.mean(times))
+        extra["n384_af3_note"] = "pair part of an AF3 pairformer block at N=384 (the 48-block stack's shape), timed like n384_ms_per_block"
         del z384, flush
 
     # end to end through the public API with host buffers: pinned host pair in, pair out, every step

@@ -178,6 +178,34 @@ class EvoformerBlockGpu:
                 "launches": launches}
 
 
+class EvoformerStackGpu:
+    """``EvoformerStackGpu.run(input)`` (``webgpu/af2/evoformer/stack.js:44-110``): the blocks of the main stack
+    one after the other, ``input["blockWeights"]`` one weight object per block; the MSA and the pair of a block
+    are the next block's input.  ``ExtraMsaStackGpu`` is the same loop over extra-MSA blocks."""
+
+    block_class = None      # set below: the block runner of this stack
+
+    def __init__(self, device=None):
+        self.device = _device(device)
+
+    def run(self, input, options=None):
+        blocks = input["blockWeights"]
+        if len(blocks) == 0:
+            raise nat.RangeError("Evoformer stack requires at least one block")
+        runner = self.block_class(self.device)
+        state = dict(input)
+        total = {"elapsedMilliseconds": 0.0, "launches": 0, "memory": {"peakBytes": 0}}
+        for index, w in enumerate(blocks):
+            r = runner.run(dict(state, weights=w), options)
+            state["msa"], state["pair"] = r["msa"], r["pair"]
+            total["elapsedMilliseconds"] += r["elapsedMilliseconds"]
+            total["launches"] += r["launches"]
+            total["memory"]["peakBytes"] = max(total["memory"]["peakBytes"], r["memory"]["peakBytes"])
+            if input.get("onBlockDone"):
+                input["onBlockDone"](index)
+        return dict(total, msa=state["msa"], pair=state["pair"])
+
+
 class ExtraMsaBlockGpu:
     """One block of the AF2 extra-MSA stack (``encodeExtraMsaBlock``, ``webgpu/af2/evoformer/block.js:1715-1744``):
     msa += rowAttention(msa, pair); msa += globalColumnAttention(msa); msa += transition(msa); then the
@@ -226,6 +254,14 @@ class ExtraMsaBlockGpu:
         elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
         return {"msa": msa, "pair": r["pair"], "elapsedMilliseconds": elapsed, "memory": r["memory"],
                 "launches": launches}
+
+
+class ExtraMsaStackGpu(EvoformerStackGpu):
+    """The extra-MSA stack (``encodeExtraMsaBlock`` per block, ``webgpu/af2/evoformer/stack.js:163``)."""
+    block_class = ExtraMsaBlockGpu
+
+
+EvoformerStackGpu.block_class = EvoformerBlockGpu
 
 
 class Af3PairformerStackGpu:

@@ -188,3 +188,21 @@ def test_extra_msa_block_f32(dev):
     record("extra_msa_block", f"S={S} n={n} f32 msa", e_msa, F32_TOL)
     record("extra_msa_block", f"S={S} n={n} f32 pair", e_pair, F32_TOL)
     assert e_msa <= F32_TOL and e_pair <= F32_TOL
+
+
+def test_extra_msa_stack_two_blocks(dev):
+    import localfold_b200 as lf
+    S, n = 10, 24
+    d = syn.draw(90)
+    msa, pair, mm, pm, w0 = syn.af2_extra_msa_block(90, S=S, n=n)
+    _, _, _, _, w1 = syn.af2_extra_msa_block(91, S=S, n=n)
+    seen = []
+    got = lf.ExtraMsaStackGpu(dev).run({"msa": msa, "pair": pair, "msaMask": mm, "pairMask": pm, "sequences": S, "length": n,
+                                        "cM": 64, "cZ": 128, "cOuter": 32, "triangleHidden": 128, "blockWeights": [w0, w1],
+                                        "onBlockDone": seen.append}, {"precision": "f32", "variance": "two-pass"})
+    want_msa, want_pair = msa, pair
+    for w in (w0, w1):
+        want_msa, want_pair = oracle.af2_extra_msa_block(want_msa, want_pair, mm, pm, w, 32, 128)
+    assert seen == [0, 1]
+    assert oracle.relative_l2(got["msa"], want_msa) <= 3 * F32_TOL
+    assert oracle.relative_l2(got["pair"], want_pair) <= 3 * F32_TOL
