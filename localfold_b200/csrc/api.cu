@@ -890,6 +890,7 @@ struct AttArgs {
   int bias_swap;       // store the bias transposed
   int pair_ch, pair_dtype, pair_variance;
   int mask_mode, clamp;
+  int tc_pair_bias;    // 16-bit mode: a separate pair bias is projected on the tensor cores when its weights allow
   float eps, pair_eps;
   int act_dtype;
   const void* act; const float* mask; const void* pair; void* out;
@@ -910,7 +911,13 @@ void att_f32(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   sgemm(ctx, cur, false, false, simt::EPI_SIGMOID_FROM_COL, (int)R, 4 * HD, c, nrm, c, 0, f[ATT_W4], 4 * HD, 0, qkvg,
         4 * HD, 0, f[ATT_B4], 3 * HD, 1);
   const int64_t QQ = (int64_t)a.Q * a.Q;
-  if (a.bias_mode == 1) {
+  if (a.bias_mode == 1 && a.tc_pair_bias && tc::pair_bias_supported(a.w) && !a.bias_swap) {
+    // the pair-sized pass of this operator: LayerNorm of the pair and its projection onto the heads, fp16 out
+    const int ldb = (a.Q + 15) / 16 * 16;
+    op16* b16 = cur.take<op16>((int64_t)a.heads * a.Q * ldb);
+    (void)tc::pair_bias_project(ctx, cur, a.pair, a.pair_dtype, a.Q, a.pair_variance, a.pair_eps, a.heads, a.w, b16, ldb);
+    LAUNCH(ctx, cur, simt::widen_bias_kernel, lf_ceil_div(QQ * a.heads, 256), 256, 0, b16, a.heads, a.Q, ldb, bias);
+  } else if (a.bias_mode == 1) {
     if (a.pair_dtype == LF_DTYPE_BF16)
       LAUNCH(ctx, cur, (simt::pair_bias_kernel<bf16>), lf_ceil_div(QQ, 8), 256, 0, (const bf16*)a.pair, a.Q, a.pair_ch,
              a.heads, f[ATT_PLN_G], f[ATT_PLN_B], f[ATT_WB], a.pair_eps, a.pair_variance, 0, a.bias_swap, bias);
@@ -961,7 +968,9 @@ lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int 
   if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && a.heads == 4 && a.d == 32 && tc::ln_gemm_supported(a.w)) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
   }
-  if (a.act_dtype == LF_DTYPE_BF16) att_f32<bf16>(ctx, cur, a); else att_f32<float>(ctx, cur, a);
+  AttArgs b = a;
+  b.tc_pair_bias = precision == LF_PRECISION_BF16 ? 1 : 0;
+  if (b.act_dtype == LF_DTYPE_BF16) att_f32<bf16>(ctx, cur, b); else att_f32<float>(ctx, cur, b);
   return LF_OK;
 }
 
@@ -1228,6 +1237,7 @@ lf_status lf_single_attention_run(lf_context* ctx, const lf_single_attention_des
     a.variance = LF_VARIANCE_FAST; a.residual = d->residual ? 1 : 0; a.bias_mode = 1; a.bias_swap = 0;
     a.pair_ch = d->pair_channels; a.pair_dtype = host ? LF_DTYPE_F32 : d->pair_dtype; a.pair_variance = LF_VARIANCE_FAST;
     a.mask_mode = 0; a.clamp = 0; a.eps = 1e-5f; a.pair_eps = 1e-5f; a.act_dtype = LF_DTYPE_F32; a.w = w;
+    a.tc_pair_bias = d->precision == LF_PRECISION_BF16 ? 1 : 0;
     a.act = st.in(d->single, (size_t)n * d->channels * 4);
     a.mask = (const float*)st.in(d->seq_mask, (size_t)n * 4);
     a.pair = st.in(d->pair, (size_t)n * n * d->pair_channels * dtype_size(a.pair_dtype));
@@ -1258,6 +1268,7 @@ lf_status lf_msa_attention_run(lf_context* ctx, const lf_msa_attention_desc* d, 
     a.variance = LF_VARIANCE_FAST; a.residual = d->residual ? 1 : 0; a.bias_mode = 1; a.bias_swap = 0;
     a.pair_ch = d->pair_channels; a.pair_dtype = host ? LF_DTYPE_F32 : d->pair_dtype; a.pair_variance = LF_VARIANCE_FAST;
     a.mask_mode = 0; a.clamp = 0; a.eps = 1e-5f; a.pair_eps = 1e-5f; a.act_dtype = LF_DTYPE_F32; a.w = w;
+    a.tc_pair_bias = d->precision == LF_PRECISION_BF16 ? 1 : 0;
     a.act = st.in(d->msa, R * d->channels * 4);
     const float* msa_mask = (const float*)st.in(d->msa_mask, R * 4);
     float* key_mask = cur.take<float>(R);

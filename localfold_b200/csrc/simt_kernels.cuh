@@ -371,6 +371,16 @@ __global__ void global_gate_kernel(const float* __restrict__ kvg, int ld, int ga
   gated[idx] = kvg[r * ld + gate0 + slot] * attended[(r % n) * HD + slot];
 }
 
+// fp16 pair bias [heads][Q][ld] (rows padded to ld) -> float32 [heads][Q][Q]
+__global__ void widen_bias_kernel(const __half* __restrict__ in, int heads, int Q, int ld, float* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)heads * Q * Q;
+  if (idx >= total) return;
+  int k = (int)(idx % Q);
+  int64_t hq = idx / Q;
+  out[idx] = __half2float(in[hq * ld + k]);
+}
+
 // One key mask for every sequence of an MSA: out[s][t] = max over s' of mask[s'][t] (AF3 pair-weighted
 // averaging: a token any sequence covers is a key for all of them).
 __global__ void msa_key_mask_kernel(const float* __restrict__ mask, int sequences, int tokens, float* __restrict__ out) {

@@ -142,6 +142,7 @@ lf_status check_status(lf_context* ctx) {
 }
 
 bool ln_gemm_supported(const lf_weights* w) { return w && !w->h.empty() && w->h[0] != nullptr; }
+bool pair_bias_supported(const lf_weights* w) { return w && w->h.size() >= 6 && w->h[4] != nullptr; }
 
 // The centre LayerNorm folded into the output projection: W' = diag(gain) Wz, s1[c] = sum_h fp16(W'[h][c]) (what the
 // tensor core will multiply the mean by), t[c] = bz[c] + sum_h offset[h] Wz[h][c]; fold = (s1 | t | bg + input offset through Wg).
@@ -231,6 +232,22 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     LF_CUDA(ctx, cudaMalloc(&img2, 128 * 256)); w->owned.push_back(img2);
     pack_weight_image(ctx, w->f[ATT_WO], 128, 128, 128, 0, 128, img2, 0, 1.0f);
     w->h[2] = img2;
+  }
+  if (w->has_pair_norm && w->has_pair_proj && w->dims.pair_channels == 128 && w->dims.heads <= 16 &&
+      (w->kind == LF_WEIGHTS_ATTENTION_AF2 || w->kind == LF_WEIGHTS_SINGLE_ATTENTION_AF3 || w->kind == LF_WEIGHTS_MSA_ATTENTION_AF3)) {
+    // pair bias from a 128-channel pair with a LayerNorm of its own: a 16-row image of the projection (gain in its
+    // rows, the offset's share as a bias) for the tensor-core projection kernel run with the bias chunk alone
+    op16* img = nullptr;
+    float* pb = nullptr;
+    LF_CUDA(ctx, cudaMalloc(&img, 16 * 256)); w->owned.push_back(img);
+    LF_CUDA(ctx, cudaMalloc(&pb, 16 * sizeof(float))); w->owned.push_back(pb);
+    LF_CUDA(ctx, cudaMemsetAsync(img, 0, 16 * 256, ctx->stream));
+    LF_CUDA(ctx, cudaMemsetAsync(pb, 0, 16 * sizeof(float), ctx->stream));
+    pack_weight_image(ctx, w->f[ATT_WB], 128, w->dims.heads, 16, 0, w->dims.heads, img, 0, 1.0f, w->f[ATT_PLN_G]);
+    fold_bias(ctx, w->f[ATT_WB], 128, w->dims.heads, 0, w->dims.heads, w->f[ATT_PLN_B], nullptr, 1.0f, pb);
+    if (w->h.size() < 6) w->h.resize(6, nullptr);
+    w->h[4] = img;
+    w->h[5] = pb;
   }
   if (w->kind == LF_WEIGHTS_TRANSITION_AF2 && w->dims.channels == 128 && w->dims.hidden == 512) {
     // per 128-wide hidden chunk: W1 slice image (rows = hidden columns, K = 128 inputs), then W2 slice

@@ -56,6 +56,9 @@ lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void
 // q (pre-scaled by head_dim^-1/2), k, v, sigmoid(gate) as fp16 logical rows [batch][ld][128] stored in 8-row x
 // 8-channel pieces (element (b, q, c) at b*ld*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8, ld = Q rounded up to 16) and the
 // pair bias fp16 [heads][batch rows][ldb] (null = none) from the normalised input
+lf_status pair_bias_project(lf_context* ctx, ArenaCursor& cur, const void* pair, int pair_dtype, int Q, int variance, float eps,
+                            int heads, const lf_weights* w, op16* bias, int ldb);
+bool pair_bias_supported(const lf_weights* w);
 lf_status attention_project(lf_context* ctx, ArenaCursor& cur, const void* act, int act_dtype, int batch, int Q,
                             int transpose, int variance, float eps, int heads, int head_dim, int bias_swap,
                             const lf_weights* w, op16* q, op16* k, op16* v, op16* g, op16* bias, int ldb);

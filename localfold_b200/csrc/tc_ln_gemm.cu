@@ -40,6 +40,8 @@ struct LnGemmParams {
   const float* bias;        // [n_bias]
   int n_bias;
   int n_chunks;
+  int first_chunk;          // attention projection: role of chunk 0 (0 = q|k, 1 = v|gate, 2 = pair bias); 2 with one chunk = bias only
+  int bias_col0;            // attention projection: where the pair-bias chunk's bias values start in `bias`
   int chunk_n[LG_MAX_CHUNKS];
   int chunk_row0[LG_MAX_CHUNKS];
   // triangle projection epilogue
@@ -750,13 +752,14 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
             }
           }
         } else {
-          if (j < 2) {
+          const int jr = j + p.first_chunk;
+          if (jr < 2) {
             // chunk 0 = (q | k), chunk 1 = (v | gate): parts 0,1 take the first tensor, 2,3 the second
             const int second = part >> 1, col0 = (part & 1) * 64;
-            op16* out = j == 0 ? (second ? p.out_k : p.out_q) : (second ? p.out_g : p.out_v);
-            const float4* bias4 = reinterpret_cast<const float4*>(sBias + j * 256 + second * 128 + col0);
-            const bool gate = (j == 1 && second == 1);
-            const bool has_bias = (p.bias_flags >> (j * 2 + second)) & 1;
+            op16* out = jr == 0 ? (second ? p.out_k : p.out_q) : (second ? p.out_g : p.out_v);
+            const float4* bias4 = reinterpret_cast<const float4*>(sBias + jr * 256 + second * 128 + col0);
+            const bool gate = (jr == 1 && second == 1);
+            const bool has_bias = (p.bias_flags >> (jr * 2 + second)) & 1;
             // destination of this row in the 8 x 8-piece layout: pieces along channels are 64 elements apart
             const uint32_t ur = (uint32_t)(valid ? r : 0), uq = (uint32_t)p.Q, rb = ur / uq, rq = ur % uq;
             op16* out_row = out + (int64_t)rb * p.ldq * 128 + (int64_t)(rq >> 3) * 1024 + (rq & 7) * 8;
@@ -808,12 +811,12 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
                   op16* ob = reinterpret_cast<op16*>(p.peer_bias.p[g2]);
 #pragma unroll
                   for (int h = 0; h < 16; ++h)
-                    if (h < p.heads) ob[h * pq + pdst] = __float2half_rn(__uint_as_float(v[h]) + sBias[512 + h]);
+                    if (h < p.heads) ob[h * pq + pdst] = __float2half_rn(__uint_as_float(v[h]) + sBias[p.bias_col0 + h]);
                 }
               } else {
 #pragma unroll
                 for (int h = 0; h < 16; ++h)
-                  if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]) + sBias[512 + h]);
+                  if (h < p.heads) p.out_bias[h * qq + dst] = __float2half_rn(__uint_as_float(v[h]) + sBias[p.bias_col0 + h]);
               }
             }
           }
@@ -993,6 +996,7 @@ static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const
   p.eps = eps; p.variance = variance;
   p.wimg = (const uint8_t*)w->h[0]; p.n_pad = 528; p.bias = (const float*)w->h[1]; p.n_bias = 528;
   p.n_chunks = bias ? 3 : 2;
+  p.first_chunk = 0; p.bias_col0 = 512;
   p.chunk_n[0] = 256; p.chunk_n[1] = 256; p.chunk_n[2] = 16;
   p.chunk_row0[0] = 0; p.chunk_row0[1] = 256; p.chunk_row0[2] = 512;
   p.out_q = q; p.out_k = k; p.out_v = v; p.out_g = g; p.out_bias = bias; p.ldb = ldb; p.heads = heads; p.bias_swap = bias_swap;
@@ -1010,6 +1014,28 @@ static lf_status attention_project_impl(lf_context* ctx, ArenaCursor& cur, const
 
 lf_status make_map_f16_3d_box(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                               uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
+
+// Pair bias from a pair tensor with a LayerNorm of its own (MSA row attention with pair bias, AF3 single attention,
+// AF3 MSA pair-weighted averaging): bias[h][q][k] = LN(pair)[q][k] . W[:, h] as fp16 [heads][Q][ldb], by the
+// projection kernel with the pair-bias chunk alone (image w->h[4]: 16 rows, gain folded; w->h[5]: the offset's share).
+lf_status pair_bias_project(lf_context* ctx, ArenaCursor& cur, const void* pair, int pair_dtype, int Q, int variance, float eps,
+                            int heads, const lf_weights* w, op16* bias, int ldb) {
+  if (cur.dry) return LF_OK;
+  LnGemmParams p{};
+  p.act = pair; p.act_bf16 = pair_dtype == LF_DTYPE_BF16; p.rows = (int64_t)Q * Q; p.transpose = 0; p.batch = Q; p.Q = Q;
+  p.eps = eps; p.variance = variance;
+  p.wimg = (const uint8_t*)w->h[4]; p.n_pad = 16; p.bias = (const float*)w->h[5]; p.n_bias = 16;
+  p.n_chunks = 1; p.chunk_n[0] = 16; p.chunk_row0[0] = 0; p.first_chunk = 2; p.bias_col0 = 0;
+  p.out_bias = bias; p.ldb = ldb; p.heads = heads; p.bias_swap = 0; p.ldq = (Q + 15) / 16 * 16;
+  p.status = (Status*)ctx->tc_status;
+  const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
+  ln_gemm_kernel<LG_EPI_ATTENTION><<<grid, LG_THREADS, ln_gemm_smem(16), ctx->stream>>>(CUtensorMap{}, CUtensorMap{}, PlaneMaps{}, p);
+  lf_prof_end(ctx);
+  ctx->launches++;
+  return LF_OK;
+}
 
 // out[dst(r)] = resid[dst(r)] + o[r] Wo + bo, r in logical order, dst the transposed-orientation rule
 lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int batch, int Q, int transpose,

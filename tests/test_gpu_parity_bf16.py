@@ -292,3 +292,55 @@ def test_af3_blocks_from_an_int5_bundle_on_disk(dev, tmp_path):
     f32 = lf.Af3PairformerStackGpu(dev).run({"pair": pair, "single": single, "pairMask": pair_mask, "seqMask": seq_mask,
                                              "tokens": n}, encoded, {"swapTransposedBias": True}, {"precision": "f32"})
     assert oracle.relative_l2(f32["pair"], wp) <= 2e-5
+
+
+@pytest.mark.parametrize("n,precision,bound", [(384, "f32", 1e-5), (384, "bf16", 2e-3), (203, "bf16", 2e-3)])
+def test_single_attention_af3_at_the_stack_shape(dev, n, precision, bound):
+    """AF3 single attention at the 48-block stack's shape (c_s = 384, 16 heads of 24, c_z = 128).  In 16-bit mode
+    its pair-sized pass - LayerNorm of the pair and the projection onto the 16 heads - runs on the tensor cores
+    (fp16 logits); the attention over the N tokens stays float32."""
+    import localfold_b200 as lf
+    from parity_report import record
+    cs, cz, heads = 384, 128, 16
+    d = syn.draw(1700 + n)
+    single = d.normal(n, cs)
+    pair = d.normal(n, n, cz)
+    seq_mask = np.ones(n, np.float32)
+    seq_mask[-5:] = 0
+    w = {"singlePairLogitsNormScale": 1 + d.normal(cz, std=0.1), "singlePairLogitsNormOffset": d.normal(cz, std=0.1),
+         "singlePairLogitsProjection": d.linear(cz, cz, heads),
+         "singleAttention": syn.af3_single_attention_weights(d, cs, heads, cs // heads)}
+    r = lf.Af3SingleAttentionGpu(dev).run(single, pair, seq_mask, {"n": n, "channels": cs, "pairChannels": cz}, w,
+                                          {"precision": precision})
+    logits = oracle.pair_logits_af3(pair, w["singlePairLogitsNormScale"], w["singlePairLogitsNormOffset"],
+                                    w["singlePairLogitsProjection"], heads)
+    want = oracle.single_attention_af3(single, logits, seq_mask, w["singleAttention"])
+    err = oracle.relative_l2(r["output"], want)
+    record("single_attention_af3", f"n={n} 16x24 {precision}", err, bound)
+    assert np.isfinite(r["output"]).all()
+    assert err <= bound
+
+
+def test_msa_row_attention_pair_bias_on_the_16_bit_path(dev):
+    """MSA row attention with a separate pair bias (c_m = 256, 8 heads of 32): in 16-bit mode the pair bias - the
+    pair-sized pass - comes from the tensor-core projection kernel; the rest of the operator is float32."""
+    import localfold_b200 as lf
+    from parity_report import record
+    S, n, cm, cz, heads = 12, 96, 256, 128, 8
+    d = syn.draw(1800)
+    msa = d.normal(S, n, cm)
+    pair = d.normal(n, n, cz)
+    mask = np.ones((S, n), np.float32)
+    mask[3] = 0
+    t = syn.af2_attention_weights(d, cm, heads, cz, separate=True)
+    t["pairBias"]["layerNormScale"] = 1 + d.normal(cz, std=0.2)
+    t["pairBias"]["layerNormOffset"] = d.normal(cz, std=0.2)
+    pb = dict(t["pairBias"], source="separate", activations=pair, channels=cz)
+    inp = {"activations": msa, "mask": mask, "batch": S, "queryLength": n, "channels": cm, "heads": heads,
+           "weights": t["attention"], "pairBias": pb}
+    want = oracle.attention_af2(msa, mask, S, n, cm, heads, t["attention"], False, pb)
+    for precision, bound in (("f32", 1e-5), ("bf16", 2e-3)):
+        r = lf.AttentionGpu(dev).run(inp, {"precision": precision, "variance": "two-pass"})
+        err = oracle.relative_l2(r["output"], want)
+        record("msa_row_attention", f"S={S} n={n} 8x32 {precision}", err, bound)
+        assert err <= bound
