@@ -1188,29 +1188,51 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
     float* nrm = cur.take<float>(rows * cm);
     float* left = cur.take<float>(rows * c);
     float* right = cur.take<float>(rows * c);
+    // 16-bit mode: the outer product sum over the sequences, [(i,a)] x [(j,b)] over s, is one tensor-core GEMM
+    // (the triangle contraction's kernel in its MN-major form, one plane) with fp16 operands and fp16 sums scaled
+    // by a power of two near 1 / S so that they stay far inside fp16 whatever the depth
+    const bool tc_outer = d->precision == LF_PRECISION_BF16 && ((int64_t)N * c) % 8 == 0 && tc::contract_supported(N, 1);
+    const float outer_scale = tc_outer ? ldexpf(1.0f, -(int)ceilf(log2f((float)S))) : 1.0f;
     // output rows per chunk: bound the [ni*c][N*c] outer-product buffer near 1 GiB
-    int64_t per_row = (int64_t)c * N * c * 4;
+    int64_t per_row = (int64_t)c * N * c * (tc_outer ? 2 : 4);
     int ni = (int)((((int64_t)1 << 30) + per_row - 1) / per_row);
     if (ni > N) ni = N;
-    float* outer = cur.take<float>((int64_t)ni * c * N * c);
+    float* outer = tc_outer ? nullptr : cur.take<float>((int64_t)ni * c * N * c);
+    op16* outer16 = tc_outer ? cur.take<op16>((int64_t)ni * c * N * c) : nullptr;
+    op16* left16 = tc_outer ? cur.take<op16>(rows * c) : nullptr;
+    op16* right16 = tc_outer ? cur.take<op16>(rows * c) : nullptr;
     LAUNCH(ctx, cur, (simt::layer_norm_kernel<float>), lf_ceil_div(rows, 8), 256, 0, msa, rows, cm, f[OPM_LN_G], f[OPM_LN_B],
            d->layer_norm_epsilon, d->variance, 0, 1, 1, nrm);
     sgemm(ctx, cur, false, false, 0, (int)rows, c, cm, nrm, cm, 0, f[OPM_WL], c, 0, left, c, 0, f[OPM_BL], 0, 1);
     sgemm(ctx, cur, false, false, 0, (int)rows, c, cm, nrm, cm, 0, f[OPM_WR], c, 0, right, c, 0, f[OPM_BR], 0, 1);
-    LAUNCH(ctx, cur, simt::mask_rows_kernel, lf_ceil_div(rows * c, 256), 256, 0, left, right, mask, rows, c);
+    if (tc_outer) LAUNCH(ctx, cur, simt::mask_rows_half_kernel, lf_ceil_div(rows * c, 256), 256, 0, left, right, mask, rows, c, left16, right16);
+    else LAUNCH(ctx, cur, simt::mask_rows_kernel, lf_ceil_div(rows * c, 256), 256, 0, left, right, mask, rows, c);
     constexpr int JT = 8;
     size_t smem = (size_t)(JT * c * c + JT) * sizeof(float);
     for (int i0 = 0; i0 < N; i0 += ni) {
       int cnt = N - i0 < ni ? N - i0 : ni;
       // outer[(i-i0)*c + a][j*c + b] = sum_s left[s][i][a] * right[s][j][b]
+      dim3 grid(lf_ceil_div(N, JT), cnt);
+      if (tc_outer) {
+        // x[(i,a)][(j,b)] = scale * sum_s left[s][(i,a)] right[s][(j,b)]: rows of the operands are s, so both are
+        // MN-major; the kernel's "b" is its M operand
+        LF_TRY(tc::contract_rect(ctx, cur, right16, left16 + (int64_t)i0 * c, outer16, cnt * c, N * c, S, N * c, N * c,
+                                 (int64_t)cnt * c * N * c, 0, 1, 1, outer_scale));
+        if (d->act_dtype == LF_DTYPE_BF16)
+          LAUNCH(ctx, cur, (simt::opm_output_kernel<bf16, JT, op16>), grid, 128, smem, outer16, 1.0f / outer_scale, f[OPM_WOUT], f[OPM_BOUT],
+                 mask, S, N, c, cz, i0, d->normalization_epsilon, 0, (const bf16*)resid, (bf16*)out);
+        else
+          LAUNCH(ctx, cur, (simt::opm_output_kernel<float, JT, op16>), grid, 128, smem, outer16, 1.0f / outer_scale, f[OPM_WOUT], f[OPM_BOUT],
+                 mask, S, N, c, cz, i0, d->normalization_epsilon, 0, (const float*)resid, (float*)out);
+        continue;
+      }
       sgemm(ctx, cur, true, false, 0, cnt * c, N * c, S, left + (int64_t)i0 * c, (int64_t)N * c, 0, right, (int64_t)N * c, 0,
             outer, (int64_t)N * c, 0, nullptr, 0, 1);
-      dim3 grid(lf_ceil_div(N, JT), cnt);
       if (d->act_dtype == LF_DTYPE_BF16)
-        LAUNCH(ctx, cur, (simt::opm_output_kernel<bf16, JT>), grid, 128, smem, outer, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
+        LAUNCH(ctx, cur, (simt::opm_output_kernel<bf16, JT, float>), grid, 128, smem, outer, 1.0f, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
                i0, d->normalization_epsilon, 0, (const bf16*)resid, (bf16*)out);
       else
-        LAUNCH(ctx, cur, (simt::opm_output_kernel<float, JT>), grid, 128, smem, outer, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
+        LAUNCH(ctx, cur, (simt::opm_output_kernel<float, JT, float>), grid, 128, smem, outer, 1.0f, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
                i0, d->normalization_epsilon, 0, (const float*)resid, (float*)out);
     }
     st.flush();

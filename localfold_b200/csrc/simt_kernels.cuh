@@ -489,6 +489,16 @@ __global__ void swiglu_kernel(const float* __restrict__ wide, int64_t rows, int 
 // ---------------------------------------------------------------------------
 // Outer product mean glue.
 // rows [S*N][c]: multiply every row by its mask value.
+// the same into fp16 copies (operands of the tensor-core outer product)
+__global__ void mask_rows_half_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ mask,
+                                      int64_t rows, int c, __half* __restrict__ a16, __half* __restrict__ b16) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * c) return;
+  float m = mask[idx / c];
+  a16[idx] = __float2half_rn(a[idx] * m);
+  b16[idx] = __float2half_rn(b[idx] * m);
+}
+
 __global__ void mask_rows_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ mask,
                                  int64_t rows, int c) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -501,8 +511,9 @@ __global__ void mask_rows_kernel(float* __restrict__ a, float* __restrict__ b, c
 // outer: [(i - i0)*c + a][j*c + b] for i in [i0, i0+ni); out[i][j][z] =
 // (sum_ab outer * wout[(a*c+b)][z] + bout[z]) / (eps + count(i,j)), + resid.
 // One block per (i, group of JT columns j); thread z loops over the c*c products.
-template <typename TAct, int JT>
-__global__ void opm_output_kernel(const float* __restrict__ outer, const float* __restrict__ wout,
+// (TOuter: float32 sums, or the tensor-core contraction's fp16 sums scaled by 1 / outer_scale)
+template <typename TAct, int JT, typename TOuter>
+__global__ void opm_output_kernel(const TOuter* __restrict__ outer, float outer_scale, const float* __restrict__ wout,
                                   const float* __restrict__ bout, const float* __restrict__ mask,
                                   int S, int N, int c, int cz, int i0, float norm_eps,
                                   int bias_after_norm, const TAct* __restrict__ resid,
@@ -517,7 +528,7 @@ __global__ void opm_output_kernel(const float* __restrict__ outer, const float* 
   for (int idx = threadIdx.x; idx < JT * cc; idx += blockDim.x) {
     int jj = idx / cc, ab = idx % cc, a = ab / c, b2 = ab % c;
     int j = j0 + jj;
-    tile[idx] = j < N ? outer[((int64_t)(i - i0) * c + a) * ldo + (int64_t)j * c + b2] : 0.f;
+    tile[idx] = j < N ? to_f(outer[((int64_t)(i - i0) * c + a) * ldo + (int64_t)j * c + b2]) * outer_scale : 0.f;
   }
   if (threadIdx.x < JT) {
     int j = j0 + threadIdx.x;

@@ -543,7 +543,9 @@ static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a,
                                int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale,
                                const PeerPtrs* peers, int rows_per_rank, int ch0) {
   if (cur.dry) return LF_OK;
-  if (ld_ab % 8 != 0 || ld_ab < k_len || ldx % 8 != 0 || col0 % 8 != 0)
+  // a row of an operand holds k (K-major form) or the M / N index (MN-major form)
+  const int row_len = incoming ? (m_rows > n_rows ? m_rows : n_rows) : k_len;
+  if (ld_ab % 8 != 0 || ld_ab < row_len || ldx % 8 != 0 || col0 % 8 != 0)
     return lf_fail(ctx, LF_ERR_ARGUMENT, "contraction strides must be multiples of 8 and cover the row");
   CUtensorMap mapA, mapB;
   const uint64_t row_bytes = (uint64_t)ld_ab * 2;
@@ -551,7 +553,7 @@ static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a,
     LF_TRY(make_map_f16_3d(ctx, &mapA, a, k_len, m_rows, c, row_bytes, (uint64_t)m_rows * row_bytes, CT_BK, CT_BM));
     LF_TRY(make_map_f16_3d(ctx, &mapB, b, k_len, n_rows, c, row_bytes, (uint64_t)n_rows * row_bytes, CT_BK, CT_BN));
   } else {
-    // square form only: A(i,k) = b[h][k][i], B(j,k) = a[h][k][j]: boxes of 64 (i or j) x 64 (k)
+    // A(i,k) = b[h][k][i], B(j,k) = a[h][k][j]: boxes of 64 (i or j) x 64 (k)
     LF_TRY(make_map_f16_3d(ctx, &mapA, b, m_rows, k_len, c, row_bytes, (uint64_t)k_len * row_bytes, 64, CT_BK));
     LF_TRY(make_map_f16_3d(ctx, &mapB, a, n_rows, k_len, c, row_bytes, (uint64_t)k_len * row_bytes, 64, CT_BK));
   }

@@ -344,3 +344,28 @@ def test_msa_row_attention_pair_bias_on_the_16_bit_path(dev):
         err = oracle.relative_l2(r["output"], want)
         record("msa_row_attention", f"S={S} n={n} 8x32 {precision}", err, bound)
         assert err <= bound
+
+
+@pytest.mark.parametrize("S,n,cm,c", [(128, 256, 256, 32), (37, 50, 64, 32), (300, 24, 64, 8)])
+def test_outer_product_mean_on_the_16_bit_path(dev, S, n, cm, c):
+    """In 16-bit mode the sum over the sequences of the outer products - one GEMM of [(i,a)] x [(j,b)] over s - runs
+    on the tensor cores with fp16 operands and fp16 sums (scaled by a power of two near 1 / S); the c*c -> c_z
+    projection and the division by the coverage stay float32.  First case: the Evoformer block's shape."""
+    import localfold_b200 as lf
+    from parity_report import record
+    d = syn.draw(1900 + S)
+    msa = d.normal(S, n, cm)
+    mask = (d.rng.random((S, n)) >= 0.15).astype(np.float32)
+    mask[0] = 1
+    w = syn.af2_opm_weights(d, cm, c, 128)
+    w["leftBias"] = d.normal(c, std=0.2)
+    w["rightBias"] = d.normal(c, std=0.2)
+    w["outputBias"] = d.normal(128, std=0.2)
+    got = lf.OuterProductMeanGpu(dev).run({"activations": msa, "mask": mask, "sequences": S, "length": n, "cM": cm,
+                                           "cOuter": c, "cZ": 128, "weights": w},
+                                          {"precision": "bf16", "variance": "two-pass"})["output"]
+    want = oracle.outer_product_mean_af2(msa, mask, w, c, 128)
+    err = oracle.relative_l2(got, want)
+    record("outer_product_mean", f"S={S} n={n} cM={cm} c={c} 16-bit", err, 2e-3)
+    assert np.isfinite(got).all()
+    assert err <= 2e-3
