@@ -964,9 +964,62 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   return LF_OK;
 }
 
+// 16-bit path for the shapes the fused projection kernel does not take (MSA row attention with pair bias: c_m = 256,
+// 8 heads of 32; MSA column attention): float32 LayerNorm and projections, then the tensor-core attention core
+// on four heads at a time (logits, softmax and P V in tensor memory), float32 output projection.
+template <typename T>
+lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
+  const int64_t R = (int64_t)a.batch * a.Q;
+  const int HD = a.heads * a.d, c = a.ch, groups = a.heads / 4;
+  const auto& f = a.w->f;
+  const int ldb = (a.Q + 15) / 16 * 16;
+  const int64_t RP = (int64_t)a.batch * ldb;
+  float* nrm = cur.take<float>(R * c);
+  float* qkvg = cur.take<float>(R * 4 * HD);
+  float* o = cur.take<float>(R * HD);
+  op16* bias16 = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
+  op16* q16 = cur.take<op16>(RP * 128);
+  op16* k16 = cur.take<op16>(RP * 128);
+  op16* v16 = cur.take<op16>(RP * 128);
+  op16* g16 = cur.take<op16>(RP * 128);
+  op16* o16 = cur.take<op16>(RP * 128);
+  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(R, 8), 256, 0, (const T*)a.act, R, c, f[ATT_LN_G],
+         f[ATT_LN_B], a.eps, a.variance, a.transpose, a.batch, a.Q, nrm);
+  sgemm(ctx, cur, false, false, simt::EPI_SIGMOID_FROM_COL, (int)R, 4 * HD, c, nrm, c, 0, f[ATT_W4], 4 * HD, 0, qkvg,
+        4 * HD, 0, f[ATT_B4], 3 * HD, 1);
+  if (ldb != a.Q && !cur.dry) {
+    // padding rows and columns are read as keys past the end (masked out): they must hold finite values
+    if (bias16) cudaMemsetAsync(bias16, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
+    cudaMemsetAsync(k16, 0, (size_t)RP * 128 * sizeof(op16), ctx->stream);
+    cudaMemsetAsync(v16, 0, (size_t)RP * 128 * sizeof(op16), ctx->stream);
+  }
+  if (a.bias_mode == 1)
+    LF_TRY(tc::pair_bias_project(ctx, cur, a.pair, a.pair_dtype, a.Q, a.pair_variance, a.pair_eps, a.heads, a.w, bias16, ldb));
+  const int64_t pieces = R * 16;
+  const float qscale = 1.0f / sqrtf((float)a.d);
+  for (int gi = 0; gi < groups; ++gi) {
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 0 * HD + gi * 128, qscale, a.batch, a.Q, ldb, q16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 1 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, k16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 2 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, v16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 3 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, g16);
+    LF_TRY(tc::attention_core(ctx, cur, q16, k16, v16, g16, bias16 ? bias16 + (int64_t)gi * 4 * a.Q * ldb : nullptr, ldb, a.mask, a.batch,
+                              a.Q, a.transpose, a.mask_mode, a.clamp, o16));
+    LAUNCH(ctx, cur, simt::pieces_to_rows_kernel, lf_ceil_div(pieces, 256), 256, 0, o16, a.batch, a.Q, ldb, (int64_t)HD, gi * 128, o);
+  }
+  float* proj = nrm;   // the normalised input is dead
+  sgemm(ctx, cur, false, false, 0, (int)R, c, HD, o, HD, 0, f[ATT_WO], c, 0, proj, c, 0, f[ATT_BO], 0, 1);
+  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
+         a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
+  return LF_OK;
+}
+
 lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int precision) {
   if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && a.heads == 4 && a.d == 32 && tc::ln_gemm_supported(a.w)) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
+  }
+  if (precision == LF_PRECISION_BF16 && a.d == 32 && a.heads % 4 == 0 && tc::contract_supported(1, 1) &&
+      (a.bias_mode == 0 || (a.bias_mode == 1 && tc::pair_bias_supported(a.w) && !a.bias_swap))) {
+    return a.act_dtype == LF_DTYPE_BF16 ? att_mixed<bf16>(ctx, cur, a) : att_mixed<float>(ctx, cur, a);
   }
   AttArgs b = a;
   b.tc_pair_bias = precision == LF_PRECISION_BF16 ? 1 : 0;

@@ -371,6 +371,42 @@ __global__ void global_gate_kernel(const float* __restrict__ kvg, int ld, int ga
   gated[idx] = kvg[r * ld + gate0 + slot] * attended[(r % n) * HD + slot];
 }
 
+// Attention activations between the float32 projections and the tensor-core attention core: 128 channels (four
+// heads of 32) of logical rows (b, q) as fp16 8-row x 8-channel pieces, element (b, q, c) at
+// b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8.  `src` rows are `ld` floats; columns col0 .. col0+127.
+__global__ void rows_to_pieces_kernel(const float* __restrict__ src, int64_t ld, int col0, float scale, int batch, int Q,
+                                      int ldq, __half* __restrict__ dst) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 8-channel piece)
+  int64_t total = (int64_t)batch * Q * 16;
+  if (idx >= total) return;
+  int piece = (int)(idx % 16);
+  int64_t r = idx / 16;
+  int b = (int)(r / Q), q = (int)(r % Q);
+  const float* x = src + r * ld + col0 + piece * 8;
+  __half2 h[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(x[2 * e] * scale, x[2 * e + 1] * scale);
+  __half* out = dst + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
+  *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h);
+}
+
+// ... and back: the core's output pieces into columns col0 .. col0+127 of float32 rows of `ld`
+__global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch, int Q, int ldq, int64_t ld, int col0,
+                                      float* __restrict__ dst) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = (int64_t)batch * Q * 16;
+  if (idx >= total) return;
+  int piece = (int)(idx % 16);
+  int64_t r = idx / 16;
+  int b = (int)(r / Q), q = (int)(r % Q);
+  const __half* in = src + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
+  uint4 raw = *reinterpret_cast<const uint4*>(in);
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+  float* out = dst + r * ld + col0 + piece * 8;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { float2 f = __half22float2(h[e]); out[2 * e] = f.x; out[2 * e + 1] = f.y; }
+}
+
 // fp16 pair bias [heads][Q][ld] (rows padded to ld) -> float32 [heads][Q][Q]
 __global__ void widen_bias_kernel(const __half* __restrict__ in, int heads, int Q, int ld, float* __restrict__ out) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
