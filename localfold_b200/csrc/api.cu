@@ -964,9 +964,26 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   return LF_OK;
 }
 
+// 16-bit GEMM on the tensor cores for activations of any width: out[m][n] = sum_k a[m][k] w[n][k], fp16 operands
+// with k contiguous, float32 accumulation, fp16 result (the triangle contraction's kernel on one plane).
+lf_status hgemm(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* w, op16* out, int64_t M, int N, int K) {
+  if (M > 0x7fffffff) return lf_fail(ctx, LF_ERR_SHAPE, "too many rows for one projection");
+  return tc::contract_rect(ctx, cur, a, w, out, (int)M, N, K, K, N, 0, 0, 1, 0, 1.0f);
+}
+
+// columns col0 .. col0+N-1 of float32 weights [K][ldw] as the fp16 [N][K] operand of hgemm
+op16* weight_operand(lf_context* ctx, ArenaCursor& cur, const float* w, int K, int ldw, int col0, int N) {
+  op16* t = cur.take<op16>((int64_t)N * K);
+  LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)N * K, 256), 256, 0, w, K, ldw, col0, N, t);
+  return t;
+}
+
+bool hgemm_supported(int k1, int k2) { return k1 % 8 == 0 && k2 % 8 == 0 && tc::contract_supported(1, 1); }
+
 // 16-bit path for the shapes the fused projection kernel does not take (MSA row attention with pair bias: c_m = 256,
-// 8 heads of 32; MSA column attention): float32 LayerNorm and projections, then the tensor-core attention core
-// on four heads at a time (logits, softmax and P V in tensor memory), float32 output projection.
+// 8 heads of 32; MSA column attention): LayerNorm to fp16, the q/k/v/gate projection as one tensor-core GEMM, the
+// attention core on four heads at a time (logits, softmax and P V in tensor memory), the output projection as a
+// second GEMM, bias and residual in float32.
 template <typename T>
 lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   const int64_t R = (int64_t)a.batch * a.Q;
@@ -974,19 +991,19 @@ lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   const auto& f = a.w->f;
   const int ldb = (a.Q + 15) / 16 * 16;
   const int64_t RP = (int64_t)a.batch * ldb;
-  float* nrm = cur.take<float>(R * c);
-  float* qkvg = cur.take<float>(R * 4 * HD);
-  float* o = cur.take<float>(R * HD);
+  op16* nrm = cur.take<op16>(R * c);
+  op16* qkvg = cur.take<op16>(R * 4 * HD);
+  op16* o = cur.take<op16>(R * HD);
   op16* bias16 = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
   op16* q16 = cur.take<op16>(RP * 128);
   op16* k16 = cur.take<op16>(RP * 128);
   op16* v16 = cur.take<op16>(RP * 128);
   op16* g16 = cur.take<op16>(RP * 128);
   op16* o16 = cur.take<op16>(RP * 128);
-  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T>), lf_ceil_div(R, 8), 256, 0, (const T*)a.act, R, c, f[ATT_LN_G],
+  LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16>), lf_ceil_div(R, 8), 256, 0, (const T*)a.act, R, c, f[ATT_LN_G],
          f[ATT_LN_B], a.eps, a.variance, a.transpose, a.batch, a.Q, nrm);
-  sgemm(ctx, cur, false, false, simt::EPI_SIGMOID_FROM_COL, (int)R, 4 * HD, c, nrm, c, 0, f[ATT_W4], 4 * HD, 0, qkvg,
-        4 * HD, 0, f[ATT_B4], 3 * HD, 1);
+  op16* w4 = weight_operand(ctx, cur, f[ATT_W4], c, 4 * HD, 0, 4 * HD);
+  LF_TRY(hgemm(ctx, cur, nrm, w4, qkvg, R, 4 * HD, c));
   if (ldb != a.Q && !cur.dry) {
     // padding rows and columns are read as keys past the end (masked out): they must hold finite values
     if (bias16) cudaMemsetAsync(bias16, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
@@ -997,18 +1014,20 @@ lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
     LF_TRY(tc::pair_bias_project(ctx, cur, a.pair, a.pair_dtype, a.Q, a.pair_variance, a.pair_eps, a.heads, a.w, bias16, ldb));
   const int64_t pieces = R * 16;
   const float qscale = 1.0f / sqrtf((float)a.d);
+  const int64_t ld4 = (int64_t)4 * HD;
   for (int gi = 0; gi < groups; ++gi) {
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 0 * HD + gi * 128, qscale, a.batch, a.Q, ldb, q16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 1 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, k16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 2 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, v16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel, lf_ceil_div(pieces, 256), 256, 0, qkvg, (int64_t)4 * HD, 3 * HD + gi * 128, 1.0f, a.batch, a.Q, ldb, g16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 0 * HD + gi * 128, f[ATT_B4], qscale, 0, a.batch, a.Q, ldb, q16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 1 * HD + gi * 128, f[ATT_B4], 1.0f, 0, a.batch, a.Q, ldb, k16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 2 * HD + gi * 128, f[ATT_B4], 1.0f, 0, a.batch, a.Q, ldb, v16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 3 * HD + gi * 128, f[ATT_B4], 1.0f, 1, a.batch, a.Q, ldb, g16);
     LF_TRY(tc::attention_core(ctx, cur, q16, k16, v16, g16, bias16 ? bias16 + (int64_t)gi * 4 * a.Q * ldb : nullptr, ldb, a.mask, a.batch,
                               a.Q, a.transpose, a.mask_mode, a.clamp, o16));
-    LAUNCH(ctx, cur, simt::pieces_to_rows_kernel, lf_ceil_div(pieces, 256), 256, 0, o16, a.batch, a.Q, ldb, (int64_t)HD, gi * 128, o);
+    LAUNCH(ctx, cur, simt::pieces_to_rows_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, o16, a.batch, a.Q, ldb, (int64_t)HD, gi * 128, o);
   }
-  float* proj = nrm;   // the normalised input is dead
-  sgemm(ctx, cur, false, false, 0, (int)R, c, HD, o, HD, 0, f[ATT_WO], c, 0, proj, c, 0, f[ATT_BO], 0, 1);
-  LAUNCH(ctx, cur, (simt::finish_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, (const float*)nullptr,
+  op16* wo = weight_operand(ctx, cur, f[ATT_WO], HD, c, 0, c);
+  op16* proj = nrm;   // the normalised input is dead
+  LF_TRY(hgemm(ctx, cur, o, wo, proj, R, c, HD));
+  LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, 1.0f, f[ATT_BO],
          a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
   return LF_OK;
 }
@@ -1017,7 +1036,7 @@ lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int 
   if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && a.heads == 4 && a.d == 32 && tc::ln_gemm_supported(a.w)) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
   }
-  if (precision == LF_PRECISION_BF16 && a.d == 32 && a.heads % 4 == 0 && tc::contract_supported(1, 1) &&
+  if (precision == LF_PRECISION_BF16 && a.d == 32 && a.heads % 4 == 0 && hgemm_supported(a.ch, a.heads * a.d) &&
       (a.bias_mode == 0 || (a.bias_mode == 1 && tc::pair_bias_supported(a.w) && !a.bias_swap))) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_mixed<bf16>(ctx, cur, a) : att_mixed<float>(ctx, cur, a);
   }
@@ -1057,9 +1076,38 @@ void trn_f32(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
   }
 }
 
+// 16-bit path for the widths the fused transition kernel does not take (the MSA transitions, other pair widths):
+// LayerNorm to fp16, both projections as tensor-core GEMMs, the hidden activation in place on fp16.
+template <typename T>
+lf_status trn_half(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
+  const auto& f = a.w->f;
+  const int c = a.ch, hd = a.hidden, wide = a.swiglu ? 2 * hd : hd;
+  const int64_t chunk = a.rows < (1 << 18) ? a.rows : (1 << 18);
+  op16* nrm = cur.take<op16>(chunk * c);
+  op16* h1 = cur.take<op16>(chunk * wide);
+  op16* h2 = a.swiglu ? cur.take<op16>(chunk * hd) : h1;
+  op16* w1 = weight_operand(ctx, cur, f[TRN_W1], c, wide, 0, wide);
+  op16* w2 = weight_operand(ctx, cur, f[TRN_W2], hd, c, 0, c);
+  for (int64_t r0 = 0; r0 < a.rows; r0 += chunk) {
+    int64_t rows = a.rows - r0 < chunk ? a.rows - r0 : chunk;
+    const T* in = (const T*)a.act + r0 * c;
+    T* out = (T*)a.out + r0 * c;
+    LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16>), lf_ceil_div(rows, 8), 256, 0, in, rows, c, f[TRN_LN_G], f[TRN_LN_B],
+           a.eps, a.variance, 0, 1, 1, nrm);
+    LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c));
+    LAUNCH(ctx, cur, simt::hidden_act_half_kernel, lf_ceil_div(rows * hd, 256), 256, 0, h1, f[TRN_B1], rows, hd, wide, a.swiglu, h2);
+    LF_TRY(hgemm(ctx, cur, h2, w2, nrm, rows, c, hd));
+    LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(rows * c, 256), 256, 0, nrm, 1.0f, f[TRN_B2],
+           a.residual ? in : (const T*)nullptr, rows, c, 0, 1, 1, out);
+  }
+  return LF_OK;
+}
+
 lf_status trn_dispatch(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a, int precision) {
   if (precision == LF_PRECISION_BF16 && tc::transition_supported(a.w))
     return tc::transition_run(ctx, cur, a.act, a.act_dtype, a.rows, a.variance, a.eps, a.w, a.residual ? a.act : nullptr, a.out);
+  if (precision == LF_PRECISION_BF16 && hgemm_supported(a.ch, a.hidden))
+    return a.act_dtype == LF_DTYPE_BF16 ? trn_half<bf16>(ctx, cur, a) : trn_half<float>(ctx, cur, a);
   if (a.act_dtype == LF_DTYPE_BF16) trn_f32<bf16>(ctx, cur, a); else trn_f32<float>(ctx, cur, a);
   return LF_OK;
 }
@@ -1238,9 +1286,11 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
       }
     } else { out = d->out; resid = d->residual ? d->out : nullptr; }
     const auto& f = w->f;
-    float* nrm = cur.take<float>(rows * cm);
-    float* left = cur.take<float>(rows * c);
-    float* right = cur.take<float>(rows * c);
+    // 16-bit mode, widths in whole groups of 8: every GEMM of the operator runs on the tensor cores
+    const bool tc_full = d->precision == LF_PRECISION_BF16 && c % 8 == 0 && hgemm_supported(cm, c * c);
+    float* nrm = tc_full ? nullptr : cur.take<float>(rows * cm);
+    float* left = tc_full ? nullptr : cur.take<float>(rows * c);
+    float* right = tc_full ? nullptr : cur.take<float>(rows * c);
     // 16-bit mode: the outer product sum over the sequences, [(i,a)] x [(j,b)] over s, is one tensor-core GEMM
     // (the triangle contraction's kernel in its MN-major form, one plane) with fp16 operands and fp16 sums scaled
     // by a power of two near 1 / S so that they stay far inside fp16 whatever the depth
@@ -1254,6 +1304,39 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
     op16* outer16 = tc_outer ? cur.take<op16>((int64_t)ni * c * N * c) : nullptr;
     op16* left16 = tc_outer ? cur.take<op16>(rows * c) : nullptr;
     op16* right16 = tc_outer ? cur.take<op16>(rows * c) : nullptr;
+    if (tc_full) {
+      // LayerNorm to fp16, left | right projection as one GEMM; then per chunk of output rows the outer product
+      // summed over the sequences (GEMM over s), regrouped per pair, projected onto c_z (GEMM over (a, b))
+      op16* nrm16 = cur.take<op16>(rows * cm);
+      op16* lr16 = cur.take<op16>(rows * 2 * c);
+      op16* wlr = cur.take<op16>((int64_t)2 * c * cm);
+      op16* grouped = cur.take<op16>((int64_t)ni * N * c * c);
+      op16* proj16 = cur.take<op16>((int64_t)ni * N * cz);
+      float* counts = cur.take<float>((int64_t)N * N);
+      LAUNCH(ctx, cur, (simt::layer_norm_kernel<float, op16>), lf_ceil_div(rows, 8), 256, 0, msa, rows, cm, f[OPM_LN_G], f[OPM_LN_B],
+             d->layer_norm_epsilon, d->variance, 0, 1, 1, nrm16);
+      LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)c * cm, 256), 256, 0, f[OPM_WL], cm, c, 0, c, wlr);
+      LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)c * cm, 256), 256, 0, f[OPM_WR], cm, c, 0, c, wlr + (int64_t)c * cm);
+      LF_TRY(hgemm(ctx, cur, nrm16, wlr, lr16, rows, 2 * c, cm));
+      LAUNCH(ctx, cur, simt::opm_split_half_kernel, lf_ceil_div(rows * c, 256), 256, 0, lr16, f[OPM_BL], f[OPM_BR], mask, rows, c, left16, right16);
+      LAUNCH(ctx, cur, simt::opm_counts_kernel, lf_ceil_div((int64_t)N * N, 256), 256, 0, mask, S, N, counts);
+      op16* wout = weight_operand(ctx, cur, f[OPM_WOUT], c * c, cz, 0, cz);
+      for (int i0 = 0; i0 < N; i0 += ni) {
+        int cnt = N - i0 < ni ? N - i0 : ni;
+        LF_TRY(tc::contract_rect(ctx, cur, right16, left16 + (int64_t)i0 * c, outer16, cnt * c, N * c, S, N * c, N * c,
+                                 (int64_t)cnt * c * N * c, 0, 1, 1, outer_scale));
+        LAUNCH(ctx, cur, simt::opm_regroup_half_kernel, lf_ceil_div((int64_t)cnt * N * c * (c / 8), 256), 256, 0, outer16, cnt, N, c, grouped);
+        LF_TRY(hgemm(ctx, cur, grouped, wout, proj16, (int64_t)cnt * N, cz, c * c));
+        if (d->act_dtype == LF_DTYPE_BF16)
+          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<bf16>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
+                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, (const bf16*)resid, (bf16*)out);
+        else
+          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<float>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
+                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, (const float*)resid, (float*)out);
+      }
+      st.flush();
+      return LF_OK;
+    }
     LAUNCH(ctx, cur, (simt::layer_norm_kernel<float>), lf_ceil_div(rows, 8), 256, 0, msa, rows, cm, f[OPM_LN_G], f[OPM_LN_B],
            d->layer_norm_epsilon, d->variance, 0, 1, 1, nrm);
     sgemm(ctx, cur, false, false, 0, (int)rows, c, cm, nrm, cm, 0, f[OPM_WL], c, 0, left, c, 0, f[OPM_BL], 0, 1);

@@ -31,11 +31,11 @@ __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf
 // LayerNorm over the last axis, one warp per row.  `rows` logical rows; logical
 // row r = b*Q + i reads memory row i*batch + b when `transpose` (batch, Q > 0).
 // variance: 1 two-pass, 2 fast (E[x^2]-E[x]^2, unclamped).
-template <typename TIn>
+template <typename TIn, typename TOut = float>
 __global__ void layer_norm_kernel(const TIn* __restrict__ in, int64_t rows, int ch,
                                   const float* __restrict__ gamma, const float* __restrict__ beta,
                                   float eps, int variance, int transpose, int batch, int Q,
-                                  float* __restrict__ out) {
+                                  TOut* __restrict__ out) {
   int lane = threadIdx.x & 31;
   int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -57,8 +57,8 @@ __global__ void layer_norm_kernel(const TIn* __restrict__ in, int64_t rows, int 
   float inv = rsqrtf(var + eps);
   // one Newton step: rsqrtf is 2 ulp, the parity bar is tighter than that squared error allows
   inv = inv * (1.5f - 0.5f * (var + eps) * inv * inv);
-  float* y = out + row * ch;
-  for (int c = lane; c < ch; c += 32) y[c] = (to_f(x[c]) - mean) * inv * gamma[c] + beta[c];
+  TOut* y = out + row * ch;
+  for (int c = lane; c < ch; c += 32) y[c] = from_f<TOut>((to_f(x[c]) - mean) * inv * gamma[c] + beta[c]);
 }
 
 // ---------------------------------------------------------------------------
@@ -371,28 +371,39 @@ __global__ void global_gate_kernel(const float* __restrict__ kvg, int ld, int ga
   gated[idx] = kvg[r * ld + gate0 + slot] * attended[(r % n) * HD + slot];
 }
 
-// Attention activations between the float32 projections and the tensor-core attention core: 128 channels (four
+// Attention activations between the projections and the tensor-core attention core: 128 channels (four
 // heads of 32) of logical rows (b, q) as fp16 8-row x 8-channel pieces, element (b, q, c) at
-// b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8.  `src` rows are `ld` floats; columns col0 .. col0+127.
-__global__ void rows_to_pieces_kernel(const float* __restrict__ src, int64_t ld, int col0, float scale, int batch, int Q,
-                                      int ldq, __half* __restrict__ dst) {
+// b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8.  `src` rows are `ld` elements; columns col0 .. col0+127;
+// value = act((src + bias[col]) * scale), act = sigmoid when `sigmoid` (bias may be null).
+template <typename TSrc>
+__global__ void rows_to_pieces_kernel(const TSrc* __restrict__ src, int64_t ld, int col0, const float* __restrict__ bias,
+                                      float scale, int sigmoid, int batch, int Q, int ldq, __half* __restrict__ dst) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 8-channel piece)
   int64_t total = (int64_t)batch * Q * 16;
   if (idx >= total) return;
   int piece = (int)(idx % 16);
   int64_t r = idx / 16;
   int b = (int)(r / Q), q = (int)(r % Q);
-  const float* x = src + r * ld + col0 + piece * 8;
+  const TSrc* x = src + r * ld + col0 + piece * 8;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float t = to_f(x[e]);
+    if (bias) t += bias[col0 + piece * 8 + e];
+    t *= scale;
+    v[e] = sigmoid ? sigmoidf_(t) : t;
+  }
   __half2 h[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(x[2 * e] * scale, x[2 * e + 1] * scale);
+  for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
   __half* out = dst + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
   *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h);
 }
 
-// ... and back: the core's output pieces into columns col0 .. col0+127 of float32 rows of `ld`
+// ... and back: the core's output pieces into columns col0 .. col0+127 of rows of `ld` elements
+template <typename TDst>
 __global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch, int Q, int ldq, int64_t ld, int col0,
-                                      float* __restrict__ dst) {
+                                      TDst* __restrict__ dst) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t total = (int64_t)batch * Q * 16;
   if (idx >= total) return;
@@ -401,10 +412,56 @@ __global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch,
   int b = (int)(r / Q), q = (int)(r % Q);
   const __half* in = src + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
   uint4 raw = *reinterpret_cast<const uint4*>(in);
-  const __half2* h = reinterpret_cast<const __half2*>(&raw);
-  float* out = dst + r * ld + col0 + piece * 8;
+  const __half* h = reinterpret_cast<const __half*>(&raw);
+  TDst* out = dst + r * ld + col0 + piece * 8;
 #pragma unroll
-  for (int e = 0; e < 4; ++e) { float2 f = __half22float2(h[e]); out[2 * e] = f.x; out[2 * e + 1] = f.y; }
+  for (int e = 0; e < 8; ++e) out[e] = from_f<TDst>(__half2float(h[e]));
+}
+
+// Glue of the 16-bit GEMM path (activations x weights on the tensor cores through the contraction kernel).
+// Weights w [K][ldw] float32, columns col0 .. col0+N-1 -> fp16 [N][K] (the GEMM wants k contiguous in both operands)
+__global__ void weight_half_t_kernel(const float* __restrict__ w, int K, int ldw, int col0, int N, __half* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)N * K) return;
+  int n = (int)(idx / K), k = (int)(idx % K);
+  out[idx] = __float2half_rn(w[(int64_t)k * ldw + col0 + n]);
+}
+
+// out[dst(r)][c] = (resid ? resid[dst(r)][c] : 0) + (proj[r][c] * scale + bias[c]) for an fp16 projection
+template <typename TAct>
+__global__ void finish_half_kernel(const __half* __restrict__ proj, float scale, const float* __restrict__ bias,
+                                   const TAct* __restrict__ resid, int64_t rows, int ch, int transpose,
+                                   int batch, int Q, TAct* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t total = rows * ch;
+  if (idx >= total) return;
+  int64_t r = idx / ch;
+  int c = (int)(idx % ch);
+  int64_t dst = r;
+  if (transpose) { int64_t b = r / Q, i = r % Q; dst = i * batch + b; }
+  float v = __half2float(proj[idx]) * scale;
+  if (bias) v += bias[c];
+  if (resid) v += to_f(resid[dst * ch + c]);
+  out[dst * ch + c] = from_f<TAct>(v);
+}
+
+// Transition hidden layer on the fp16 projection h [rows][wide] into out [rows][hidden] (out may be h when wide == hidden):
+//   relu:   out[r][j] = relu(h[r][j] + b[j]), wide = hidden
+//   swiglu: out[r][j] = silu(h[r][j] + b[j]) * (h[r][hidden + j] + b[hidden + j]), wide = 2 hidden
+__global__ void hidden_act_half_kernel(const __half* h, const float* __restrict__ bias, int64_t rows, int hidden, int wide,
+                                       int swiglu, __half* out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * hidden) return;
+  int64_t r = idx / hidden;
+  int j = (int)(idx % hidden);
+  const __half* row = h + r * wide;
+  float g = __half2float(row[j]) + (bias ? bias[j] : 0.f);
+  if (swiglu) {
+    float v = __half2float(row[hidden + j]) + (bias ? bias[hidden + j] : 0.f);
+    out[idx] = __float2half_rn(g * sigmoidf_(g) * v);
+  } else {
+    out[idx] = __float2half_rn(fmaxf(g, 0.f));
+  }
 }
 
 // fp16 pair bias [heads][Q][ld] (rows padded to ld) -> float32 [heads][Q][Q]
@@ -533,6 +590,60 @@ __global__ void mask_rows_half_kernel(const float* __restrict__ a, const float* 
   float m = mask[idx / c];
   a16[idx] = __float2half_rn(a[idx] * m);
   b16[idx] = __float2half_rn(b[idx] * m);
+}
+
+// the fp16 projection lr [rows][2c] (left | right) + biases, masked, into the outer product's operands
+__global__ void opm_split_half_kernel(const __half* __restrict__ lr, const float* __restrict__ bl, const float* __restrict__ br,
+                                      const float* __restrict__ mask, int64_t rows, int c, __half* __restrict__ a16,
+                                      __half* __restrict__ b16) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * c) return;
+  int64_t r = idx / c;
+  int a = (int)(idx % c);
+  float m = mask[r];
+  a16[idx] = __float2half_rn((__half2float(lr[r * 2 * c + a]) + bl[a]) * m);
+  b16[idx] = __float2half_rn((__half2float(lr[r * 2 * c + c + a]) + br[a]) * m);
+}
+
+// outer [(i, a)][(j, b)] (cnt*c rows of N*c) -> per pair [(i, j)][(a, b)], 8 values of b per thread (c % 8 == 0)
+__global__ void opm_regroup_half_kernel(const __half* __restrict__ outer, int cnt, int N, int c, __half* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c8 = c >> 3;
+  int64_t total = (int64_t)cnt * N * c * c8;
+  if (idx >= total) return;
+  int b8 = (int)(idx % c8);
+  int64_t t = idx / c8;
+  int a = (int)(t % c); t /= c;
+  int j = (int)(t % N);
+  int i = (int)(t / N);
+  const uint4 v = *reinterpret_cast<const uint4*>(outer + ((int64_t)i * c + a) * ((int64_t)N * c) + (int64_t)j * c + b8 * 8);
+  *reinterpret_cast<uint4*>(out + idx * 8) = v;
+}
+
+// counts[i][j] = sum_s mask[s][i] mask[s][j]
+__global__ void opm_counts_kernel(const float* __restrict__ mask, int S, int N, float* __restrict__ counts) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)N * N) return;
+  int i = (int)(idx / N), j = (int)(idx % N);
+  float cnt = 0.f;
+  for (int s = 0; s < S; ++s) cnt += mask[(int64_t)s * N + i] * mask[(int64_t)s * N + j];
+  counts[idx] = cnt;
+}
+
+// out[i][j][z] = (proj[(i - i0) N + j][z] * scale + bout[z]) / (eps + counts[i][j]) (+ resid); fp16 projection
+template <typename TAct>
+__global__ void opm_finish_half_kernel(const __half* __restrict__ proj, float scale, const float* __restrict__ bout,
+                                       const float* __restrict__ counts, int N, int cz, int i0, int cnt, float norm_eps,
+                                       const TAct* __restrict__ resid, TAct* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)cnt * N * cz) return;
+  int z = (int)(idx % cz);
+  int64_t pr = idx / cz;                       // (i - i0) * N + j
+  int64_t pair = (int64_t)i0 * N + pr;
+  float v = (__half2float(proj[idx]) * scale + bout[z]) / (norm_eps + counts[pair]);
+  int64_t o = pair * cz + z;
+  if (resid) v += to_f(resid[o]);
+  out[o] = from_f<TAct>(v);
 }
 
 __global__ void mask_rows_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ mask,
