@@ -469,7 +469,29 @@ def main():
         stack3.close()
         extra["n384_af3_ms_per_block"] = float(np.mean(times))
         extra["n384_af3_note"] = "pair part of an AF3 pairformer block at N=384 (the 48-block stack's shape), timed like n384_ms_per_block"
-        del z384, flush
+        del z384
+        # config 1 of the baseline: one whole AF2 Evoformer block (MSA row / column attention, MSA transition, outer
+        # product mean, the five pair updates) at S = 128 sequences, N = 256, c_m = 256, MSA and pair resident
+        msa_h, pair_c1, mm_h, pm_h, w_c1 = syn.af2_evoformer_block(1, S=128, n=256)
+        block_c1 = lf.PreparedMsaBlock(dev, w_c1, 256, C_Z, 32, C_Z)
+        msa_d, pair_c1d = torch.from_numpy(msa_h).cuda(), torch.from_numpy(pair_c1).cuda()
+        mm_d, pm_d = torch.from_numpy(mm_h).cuda(), torch.from_numpy(pm_h).cuda()
+        for name, o in (("evoformer_block_ms", opts), ("evoformer_block_f32_ms", dict(opts, precision="f32"))):
+            times = []
+            for i in range(3 + 6):
+                flush.fill_(i & 0xff)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                block_c1.run(msa_d, pair_c1d, mm_d, pm_d, 128, 256, o)
+                b.record(stream)
+                torch.cuda.synchronize()
+                if i >= 3:
+                    times.append(a.elapsed_time(b))
+            extra[name] = float(np.mean(times))
+        block_c1.close()
+        extra["evoformer_block_note"] = ("one AF2 Evoformer block at S=128, N=256, c_m=256 (the baseline's CPU-runnable configuration), "
+                                         "MSA and pair resident, mean of 6 blocks, L2 flushed between; _f32_ is the float32 SIMT mode")
+        del flush, msa_d, pair_c1d
 
     # end to end through the public API with host buffers: pinned host pair in, pair out, every step
     e2e = None

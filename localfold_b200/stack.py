@@ -128,140 +128,154 @@ class PairStackGpu:
         self.blocks = []
 
 
-class EvoformerBlockGpu:
-    """One whole AF2 Evoformer block (``webgpu/af2/evoformer/block.js:1536-1613,1783-1824``):
-    msa += rowAttention(msa, pair); msa += columnAttention(msa); msa += transition(msa);
-    pair += outerProductMean(msa); then the five pair updates."""
+class PreparedMsaBlock:
+    """Resident weights of one Evoformer or extra-MSA block: the three MSA operators, the outer product mean and
+    the five pair updates (``weights["msaColumnGlobalAttention"]`` makes it an extra-MSA block)."""
 
-    def __init__(self, device=None):
-        self.device = _device(device)
-
-    def run(self, input, options=None):
-        opts = dict(options or {})
-        dev = self.device
-        S, n, cm, cz = (int(input[k]) for k in ("sequences", "length", "cM", "cZ"))
-        co, ch = int(input["cOuter"]), int(input["triangleHidden"])
-        w = input["weights"]
-        msa = np.array(input["msa"], np.float32, copy=True).reshape(S, n, cm)
-        pair = np.array(input["pair"], np.float32, copy=True).reshape(n, n, cz)
-        msa_mask, pair_mask = input["msaMask"], input["pairMask"]
-        elapsed = 0.0
-        launches = 0
+    def __init__(self, device, w, c_m, c_z, c_outer, c_hidden):
+        from .operators import GLOBAL_ATTENTION_ORDER, OPM_WEIGHT_ORDER
+        self.device = device
+        self.dims = (c_m, c_z, c_outer, c_hidden)
         row = w["msaRowAttention"]
-        sub = dict(opts, residual=True)
-        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": S, "queryLength": n,
-                                   "channels": cm, "heads": row["heads"], "weights": row["attention"],
-                                   "pairBias": dict(row["pairBias"], source="separate", activations=pair,
-                                                    channels=cz)}, sub)
-        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        col = w["msaColumnAttention"]
-        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": n, "queryLength": S,
-                                   "channels": cm, "heads": col["heads"], "transpose": True,
-                                   "weights": col["attention"]}, sub)
-        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
+        self.row_heads = int(row["heads"])
+        self.row = prepare_attention_weights(device, row["attention"], c_m, self.row_heads,
+                                             dict(row["pairBias"], source="separate", channels=c_z))
+        self.global_column = "msaColumnGlobalAttention" in w
+        if self.global_column:
+            g = w["msaColumnGlobalAttention"]
+            heads = g.get("heads")
+            if not isinstance(heads, (int, np.integer)) or heads <= 0:
+                raise nat.RangeError("global attention weights.heads must be a positive integer")
+            self.col_heads = int(heads)
+            self.col = PreparedWeights(device, nat.WEIGHTS_GLOBAL_ATTENTION_AF2, {"channels": c_m, "heads": self.col_heads},
+                                       [g[k] for k in GLOBAL_ATTENTION_ORDER])
+        else:
+            col = w["msaColumnAttention"]
+            self.col_heads = int(col["heads"])
+            self.col = prepare_attention_weights(device, col["attention"], c_m, self.col_heads)
         t = w["msaTransition"]
+        self.transition_hidden = np.asarray(t["firstBias"]).size
+        self.transition = PreparedWeights(device, nat.WEIGHTS_TRANSITION_AF2,
+                                          {"channels": c_m, "hidden": self.transition_hidden},
+                                          [t[k] for k in TRANSITION_WEIGHT_ORDER])
+        self.opm = PreparedWeights(device, nat.WEIGHTS_OPM_AF2, {"channels": c_m, "hidden": c_outer, "out_channels": c_z},
+                                   [w["outerProductMean"][k] for k in OPM_WEIGHT_ORDER])
+        self.pair = PairStackGpu(device).prepare([w], c_z, c_hidden)
+
+    def run(self, msa, pair, msa_mask, pair_mask, S, n, opts):
+        """One block in place on the device tensors ``msa`` [S, n, c_m] and ``pair`` [n, n, c_z]; returns its launches."""
+        from .operators import GlobalColumnAttentionGpu
+        dev = self.device
+        cm, cz, co, _ = self.dims
+        sub = dict(opts, residual=True)
+        launches = 0
+        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": S, "queryLength": n, "channels": cm,
+                                   "heads": self.row_heads, "weights": self.row,
+                                   "pairBias": {"source": "separate", "activations": pair, "channels": cz}}, sub, out=msa)
+        launches += r["launches"]
+        if self.global_column:
+            r = GlobalColumnAttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
+                                                   "channels": cm, "weights": self.col}, sub, out=msa)
+        else:
+            r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": n, "queryLength": S, "channels": cm,
+                                       "heads": self.col_heads, "transpose": True, "weights": self.col}, sub, out=msa)
+        launches += r["launches"]
         r = TransitionGpu(dev).run({"activations": msa, "rows": S * n, "channels": cm,
-                                    "hiddenChannels": np.asarray(t["firstBias"]).size, "weights": t}, sub)
-        msa = r["output"].reshape(S, n, cm); elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        r = OuterProductMeanGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
-                                          "cM": cm, "cOuter": co, "cZ": cz, "weights": w["outerProductMean"]},
-                                         sub, out=pair)
-        pair = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        stack = PairStackGpu(dev).prepare([w], cz, ch)
-        try:
-            r = stack.run(pair, pair_mask, opts)
-        finally:
-            dev.synchronize()
-            stack.close()
-        elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        return {"msa": msa, "pair": r["pair"], "elapsedMilliseconds": elapsed, "memory": r["memory"],
-                "launches": launches}
+                                    "hiddenChannels": self.transition_hidden, "weights": self.transition}, sub, out=msa)
+        launches += r["launches"]
+        r = OuterProductMeanGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n, "cM": cm,
+                                          "cOuter": co, "cZ": cz, "weights": self.opm}, sub, out=pair)
+        launches += r["launches"]
+        r = self.pair.run(pair, pair_mask, opts)
+        return launches + r["launches"]
+
+    def close(self):
+        for w in (self.row, self.col, self.transition, self.opm, self.pair):
+            w.close()
 
 
 class EvoformerStackGpu:
     """``EvoformerStackGpu.run(input)`` (``webgpu/af2/evoformer/stack.js:44-110``): the blocks of the main stack
-    one after the other, ``input["blockWeights"]`` one weight object per block; the MSA and the pair of a block
-    are the next block's input.  ``ExtraMsaStackGpu`` is the same loop over extra-MSA blocks."""
-
-    block_class = None      # set below: the block runner of this stack
+    one after the other, ``input["blockWeights"]`` one weight object (or ``PreparedMsaBlock``) per block.  The MSA,
+    the pair and the masks are uploaded once and stay on the device for the whole stack; device tensors given as
+    ``msa`` / ``pair`` are updated in place and returned.  ``ExtraMsaStackGpu`` is the same loop over extra-MSA
+    blocks (``webgpu/af2/evoformer/stack.js:163``), told apart by the weights."""
 
     def __init__(self, device=None):
         self.device = _device(device)
 
     def run(self, input, options=None):
+        import torch
         blocks = input["blockWeights"]
         if len(blocks) == 0:
             raise nat.RangeError("Evoformer stack requires at least one block")
-        runner = self.block_class(self.device)
-        state = dict(input)
-        total = {"elapsedMilliseconds": 0.0, "launches": 0, "memory": {"peakBytes": 0}}
-        for index, w in enumerate(blocks):
-            r = runner.run(dict(state, weights=w), options)
-            state["msa"], state["pair"] = r["msa"], r["pair"]
-            total["elapsedMilliseconds"] += r["elapsedMilliseconds"]
-            total["launches"] += r["launches"]
-            total["memory"]["peakBytes"] = max(total["memory"]["peakBytes"], r["memory"]["peakBytes"])
-            if input.get("onBlockDone"):
-                input["onBlockDone"](index)
-        return dict(total, msa=state["msa"], pair=state["pair"])
+        opts = dict(options or {})
+        dev = self.device
+        S, n, cm, cz = (int(input[k]) for k in ("sequences", "length", "cM", "cZ"))
+        co, ch = int(input["cOuter"]), int(input["triangleHidden"])
+        where = f"cuda:{dev.ordinal}"
+
+        def resident(value, shape, copy):
+            if getattr(value, "is_cuda", False):
+                if value.numel() != int(np.prod(shape)):
+                    raise nat.RangeError(f"tensor has {value.numel()} values; expected {int(np.prod(shape))}")
+                return value.view(shape), True
+            host = np.asarray(value, np.float32)
+            if host.size != int(np.prod(shape)):
+                raise nat.RangeError(f"array has {host.size} values; expected {int(np.prod(shape))}")
+            return torch.from_numpy(np.array(host, np.float32, copy=copy).reshape(shape)).to(where), False
+
+        stream = torch.cuda.ExternalStream(dev.stream, device=where) if dev.stream else torch.cuda.default_stream(where)
+        with torch.cuda.stream(stream):       # uploads, the library's kernels and read-backs share one stream
+            msa, msa_given = resident(input["msa"], (S, n, cm), True)
+            pair, pair_given = resident(input["pair"], (n, n, cz), True)
+            msa_mask, _ = resident(input["msaMask"], (S, n), False)
+            pair_mask, _ = resident(input["pairMask"], (n, n), False)
+            owned = []
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            launches = 0
+            try:
+                prepared = []
+                for w in blocks:
+                    if isinstance(w, PreparedMsaBlock):
+                        prepared.append(w)
+                    else:
+                        prepared.append(PreparedMsaBlock(dev, w, cm, cz, co, ch))
+                        owned.append(prepared[-1])
+                start.record(stream)
+                for index, block in enumerate(prepared):
+                    launches += block.run(msa, pair, msa_mask, pair_mask, S, n, opts)
+                    if input.get("onBlockDone"):
+                        input["onBlockDone"](index)
+                stop.record(stream)
+                dev.synchronize()
+            finally:
+                dev.synchronize()
+                for block in owned:
+                    block.close()
+            return {"msa": msa if msa_given else msa.cpu().numpy(), "pair": pair if pair_given else pair.cpu().numpy(),
+                    "elapsedMilliseconds": float(start.elapsed_time(stop)), "memory": {"peakBytes": 0},
+                    "launches": launches}
 
 
-class ExtraMsaBlockGpu:
+class EvoformerBlockGpu(EvoformerStackGpu):
+    """One whole AF2 Evoformer block (``webgpu/af2/evoformer/block.js:1536-1613,1783-1824``):
+    msa += rowAttention(msa, pair); msa += columnAttention(msa); msa += transition(msa);
+    pair += outerProductMean(msa); then the five pair updates.  ``input["weights"]``: the block's weight object."""
+
+    def run(self, input, options=None):
+        return EvoformerStackGpu.run(self, dict(input, blockWeights=[input["weights"]]), options)
+
+
+class ExtraMsaBlockGpu(EvoformerBlockGpu):
     """One block of the AF2 extra-MSA stack (``encodeExtraMsaBlock``, ``webgpu/af2/evoformer/block.js:1715-1744``):
     msa += rowAttention(msa, pair); msa += globalColumnAttention(msa); msa += transition(msa); then the
     Evoformer pair part (pair += outerProductMean(msa) and the five pair updates).  Same input as
     ``EvoformerBlockGpu`` with ``weights["msaColumnGlobalAttention"]`` in place of the column attention."""
 
-    def __init__(self, device=None):
-        self.device = _device(device)
-
-    def run(self, input, options=None):
-        from .operators import GlobalColumnAttentionGpu
-        opts = dict(options or {})
-        dev = self.device
-        S, n, cm, cz = (int(input[k]) for k in ("sequences", "length", "cM", "cZ"))
-        co, ch = int(input["cOuter"]), int(input["triangleHidden"])
-        w = input["weights"]
-        msa = np.array(input["msa"], np.float32, copy=True).reshape(S, n, cm)
-        pair = np.array(input["pair"], np.float32, copy=True).reshape(n, n, cz)
-        msa_mask, pair_mask = input["msaMask"], input["pairMask"]
-        elapsed = 0.0
-        launches = 0
-        row = w["msaRowAttention"]
-        sub = dict(opts, residual=True)
-        r = AttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "batch": S, "queryLength": n,
-                                   "channels": cm, "heads": row["heads"], "weights": row["attention"],
-                                   "pairBias": dict(row["pairBias"], source="separate", activations=pair,
-                                                    channels=cz)}, sub)
-        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        r = GlobalColumnAttentionGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
-                                               "channels": cm, "weights": w["msaColumnGlobalAttention"]}, sub)
-        msa = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        t = w["msaTransition"]
-        r = TransitionGpu(dev).run({"activations": msa, "rows": S * n, "channels": cm,
-                                    "hiddenChannels": np.asarray(t["firstBias"]).size, "weights": t}, sub)
-        msa = r["output"].reshape(S, n, cm); elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        r = OuterProductMeanGpu(dev).run({"activations": msa, "mask": msa_mask, "sequences": S, "length": n,
-                                          "cM": cm, "cOuter": co, "cZ": cz, "weights": w["outerProductMean"]},
-                                         sub, out=pair)
-        pair = r["output"]; elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        stack = PairStackGpu(dev).prepare([w], cz, ch)
-        try:
-            r = stack.run(pair, pair_mask, opts)
-        finally:
-            dev.synchronize()
-            stack.close()
-        elapsed += r["elapsedMilliseconds"]; launches += r["launches"]
-        return {"msa": msa, "pair": r["pair"], "elapsedMilliseconds": elapsed, "memory": r["memory"],
-                "launches": launches}
-
 
 class ExtraMsaStackGpu(EvoformerStackGpu):
     """The extra-MSA stack (``encodeExtraMsaBlock`` per block, ``webgpu/af2/evoformer/stack.js:163``)."""
-    block_class = ExtraMsaBlockGpu
-
-
-EvoformerStackGpu.block_class = EvoformerBlockGpu
 
 
 class Af3PairformerStackGpu:
