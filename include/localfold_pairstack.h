@@ -323,6 +323,8 @@ typedef struct lf_opm_desc {
   const float* mask;           /* [sequences, length] */
   void* out;                   /* pair */
   const lf_weights* weights;
+  int32_t bias_after_norm;     /* 0: (sum + bias) / (epsilon + count); 1: sum / max(count, 1) + bias, the
+                                * dialect key opmBiasAfterNorm (cpu/af3/trunk/msa.js:81,141-150) */
 } lf_opm_desc;
 LF_API lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_result* r);
 

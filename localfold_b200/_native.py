@@ -72,7 +72,7 @@ class OpmDesc(ctypes.Structure):
                 ("c_z", c_int32), ("variance", c_int32), ("precision", c_int32), ("residual", c_int32),
                 ("layer_norm_epsilon", c_float), ("normalization_epsilon", c_float), ("space", c_int32),
                 ("act_dtype", c_int32), ("activations", c_void_p), ("mask", c_void_p), ("out", c_void_p),
-                ("weights", c_void_p)]
+                ("weights", c_void_p), ("bias_after_norm", c_int32)]
 
 
 class SingleAttentionDesc(ctypes.Structure):

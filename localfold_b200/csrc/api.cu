@@ -1286,6 +1286,7 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
       }
     } else { out = d->out; resid = d->residual ? d->out : nullptr; }
     const auto& f = w->f;
+    const int ban = d->bias_after_norm ? 1 : 0;
     // 16-bit mode, widths in whole groups of 8: every GEMM of the operator runs on the tensor cores
     const bool tc_full = d->precision == LF_PRECISION_BF16 && c % 8 == 0 && hgemm_supported(cm, c * c);
     float* nrm = tc_full ? nullptr : cur.take<float>(rows * cm);
@@ -1329,10 +1330,10 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
         LF_TRY(hgemm(ctx, cur, grouped, wout, proj16, (int64_t)cnt * N, cz, c * c));
         if (d->act_dtype == LF_DTYPE_BF16)
           LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<bf16>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
-                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, (const bf16*)resid, (bf16*)out);
+                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, ban, (const bf16*)resid, (bf16*)out);
         else
           LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<float>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
-                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, (const float*)resid, (float*)out);
+                 f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, ban, (const float*)resid, (float*)out);
       }
       st.flush();
       return LF_OK;
@@ -1356,20 +1357,20 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
                                  (int64_t)cnt * c * N * c, 0, 1, 1, outer_scale));
         if (d->act_dtype == LF_DTYPE_BF16)
           LAUNCH(ctx, cur, (simt::opm_output_kernel<bf16, JT, op16>), grid, 128, smem, outer16, 1.0f / outer_scale, f[OPM_WOUT], f[OPM_BOUT],
-                 mask, S, N, c, cz, i0, d->normalization_epsilon, 0, (const bf16*)resid, (bf16*)out);
+                 mask, S, N, c, cz, i0, d->normalization_epsilon, ban, (const bf16*)resid, (bf16*)out);
         else
           LAUNCH(ctx, cur, (simt::opm_output_kernel<float, JT, op16>), grid, 128, smem, outer16, 1.0f / outer_scale, f[OPM_WOUT], f[OPM_BOUT],
-                 mask, S, N, c, cz, i0, d->normalization_epsilon, 0, (const float*)resid, (float*)out);
+                 mask, S, N, c, cz, i0, d->normalization_epsilon, ban, (const float*)resid, (float*)out);
         continue;
       }
       sgemm(ctx, cur, true, false, 0, cnt * c, N * c, S, left + (int64_t)i0 * c, (int64_t)N * c, 0, right, (int64_t)N * c, 0,
             outer, (int64_t)N * c, 0, nullptr, 0, 1);
       if (d->act_dtype == LF_DTYPE_BF16)
         LAUNCH(ctx, cur, (simt::opm_output_kernel<bf16, JT, float>), grid, 128, smem, outer, 1.0f, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
-               i0, d->normalization_epsilon, 0, (const bf16*)resid, (bf16*)out);
+               i0, d->normalization_epsilon, ban, (const bf16*)resid, (bf16*)out);
       else
         LAUNCH(ctx, cur, (simt::opm_output_kernel<float, JT, float>), grid, 128, smem, outer, 1.0f, f[OPM_WOUT], f[OPM_BOUT], mask, S, N, c, cz,
-               i0, d->normalization_epsilon, 0, (const float*)resid, (float*)out);
+               i0, d->normalization_epsilon, ban, (const float*)resid, (float*)out);
     }
     st.flush();
     return LF_OK;

@@ -630,17 +630,20 @@ __global__ void opm_counts_kernel(const float* __restrict__ mask, int S, int N, 
   counts[idx] = cnt;
 }
 
-// out[i][j][z] = (proj[(i - i0) N + j][z] * scale + bout[z]) / (eps + counts[i][j]) (+ resid); fp16 projection
+// out[i][j][z] = (proj[(i - i0) N + j][z] * scale + bout[z]) / (eps + counts[i][j]) (+ resid), or with the bias after
+// the division by max(count, 1); fp16 projection
 template <typename TAct>
 __global__ void opm_finish_half_kernel(const __half* __restrict__ proj, float scale, const float* __restrict__ bout,
                                        const float* __restrict__ counts, int N, int cz, int i0, int cnt, float norm_eps,
-                                       const TAct* __restrict__ resid, TAct* __restrict__ out) {
+                                       int bias_after_norm, const TAct* __restrict__ resid, TAct* __restrict__ out) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)cnt * N * cz) return;
   int z = (int)(idx % cz);
   int64_t pr = idx / cz;                       // (i - i0) * N + j
   int64_t pair = (int64_t)i0 * N + pr;
-  float v = (__half2float(proj[idx]) * scale + bout[z]) / (norm_eps + counts[pair]);
+  float v = __half2float(proj[idx]) * scale;
+  if (bias_after_norm) v = v / fmaxf(counts[pair], 1.0f) + bout[z];
+  else v = (v + bout[z]) / (norm_eps + counts[pair]);
   int64_t o = pair * cz + z;
   if (resid) v += to_f(resid[o]);
   out[o] = from_f<TAct>(v);

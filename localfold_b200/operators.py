@@ -600,7 +600,8 @@ class Af3TransitionGpu:
 
 
 class OuterProductMeanGpu:
-    """``OuterProductMeanGpu`` (``webgpu/kernels/outer-product-mean.js:1748``)."""
+    """``OuterProductMeanGpu`` (``webgpu/kernels/outer-product-mean.js:1748``).  ``input["biasAfterNorm"]`` selects the
+    form of the dialect key ``opmBiasAfterNorm``: sum / max(count, 1) + bias (``cpu/af3/trunk/msa.js:141-150``)."""
 
     def __init__(self, device: Device | None = None):
         self.device = _device(device)
@@ -635,7 +636,7 @@ class OuterProductMeanGpu:
                                float(input.get("layerNormEpsilon") or 1e-5),
                                float(input.get("normalizationEpsilon") or 1e-3),
                                nat.SPACE_DEVICE if act.is_device else nat.SPACE_HOST, obuf.dtype,
-                               act.ptr, mask.ptr, obuf.ptr, w.handle)
+                               act.ptr, mask.ptr, obuf.ptr, w.handle, 1 if input.get("biasAfterNorm") else 0)
             res = nat.Result()
             dev.check(dev.lib.lf_outer_product_mean_run(dev.handle, ctypes.byref(desc), ctypes.byref(res)))
             return _result(dev, res, output)

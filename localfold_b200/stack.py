@@ -372,7 +372,8 @@ class Af3MsaStackGpu:
     """``Af3MsaStackGpu.run(state, blocks, dialect, options)`` (``webgpu/af3/trunk/msa-stack.js:67-89``): the
     blocks of the AF3 MSA stack, each ``msaBlock`` (``cpu/af3/trunk/msa.js:235-287``) - the outer product mean
     into the pair and the MSA update (pair-weighted averaging, then the MSA transition) in the order
-    ``dialect["msaUpdateBeforeOuterProduct"]`` names (it has no default), followed by the five pair updates.
+    ``dialect["msaUpdateBeforeOuterProduct"]`` names (it has no default), followed by the five pair updates;
+    ``dialect["opmBiasAfterNorm"]`` moves the outer product's output bias behind the division by the coverage.
     ``state = {msa, pair, msaMask, pairMask, sequences, tokens}``; host arrays are uploaded once, the MSA and the
     pair stay on the device for the whole stack and are read back once; CUDA tensors are updated in place and
     returned (``options["keepPair"]`` returns the device tensors as ``pairTensor`` / ``msaTensor`` either way, the
@@ -389,8 +390,6 @@ class Af3MsaStackGpu:
         if dialect.get("msaUpdateBeforeOuterProduct") not in (True, False):
             raise ValueError("dialect.msaUpdateBeforeOuterProduct has no default: AF3 takes the outer product off "
                              "the pre-update MSA and OpenDDE off the updated one")
-        if dialect.get("outerProductBiasAfterNorm"):
-            raise NotImplementedError("the bias-after-normalisation form of the outer product mean is not built")
         if len(blocks) == 0:
             raise nat.RangeError("the MSA stack requires at least one block")
         opts = dict(options or {})
@@ -441,7 +440,8 @@ class Af3MsaStackGpu:
                 for b, (co, opm_w, att_w, trn_w) in enumerate(prepared):
                     def outer_product():
                         return OuterProductMeanGpu(dev).run({"sequences": S, "length": n, "cM": cm, "cOuter": co, "cZ": cz,
-                                                             "activations": msa, "mask": msa_mask, "weights": opm_w},
+                                                             "activations": msa, "mask": msa_mask, "weights": opm_w,
+                                                             "biasAfterNorm": bool(dialect.get("opmBiasAfterNorm"))},
                                                             dict(sub, variance="fast"), out=pair)["launches"]
 
                     def update_msa():

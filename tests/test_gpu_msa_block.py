@@ -91,6 +91,27 @@ def test_msa_block_16_bit_pair_path(dev):
     assert e_pair <= 2e-3 and e_msa <= 2e-3
 
 
+@pytest.mark.parametrize("precision,tol", [("f32", F32_TOL), ("bf16", 2e-3)])
+def test_msa_block_bias_after_norm(dev, precision, tol):
+    """The dialect key ``opmBiasAfterNorm``: sum / max(count, 1) + bias (``cpu/af3/trunk/msa.js:141-150``); the two
+    forms differ by about (1 - 1/count) * bias on every pair, far above either bound."""
+    import localfold_b200 as lf
+    from parity_report import record
+    S, n = 12, 48
+    msa, pair, mm, pm, w = syn.af3_msa_block(43, S=S, n=n)
+    assert np.abs(np.asarray(w["outerProductMean"]["outputB"])).max() > 0
+    dialect = {"swapTransposedBias": False, "msaUpdateBeforeOuterProduct": False, "opmBiasAfterNorm": True}
+    got = lf.Af3MsaBlockGpu(dev).run({"msa": msa, "pair": pair, "msaMask": mm, "pairMask": pm, "sequences": S, "tokens": n},
+                                     w, dialect, {"precision": precision})
+    want_msa, want_pair = oracle.msa_block_af3(msa, pair, mm, pm, w, False, False, bias_after_norm=True)
+    _, other_pair = oracle.msa_block_af3(msa, pair, mm, pm, w, False, False, bias_after_norm=False)
+    assert oracle.relative_l2(other_pair, want_pair) > 10 * tol      # the option is visible on this input
+    e_msa, e_pair = oracle.relative_l2(got["msa"], want_msa), oracle.relative_l2(got["pair"], want_pair)
+    record("msa_block_af3", f"S={S} n={n} {precision} bias after norm msa", e_msa, tol)
+    record("msa_block_af3", f"S={S} n={n} {precision} bias after norm pair", e_pair, tol)
+    assert e_msa <= tol and e_pair <= tol
+
+
 def test_msa_block_needs_its_dialect(dev):
     import localfold_b200 as lf
     msa, pair, mm, pm, w = syn.af3_msa_block(42, S=2, n=16)
