@@ -966,19 +966,18 @@ lf_status att_bf16(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
 
 // 16-bit GEMM on the tensor cores for activations of any width: out[m][n] = sum_k a[m][k] w[n][k], fp16 operands
 // with k contiguous, float32 accumulation, fp16 result (the triangle contraction's kernel on one plane).
-lf_status hgemm(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* w, op16* out, int64_t M, int N, int K) {
+lf_status hgemm(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* w, op16* out, int64_t M, int N, int K,
+                const float* bias = nullptr, int relu = 0) {
   if (M > 0x7fffffff) return lf_fail(ctx, LF_ERR_SHAPE, "too many rows for one projection");
-  return tc::contract_rect(ctx, cur, a, w, out, (int)M, N, K, K, N, 0, 0, 1, 0, 1.0f);
+  return tc::contract_gemm(ctx, cur, a, w, out, (int)M, N, K, bias, relu);
 }
 
-// columns col0 .. col0+N-1 of float32 weights [K][ldw] as the fp16 [N][K] operand of hgemm
-op16* weight_operand(lf_context* ctx, ArenaCursor& cur, const float* w, int K, int ldw, int col0, int N) {
-  op16* t = cur.take<op16>((int64_t)N * K);
-  LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)N * K, 256), 256, 0, w, K, ldw, col0, N, t);
-  return t;
+// the weights' fp16 [n_out][k] GEMM operands, made when the weights were prepared (null: none for this width)
+const op16* gemm_operand(const lf_weights* w, int slot) {
+  return slot < (int)w->g.size() ? (const op16*)w->g[slot] : nullptr;
 }
 
-bool hgemm_supported(int k1, int k2) { return k1 % 8 == 0 && k2 % 8 == 0 && tc::contract_supported(1, 1); }
+bool hgemm_supported(const lf_weights* w) { return gemm_operand(w, 0) && gemm_operand(w, 1) && tc::contract_supported(1, 1); }
 
 // 16-bit path for the shapes the fused projection kernel does not take (MSA row attention with pair bias: c_m = 256,
 // 8 heads of 32; MSA column attention): LayerNorm to fp16, the q/k/v/gate projection as one tensor-core GEMM, the
@@ -995,15 +994,14 @@ lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   op16* qkvg = cur.take<op16>(R * 4 * HD);
   op16* o = cur.take<op16>(R * HD);
   op16* bias16 = a.bias_mode ? cur.take<op16>((int64_t)a.heads * a.Q * ldb) : nullptr;
-  op16* q16 = cur.take<op16>(RP * 128);
-  op16* k16 = cur.take<op16>(RP * 128);
-  op16* v16 = cur.take<op16>(RP * 128);
-  op16* g16 = cur.take<op16>(RP * 128);
+  op16* q16 = cur.take<op16>(4 * RP * 128);      // q | k | v | gate of one group of four heads
+  op16* k16 = q16 + RP * 128;
+  op16* v16 = k16 + RP * 128;
+  op16* g16 = v16 + RP * 128;
   op16* o16 = cur.take<op16>(RP * 128);
   LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16>), lf_ceil_div(R, 8), 256, 0, (const T*)a.act, R, c, f[ATT_LN_G],
          f[ATT_LN_B], a.eps, a.variance, a.transpose, a.batch, a.Q, nrm);
-  op16* w4 = weight_operand(ctx, cur, f[ATT_W4], c, 4 * HD, 0, 4 * HD);
-  LF_TRY(hgemm(ctx, cur, nrm, w4, qkvg, R, 4 * HD, c));
+  LF_TRY(hgemm(ctx, cur, nrm, gemm_operand(a.w, 0), qkvg, R, 4 * HD, c));
   if (ldb != a.Q && !cur.dry) {
     // padding rows and columns are read as keys past the end (masked out): they must hold finite values
     if (bias16) cudaMemsetAsync(bias16, 0, (size_t)a.heads * a.Q * ldb * sizeof(op16), ctx->stream);
@@ -1012,22 +1010,18 @@ lf_status att_mixed(lf_context* ctx, ArenaCursor& cur, const AttArgs& a) {
   }
   if (a.bias_mode == 1)
     LF_TRY(tc::pair_bias_project(ctx, cur, a.pair, a.pair_dtype, a.Q, a.pair_variance, a.pair_eps, a.heads, a.w, bias16, ldb));
-  const int64_t pieces = R * 16;
+  const int64_t pieces = (int64_t)a.batch * ((a.Q + 7) / 8) * 128;      // threads of the repack kernels
   const float qscale = 1.0f / sqrtf((float)a.d);
-  const int64_t ld4 = (int64_t)4 * HD;
   for (int gi = 0; gi < groups; ++gi) {
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 0 * HD + gi * 128, f[ATT_B4], qscale, 0, a.batch, a.Q, ldb, q16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 1 * HD + gi * 128, f[ATT_B4], 1.0f, 0, a.batch, a.Q, ldb, k16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 2 * HD + gi * 128, f[ATT_B4], 1.0f, 0, a.batch, a.Q, ldb, v16);
-    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, qkvg, ld4, 3 * HD + gi * 128, f[ATT_B4], 1.0f, 1, a.batch, a.Q, ldb, g16);
+    LAUNCH(ctx, cur, simt::rows_to_pieces_kernel<op16>, dim3((unsigned)lf_ceil_div(pieces, 256), 4), 256, 0, qkvg, HD, gi, f[ATT_B4], qscale,
+           a.batch, a.Q, ldb, q16, RP * 128);
     LF_TRY(tc::attention_core(ctx, cur, q16, k16, v16, g16, bias16 ? bias16 + (int64_t)gi * 4 * a.Q * ldb : nullptr, ldb, a.mask, a.batch,
                               a.Q, a.transpose, a.mask_mode, a.clamp, o16));
     LAUNCH(ctx, cur, simt::pieces_to_rows_kernel<op16>, lf_ceil_div(pieces, 256), 256, 0, o16, a.batch, a.Q, ldb, (int64_t)HD, gi * 128, o);
   }
-  op16* wo = weight_operand(ctx, cur, f[ATT_WO], HD, c, 0, c);
   op16* proj = nrm;   // the normalised input is dead
-  LF_TRY(hgemm(ctx, cur, o, wo, proj, R, c, HD));
-  LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(R * c, 256), 256, 0, proj, 1.0f, f[ATT_BO],
+  LF_TRY(hgemm(ctx, cur, o, gemm_operand(a.w, 1), proj, R, c, HD));
+  LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(R * c / 8, 256), 256, 0, proj, 1.0f, f[ATT_BO],
          a.residual ? (const T*)a.act : (const T*)nullptr, R, c, a.transpose, a.batch, a.Q, (T*)a.out);
   return LF_OK;
 }
@@ -1036,7 +1030,7 @@ lf_status att_dispatch(lf_context* ctx, ArenaCursor& cur, const AttArgs& a, int 
   if (precision == LF_PRECISION_BF16 && a.bias_mode != 1 && a.heads == 4 && a.d == 32 && tc::ln_gemm_supported(a.w)) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_bf16<bf16>(ctx, cur, a) : att_bf16<float>(ctx, cur, a);
   }
-  if (precision == LF_PRECISION_BF16 && a.d == 32 && a.heads % 4 == 0 && hgemm_supported(a.ch, a.heads * a.d) &&
+  if (precision == LF_PRECISION_BF16 && a.d == 32 && a.heads % 4 == 0 && hgemm_supported(a.w) &&
       (a.bias_mode == 0 || (a.bias_mode == 1 && tc::pair_bias_supported(a.w) && !a.bias_swap))) {
     return a.act_dtype == LF_DTYPE_BF16 ? att_mixed<bf16>(ctx, cur, a) : att_mixed<float>(ctx, cur, a);
   }
@@ -1086,18 +1080,22 @@ lf_status trn_half(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
   op16* nrm = cur.take<op16>(chunk * c);
   op16* h1 = cur.take<op16>(chunk * wide);
   op16* h2 = a.swiglu ? cur.take<op16>(chunk * hd) : h1;
-  op16* w1 = weight_operand(ctx, cur, f[TRN_W1], c, wide, 0, wide);
-  op16* w2 = weight_operand(ctx, cur, f[TRN_W2], hd, c, 0, c);
+  const op16* w1 = gemm_operand(a.w, 0);
+  const op16* w2 = gemm_operand(a.w, 1);
   for (int64_t r0 = 0; r0 < a.rows; r0 += chunk) {
     int64_t rows = a.rows - r0 < chunk ? a.rows - r0 : chunk;
     const T* in = (const T*)a.act + r0 * c;
     T* out = (T*)a.out + r0 * c;
     LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16>), lf_ceil_div(rows, 8), 256, 0, in, rows, c, f[TRN_LN_G], f[TRN_LN_B],
            a.eps, a.variance, 0, 1, 1, nrm);
-    LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c));
-    LAUNCH(ctx, cur, simt::hidden_act_half_kernel, lf_ceil_div(rows * hd, 256), 256, 0, h1, f[TRN_B1], rows, hd, wide, a.swiglu, h2);
+    if (a.swiglu) {
+      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c));
+      LAUNCH(ctx, cur, simt::hidden_act_half_kernel, lf_ceil_div(rows * hd, 256), 256, 0, h1, f[TRN_B1], rows, hd, wide, 1, h2);
+    } else {
+      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c, f[TRN_B1], 1));     // bias and ReLU in the GEMM's epilogue
+    }
     LF_TRY(hgemm(ctx, cur, h2, w2, nrm, rows, c, hd));
-    LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(rows * c, 256), 256, 0, nrm, 1.0f, f[TRN_B2],
+    LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(rows * c / 8, 256), 256, 0, nrm, 1.0f, f[TRN_B2],
            a.residual ? in : (const T*)nullptr, rows, c, 0, 1, 1, out);
   }
   return LF_OK;
@@ -1106,7 +1104,7 @@ lf_status trn_half(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
 lf_status trn_dispatch(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a, int precision) {
   if (precision == LF_PRECISION_BF16 && tc::transition_supported(a.w))
     return tc::transition_run(ctx, cur, a.act, a.act_dtype, a.rows, a.variance, a.eps, a.w, a.residual ? a.act : nullptr, a.out);
-  if (precision == LF_PRECISION_BF16 && hgemm_supported(a.ch, a.hidden))
+  if (precision == LF_PRECISION_BF16 && hgemm_supported(a.w))
     return a.act_dtype == LF_DTYPE_BF16 ? trn_half<bf16>(ctx, cur, a) : trn_half<float>(ctx, cur, a);
   if (a.act_dtype == LF_DTYPE_BF16) trn_f32<bf16>(ctx, cur, a); else trn_f32<float>(ctx, cur, a);
   return LF_OK;
@@ -1288,7 +1286,7 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
     const auto& f = w->f;
     const int ban = d->bias_after_norm ? 1 : 0;
     // 16-bit mode, widths in whole groups of 8: every GEMM of the operator runs on the tensor cores
-    const bool tc_full = d->precision == LF_PRECISION_BF16 && c % 8 == 0 && hgemm_supported(cm, c * c);
+    const bool tc_full = d->precision == LF_PRECISION_BF16 && c % 8 == 0 && hgemm_supported(w);
     float* nrm = tc_full ? nullptr : cur.take<float>(rows * cm);
     float* left = tc_full ? nullptr : cur.take<float>(rows * c);
     float* right = tc_full ? nullptr : cur.take<float>(rows * c);
@@ -1307,32 +1305,27 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
     op16* right16 = tc_outer ? cur.take<op16>(rows * c) : nullptr;
     if (tc_full) {
       // LayerNorm to fp16, left | right projection as one GEMM; then per chunk of output rows the outer product
-      // summed over the sequences (GEMM over s), regrouped per pair, projected onto c_z (GEMM over (a, b))
+      // summed over the sequences (GEMM over s, stored grouped per pair), projected onto c_z (GEMM over (a, b))
       op16* nrm16 = cur.take<op16>(rows * cm);
       op16* lr16 = cur.take<op16>(rows * 2 * c);
-      op16* wlr = cur.take<op16>((int64_t)2 * c * cm);
-      op16* grouped = cur.take<op16>((int64_t)ni * N * c * c);
+      const op16* wlr = gemm_operand(w, 0);
+      const op16* wout = gemm_operand(w, 1);
       op16* proj16 = cur.take<op16>((int64_t)ni * N * cz);
       float* counts = cur.take<float>((int64_t)N * N);
       LAUNCH(ctx, cur, (simt::layer_norm_kernel<float, op16>), lf_ceil_div(rows, 8), 256, 0, msa, rows, cm, f[OPM_LN_G], f[OPM_LN_B],
              d->layer_norm_epsilon, d->variance, 0, 1, 1, nrm16);
-      LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)c * cm, 256), 256, 0, f[OPM_WL], cm, c, 0, c, wlr);
-      LAUNCH(ctx, cur, simt::weight_half_t_kernel, lf_ceil_div((int64_t)c * cm, 256), 256, 0, f[OPM_WR], cm, c, 0, c, wlr + (int64_t)c * cm);
       LF_TRY(hgemm(ctx, cur, nrm16, wlr, lr16, rows, 2 * c, cm));
       LAUNCH(ctx, cur, simt::opm_split_half_kernel, lf_ceil_div(rows * c, 256), 256, 0, lr16, f[OPM_BL], f[OPM_BR], mask, rows, c, left16, right16);
       LAUNCH(ctx, cur, simt::opm_counts_kernel, lf_ceil_div((int64_t)N * N, 256), 256, 0, mask, S, N, counts);
-      op16* wout = weight_operand(ctx, cur, f[OPM_WOUT], c * c, cz, 0, cz);
       for (int i0 = 0; i0 < N; i0 += ni) {
         int cnt = N - i0 < ni ? N - i0 : ni;
-        LF_TRY(tc::contract_rect(ctx, cur, right16, left16 + (int64_t)i0 * c, outer16, cnt * c, N * c, S, N * c, N * c,
-                                 (int64_t)cnt * c * N * c, 0, 1, 1, outer_scale));
-        LAUNCH(ctx, cur, simt::opm_regroup_half_kernel, lf_ceil_div((int64_t)cnt * N * c * (c / 8), 256), 256, 0, outer16, cnt, N, c, grouped);
-        LF_TRY(hgemm(ctx, cur, grouped, wout, proj16, (int64_t)cnt * N, cz, c * c));
+        LF_TRY(tc::contract_outer(ctx, cur, left16 + (int64_t)i0 * c, right16, outer16, cnt, N, c, S, outer_scale));
+        LF_TRY(hgemm(ctx, cur, outer16, wout, proj16, (int64_t)cnt * N, cz, c * c));
         if (d->act_dtype == LF_DTYPE_BF16)
-          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<bf16>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
+          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<bf16>), lf_ceil_div((int64_t)cnt * N * (cz / 8), 256), 256, 0, proj16, 1.0f / outer_scale,
                  f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, ban, (const bf16*)resid, (bf16*)out);
         else
-          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<float>), lf_ceil_div((int64_t)cnt * N * cz, 256), 256, 0, proj16, 1.0f / outer_scale,
+          LAUNCH(ctx, cur, (simt::opm_finish_half_kernel<float>), lf_ceil_div((int64_t)cnt * N * (cz / 8), 256), 256, 0, proj16, 1.0f / outer_scale,
                  f[OPM_BOUT], counts, N, cz, i0, cnt, d->normalization_epsilon, ban, (const float*)resid, (float*)out);
       }
       st.flush();

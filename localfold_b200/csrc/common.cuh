@@ -72,6 +72,7 @@ struct lf_weights {
   lf_weight_dims dims{};
   std::vector<float*> f;     // named by the per-kind enums in weights.cuh
   std::vector<void*> h;      // fp16 repacks (tensor-core path)
+  std::vector<void*> g;      // fp16 [n_out][k] operands of the plain tensor-core GEMM (widths the fused kernels do not take)
   std::vector<void*> owned;  // every device allocation, for destroy
   int bias_flags = 0;        // per 128-column group of the fused projection: bias is non-zero
   bool has_gate_bias = false, has_out_bias = false, has_pair_norm = false, has_pair_proj = false;

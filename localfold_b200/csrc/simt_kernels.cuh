@@ -27,6 +27,27 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
 
+// o[0..7] = v[0..7] (+ r[0..7] when r is given): 16-byte accesses for float32 activations
+template <typename TAct>
+__device__ __forceinline__ void add_store8(float (&v)[8], const TAct* r, TAct* o) {
+  if (sizeof(TAct) == 4) {
+    if (r) {
+      const float4 r0 = *reinterpret_cast<const float4*>(r), r1 = *reinterpret_cast<const float4*>(r + 4);
+      v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+      v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+    }
+    *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    if (r) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += to_f(r[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = from_f<TAct>(v[e]);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // LayerNorm over the last axis, one warp per row.  `rows` logical rows; logical
 // row r = b*Q + i reads memory row i*batch + b when `transpose` (batch, Q > 0).
@@ -373,30 +394,37 @@ __global__ void global_gate_kernel(const float* __restrict__ kvg, int ld, int ga
 
 // Attention activations between the projections and the tensor-core attention core: 128 channels (four
 // heads of 32) of logical rows (b, q) as fp16 8-row x 8-channel pieces, element (b, q, c) at
-// b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8.  `src` rows are `ld` elements; columns col0 .. col0+127;
-// value = act((src + bias[col]) * scale), act = sigmoid when `sigmoid` (bias may be null).
+// b*ldq*128 + (q/8)*1024 + (c/8)*64 + (q%8)*8 + c%8.  `src` rows hold q | k | v | gate, HD columns each;
+// blockIdx.y = which of the four, written to dst + blockIdx.y * kind_stride from columns kind*HD + group*128 ..;
+// value = (src + bias[col]) (bias may be null), times qscale for the query, through a sigmoid for the gate.
 template <typename TSrc>
-__global__ void rows_to_pieces_kernel(const TSrc* __restrict__ src, int64_t ld, int col0, const float* __restrict__ bias,
-                                      float scale, int sigmoid, int batch, int Q, int ldq, __half* __restrict__ dst) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per (row, 8-channel piece)
-  int64_t total = (int64_t)batch * Q * 16;
-  if (idx >= total) return;
-  int piece = (int)(idx % 16);
-  int64_t r = idx / 16;
-  int b = (int)(r / Q), q = (int)(r % Q);
-  const TSrc* x = src + r * ld + col0 + piece * 8;
+__global__ void rows_to_pieces_kernel(const TSrc* __restrict__ src, int HD, int group, const float* __restrict__ bias,
+                                      float qscale, int batch, int Q, int ldq, __half* __restrict__ dst, int64_t kind_stride) {
+  // one thread per (row, 8-channel piece); a warp takes 8 rows x 4 pieces, which it writes as 512 contiguous bytes
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int q8 = (Q + 7) >> 3;
+  if (idx >= (int64_t)batch * q8 * 128) return;
+  const int kind = blockIdx.y;
+  const int col0 = kind * HD + group * 128;
+  const float scale = kind == 0 ? qscale : 1.0f;
+  const int piece = (int)((idx >> 3) & 15);
+  const int64_t rg = idx >> 7;
+  const int b = (int)(rg / q8), q = (int)(rg % q8) * 8 + (int)(idx & 7);
+  if (q >= Q) return;
+  const int64_t r = (int64_t)b * Q + q;
+  const TSrc* x = src + r * 4 * HD + col0 + piece * 8;
   float v[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     float t = to_f(x[e]);
     if (bias) t += bias[col0 + piece * 8 + e];
     t *= scale;
-    v[e] = sigmoid ? sigmoidf_(t) : t;
+    v[e] = kind == 3 ? sigmoidf_(t) : t;
   }
   __half2 h[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-  __half* out = dst + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
+  __half* out = dst + kind * kind_stride + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
   *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h);
 }
 
@@ -404,12 +432,14 @@ __global__ void rows_to_pieces_kernel(const TSrc* __restrict__ src, int64_t ld, 
 template <typename TDst>
 __global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch, int Q, int ldq, int64_t ld, int col0,
                                       TDst* __restrict__ dst) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  int64_t total = (int64_t)batch * Q * 16;
-  if (idx >= total) return;
-  int piece = (int)(idx % 16);
-  int64_t r = idx / 16;
-  int b = (int)(r / Q), q = (int)(r % Q);
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // the thread order of rows_to_pieces_kernel
+  const int q8 = (Q + 7) >> 3;
+  if (idx >= (int64_t)batch * q8 * 128) return;
+  const int piece = (int)((idx >> 3) & 15);
+  const int64_t rg = idx >> 7;
+  const int b = (int)(rg / q8), q = (int)(rg % q8) * 8 + (int)(idx & 7);
+  if (q >= Q) return;
+  const int64_t r = (int64_t)b * Q + q;
   const __half* in = src + (int64_t)b * ldq * 128 + (int64_t)(q >> 3) * 1024 + piece * 64 + (q & 7) * 8;
   uint4 raw = *reinterpret_cast<const uint4*>(in);
   const __half* h = reinterpret_cast<const __half*>(&raw);
@@ -419,30 +449,27 @@ __global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch,
 }
 
 // Glue of the 16-bit GEMM path (activations x weights on the tensor cores through the contraction kernel).
-// Weights w [K][ldw] float32, columns col0 .. col0+N-1 -> fp16 [N][K] (the GEMM wants k contiguous in both operands)
-__global__ void weight_half_t_kernel(const float* __restrict__ w, int K, int ldw, int col0, int N, __half* __restrict__ out) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)N * K) return;
-  int n = (int)(idx / K), k = (int)(idx % K);
-  out[idx] = __float2half_rn(w[(int64_t)k * ldw + col0 + n]);
-}
-
-// out[dst(r)][c] = (resid ? resid[dst(r)][c] : 0) + (proj[r][c] * scale + bias[c]) for an fp16 projection
+// out[dst(r)][c] = (resid ? resid[dst(r)][c] : 0) + (proj[r][c] * scale + bias[c]) for an fp16 projection;
+// eight channels per thread (ch a multiple of 8)
 template <typename TAct>
 __global__ void finish_half_kernel(const __half* __restrict__ proj, float scale, const float* __restrict__ bias,
                                    const TAct* __restrict__ resid, int64_t rows, int ch, int transpose,
                                    int batch, int Q, TAct* __restrict__ out) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  int64_t total = rows * ch;
-  if (idx >= total) return;
-  int64_t r = idx / ch;
-  int c = (int)(idx % ch);
+  const int c8 = ch >> 3;
+  if (idx >= rows * c8) return;
+  int64_t r = idx / c8;
+  int c = (int)(idx % c8) * 8;
   int64_t dst = r;
   if (transpose) { int64_t b = r / Q, i = r % Q; dst = i * batch + b; }
-  float v = __half2float(proj[idx]) * scale;
-  if (bias) v += bias[c];
-  if (resid) v += to_f(resid[dst * ch + c]);
-  out[dst * ch + c] = from_f<TAct>(v);
+  const uint4 raw = *reinterpret_cast<const uint4*>(proj + r * ch + c);
+  const __half* h = reinterpret_cast<const __half*>(&raw);
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = __half2float(h[e]) * scale + (bias ? bias[c + e] : 0.f);
+  const TAct* rs = resid ? resid + dst * ch + c : nullptr;
+  TAct* o = out + dst * ch + c;
+  add_store8<TAct>(v, rs, o);
 }
 
 // Transition hidden layer on the fp16 projection h [rows][wide] into out [rows][hidden] (out may be h when wide == hidden):
@@ -605,21 +632,6 @@ __global__ void opm_split_half_kernel(const __half* __restrict__ lr, const float
   b16[idx] = __float2half_rn((__half2float(lr[r * 2 * c + c + a]) + br[a]) * m);
 }
 
-// outer [(i, a)][(j, b)] (cnt*c rows of N*c) -> per pair [(i, j)][(a, b)], 8 values of b per thread (c % 8 == 0)
-__global__ void opm_regroup_half_kernel(const __half* __restrict__ outer, int cnt, int N, int c, __half* __restrict__ out) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c8 = c >> 3;
-  int64_t total = (int64_t)cnt * N * c * c8;
-  if (idx >= total) return;
-  int b8 = (int)(idx % c8);
-  int64_t t = idx / c8;
-  int a = (int)(t % c); t /= c;
-  int j = (int)(t % N);
-  int i = (int)(t / N);
-  const uint4 v = *reinterpret_cast<const uint4*>(outer + ((int64_t)i * c + a) * ((int64_t)N * c) + (int64_t)j * c + b8 * 8);
-  *reinterpret_cast<uint4*>(out + idx * 8) = v;
-}
-
 // counts[i][j] = sum_s mask[s][i] mask[s][j]
 __global__ void opm_counts_kernel(const float* __restrict__ mask, int S, int N, float* __restrict__ counts) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -636,17 +648,24 @@ template <typename TAct>
 __global__ void opm_finish_half_kernel(const __half* __restrict__ proj, float scale, const float* __restrict__ bout,
                                        const float* __restrict__ counts, int N, int cz, int i0, int cnt, float norm_eps,
                                        int bias_after_norm, const TAct* __restrict__ resid, TAct* __restrict__ out) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)cnt * N * cz) return;
-  int z = (int)(idx % cz);
-  int64_t pr = idx / cz;                       // (i - i0) * N + j
-  int64_t pair = (int64_t)i0 * N + pr;
-  float v = __half2float(proj[idx]) * scale;
-  if (bias_after_norm) v = v / fmaxf(counts[pair], 1.0f) + bout[z];
-  else v = (v + bout[z]) / (norm_eps + counts[pair]);
-  int64_t o = pair * cz + z;
-  if (resid) v += to_f(resid[o]);
-  out[o] = from_f<TAct>(v);
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // eight channels per thread (cz a multiple of 8)
+  const int z8 = cz >> 3;
+  if (idx >= (int64_t)cnt * N * z8) return;
+  const int z = (int)(idx % z8) * 8;
+  const int64_t pr = idx / z8;                 // (i - i0) * N + j
+  const int64_t pair = (int64_t)i0 * N + pr;
+  const uint4 raw = *reinterpret_cast<const uint4*>(proj + pr * cz + z);
+  const __half* h = reinterpret_cast<const __half*>(&raw);
+  const float count = counts[pair];
+  const float inv = bias_after_norm ? 1.0f / fmaxf(count, 1.0f) : 1.0f / (norm_eps + count);
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float t = __half2float(h[e]) * scale;
+    v[e] = bias_after_norm ? t * inv + bout[z + e] : (t + bout[z + e]) * inv;
+  }
+  const int64_t o = pair * cz + z;
+  add_store8<TAct>(v, resid ? resid + o : nullptr, out + o);
 }
 
 __global__ void mask_rows_kernel(float* __restrict__ a, float* __restrict__ b, const float* __restrict__ mask,

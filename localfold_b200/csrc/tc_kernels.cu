@@ -165,6 +165,14 @@ __global__ void triangle_fold_kernel(const float* __restrict__ wz, const float* 
 
 // bf16/fp16 repacks for the tensor-core kernels: h[0] = swizzled fp16 image of the fused
 // projection W^T (plus the pair-bias projection rows for attention), h[1] = its bias vector.
+// weights w [K][ldw] float32, columns col0 .. col0+N-1 -> fp16 [N][K] (the plain GEMM wants k contiguous in both operands)
+__global__ void gemm_operand_kernel(const float* __restrict__ w, int K, int ldw, int col0, int N, op16* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)N * K) return;
+  int n = (int)(idx / K), k = (int)(idx % K);
+  out[idx] = __float2half_rn(w[(int64_t)k * ldw + col0 + n]);
+}
+
 lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
   const bool tri = w->kind == LF_WEIGHTS_TRIANGLE_AF2 || w->kind == LF_WEIGHTS_TRIANGLE_AF3;
   const bool att = w->kind == LF_WEIGHTS_ATTENTION_AF2 || w->kind == LF_WEIGHTS_GRID_ATTENTION_AF3;
@@ -285,6 +293,45 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
     w->h[0] = img;
     w->h[1] = b1;
   }
+  // Operands of the plain fp16 GEMM for the widths the fused kernels do not take: weights [k][n] -> fp16 [n][k]
+  auto operand = [&](const float* src, int K, int ldw, int col0, int N, op16* dst) {
+    gemm_operand_kernel<<<(unsigned)(((int64_t)N * K + 255) / 256), 256, 0, ctx->stream>>>(src, K, ldw, col0, N, dst);
+  };
+  auto alloc16 = [&](int64_t count, op16** out) -> lf_status {
+    LF_CUDA(ctx, cudaMalloc(out, (size_t)count * sizeof(op16)));
+    w->owned.push_back(*out);
+    return LF_OK;
+  };
+  if (w->kind == LF_WEIGHTS_ATTENTION_AF2 && (w->h.empty() || !w->h[0]) && w->dims.heads > 0 && w->dims.channels % w->dims.heads == 0 &&
+      w->dims.channels % 8 == 0) {
+    const int c = w->dims.channels, HD = c;          // heads * (channels / heads)
+    op16 *w4 = nullptr, *wo = nullptr;
+    LF_TRY(alloc16((int64_t)4 * HD * c, &w4));
+    LF_TRY(alloc16((int64_t)c * HD, &wo));
+    operand(w->f[ATT_W4], c, 4 * HD, 0, 4 * HD, w4);
+    operand(w->f[ATT_WO], HD, c, 0, c, wo);
+    w->g = {w4, wo};
+  }
+  if ((w->kind == LF_WEIGHTS_TRANSITION_AF2 || w->kind == LF_WEIGHTS_TRANSITION_AF3) && w->h.empty() &&
+      w->dims.channels % 8 == 0 && w->dims.hidden % 8 == 0) {
+    const int c = w->dims.channels, hd = w->dims.hidden, wide = w->kind == LF_WEIGHTS_TRANSITION_AF3 ? 2 * hd : hd;
+    op16 *w1 = nullptr, *w2 = nullptr;
+    LF_TRY(alloc16((int64_t)wide * c, &w1));
+    LF_TRY(alloc16((int64_t)c * hd, &w2));
+    operand(w->f[TRN_W1], c, wide, 0, wide, w1);
+    operand(w->f[TRN_W2], hd, c, 0, c, w2);
+    w->g = {w1, w2};
+  }
+  if (w->kind == LF_WEIGHTS_OPM_AF2 && w->dims.channels % 8 == 0 && w->dims.hidden % 8 == 0 && w->dims.out_channels % 8 == 0) {
+    const int cm = w->dims.channels, c = w->dims.hidden, cz = w->dims.out_channels;
+    op16 *wlr = nullptr, *wout = nullptr;
+    LF_TRY(alloc16((int64_t)2 * c * cm, &wlr));
+    LF_TRY(alloc16((int64_t)cz * c * c, &wout));
+    operand(w->f[OPM_WL], cm, c, 0, c, wlr);
+    operand(w->f[OPM_WR], cm, c, 0, c, wlr + (int64_t)c * cm);
+    operand(w->f[OPM_WOUT], c * c, cz, 0, cz, wout);
+    w->g = {wlr, wout};
+  }
   LF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return LF_OK;
 }
@@ -307,11 +354,19 @@ constexpr int CT_OUT_STAGE = 32 * 256;          // per epilogue warp: 32 rows x 
 constexpr int CT_SMEM = CT_STAGES * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * CT_OUT_STAGE;
 constexpr int CT_THREADS = 192;
 
+// Extras of the plain-GEMM uses of the kernel (local stores): a bias per output column and a ReLU in the epilogue;
+// `group_c` > 0: rows are (i, a) and columns (j, b) with a, b < group_c, and element (i, a, j, b) is stored at
+// ((i * group_n + j) * group_c + a) * group_c + b - the outer product mean's sums grouped per pair (i, j), which a
+// warp writes as whole 2 * group_c^2-byte runs.  `staged`: local rows leave in 256-byte runs through the staging
+// rows, as rows bound for a peer do (a GEMM with a short k loop is bound by its stores otherwise).
+struct ContractExtra { const float* bias; int relu; int group_c; int group_n; int staged; };
+
 template <int MAJOR>
 __global__ void __launch_bounds__(CT_THREADS, 1)
 contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 op16* __restrict__ x, int m_rows, int n_rows, int k_len, int ldx, int64_t x_plane, int col0, int c,
-                float scale, Status* status, const __grid_constant__ PeerPtrs xpeer, int rows_per_rank, int ch0) {
+                float scale, Status* status, const __grid_constant__ PeerPtrs xpeer, int rows_per_rank, int ch0,
+                const ContractExtra ex) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CT_STAGES * CT_STAGE_BYTES);
@@ -425,15 +480,16 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         dst_row = x + (int64_t)h * x_plane + (int64_t)gi * ldx + col0;
       }
       const int col_limit = (n_rows + 15) / 16 * 16 < ldx - col0 ? (n_rows + 15) / 16 * 16 : ldx - col0;
-      if (rows_per_rank > 0) {
+      if (rows_per_rank > 0 || ex.staged) {
         // Rows bound for another GPU leave in 256-byte runs: a thread holds a row of the accumulator, so its
         // own stores would be 16-byte pieces 32 rows apart, which NVLink carries as 32 small packets.  The
         // warp's 32 rows x 128 columns are turned round in shared memory (16-byte pieces swizzled by row)
         // and written two rows per instruction, 16 lanes x 16 bytes each.
         uint8_t* stage = out_stage + (warp - 2) * CT_OUT_STAGE;
         const int g_row0 = mi * CT_BM + q * 32;            // the warp's rows share an owner: rows_per_rank % 128 == 0
-        const int owner = g_row0 < m_rows ? g_row0 / rows_per_rank : 0;
-        op16* owner_base = reinterpret_cast<op16*>(xpeer.p[owner]) + (int64_t)(ch0 + h) * x_plane + col0;
+        const int owner = rows_per_rank > 0 && g_row0 < m_rows ? g_row0 / rows_per_rank : 0;
+        op16* owner_base = rows_per_rank > 0 ? reinterpret_cast<op16*>(xpeer.p[owner]) + (int64_t)(ch0 + h) * x_plane + col0
+                                             : x + (int64_t)h * x_plane + col0;
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
 #pragma unroll 1
@@ -443,11 +499,30 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             tmem_ld_wait();
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[v * 8 + e]) * scale;
+              if (ex.bias) {
+                const int gj = nj * CT_BN + half * 128 + (cc * 4 + v) * 8;
+                if (gj + 8 <= n_rows) {      // bias is 16-byte aligned and gj a multiple of 8
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(ex.bias + gj));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(ex.bias + gj + 4));
+                  o[0] += b0.x; o[1] += b0.y; o[2] += b0.z; o[3] += b0.w;
+                  o[4] += b1.x; o[5] += b1.y; o[6] += b1.z; o[7] += b1.w;
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] += gj + e < n_rows ? __ldg(ex.bias + gj + e) : 0.f;
+                }
+              }
+              if (ex.relu) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = fmaxf(o[e], 0.f);
+              }
               uint4 pk;
-              pk.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
-              pk.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
-              pk.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
-              pk.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+              pk.x = pack_half2(o[0], o[1]);
+              pk.y = pack_half2(o[2], o[3]);
+              pk.z = pack_half2(o[4], o[5]);
+              pk.w = pack_half2(o[6], o[7]);
               *reinterpret_cast<uint4*>(stage + lane * 256 + (((cc * 4 + v) ^ (lane & 15)) << 4)) = pk;
             }
           }
@@ -474,12 +549,35 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           for (int v = 0; v < 4; ++v) {
             const int gj = gj0 + v * 8;
             if (gj < col_limit) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[v * 8 + e]) * scale;
+              if (ex.bias) {
+                if (gj + 8 <= n_rows) {      // bias is 16-byte aligned and gj a multiple of 8
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(ex.bias + gj));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(ex.bias + gj + 4));
+                  o[0] += b0.x; o[1] += b0.y; o[2] += b0.z; o[3] += b0.w;
+                  o[4] += b1.x; o[5] += b1.y; o[6] += b1.z; o[7] += b1.w;
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] += gj + e < n_rows ? __ldg(ex.bias + gj + e) : 0.f;
+                }
+              }
+              if (ex.relu) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = fmaxf(o[e], 0.f);
+              }
               uint4 pk;
-              pk.x = pack_half2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
-              pk.y = pack_half2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
-              pk.z = pack_half2(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
-              pk.w = pack_half2(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
-              *reinterpret_cast<uint4*>(dst_row + gj) = pk;
+              pk.x = pack_half2(o[0], o[1]);
+              pk.y = pack_half2(o[2], o[3]);
+              pk.z = pack_half2(o[4], o[5]);
+              pk.w = pack_half2(o[6], o[7]);
+              if (ex.group_c) {
+                const int gc = ex.group_c;
+                *reinterpret_cast<uint4*>(x + ((((int64_t)(gi / gc) * ex.group_n + gj / gc) * gc + gi % gc) * gc + gj % gc)) = pk;
+              } else {
+                *reinterpret_cast<uint4*>(dst_row + gj) = pk;
+              }
             }
           }
         }
@@ -524,7 +622,8 @@ bool contract_supported(int n, int c) { return n >= 1 && c >= 1 && g_encode != n
 
 static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                                int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale,
-                               const PeerPtrs* peers, int rows_per_rank, int ch0);
+                               const PeerPtrs* peers, int rows_per_rank, int ch0,
+                               ContractExtra ex = ContractExtra{nullptr, 0, 0, 0, 0});
 
 lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                         int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale) {
@@ -539,9 +638,23 @@ lf_status contract_scatter(lf_context* ctx, ArenaCursor& cur, const op16* a, con
                        rows_per_rank, ch0);
 }
 
+lf_status contract_gemm(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* w, op16* out, int m_rows, int n_out,
+                        int k_len, const float* bias, int relu) {
+  return contract_impl(ctx, cur, a, w, out, m_rows, n_out, k_len, k_len, n_out, 0, 0, 1, 0, 1.0f, nullptr, 0, 0,
+                       ContractExtra{bias, relu, 0, 0, 1});
+}
+
+lf_status contract_outer(lf_context* ctx, ArenaCursor& cur, const op16* left, const op16* right, op16* out, int cnt, int n, int c,
+                         int k_len, float scale) {
+  if (c % 8 != 0) return lf_fail(ctx, LF_ERR_UNSUPPORTED, "the grouped outer product needs c in whole groups of 8");
+  // x[(i, a)][(j, b)] = scale * sum_s left[s][(i, a)] right[s][(j, b)]: both operands MN-major, the kernel's "b" is its M operand
+  return contract_impl(ctx, cur, right, left, out, cnt * c, n * c, k_len, n * c, n * c, 0, 0, 1, 1, scale, nullptr, 0, 0,
+                       ContractExtra{nullptr, 0, c, n, 0});
+}
+
 static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                                int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale,
-                               const PeerPtrs* peers, int rows_per_rank, int ch0) {
+                               const PeerPtrs* peers, int rows_per_rank, int ch0, ContractExtra ex) {
   if (cur.dry) return LF_OK;
   // a row of an operand holds k (K-major form) or the M / N index (MN-major form)
   const int row_len = incoming ? (m_rows > n_rows ? m_rows : n_rows) : k_len;
@@ -561,9 +674,9 @@ static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a,
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_CONTRACT);
   if (!incoming)
-    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0);
+    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0, ex);
   else
-    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0);
+    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0, ex);
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;

@@ -29,6 +29,17 @@ lf_status contract(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16*
 lf_status contract_rect(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* b, op16* x, int m_rows, int n_rows,
                         int k_len, int ld_ab, int ldx, int64_t x_plane, int col0, int c, int incoming, float scale);
 
+// The same kernel as a plain fp16 GEMM: out[m][n] = act(sum_k a[m][k] w[n][k] + bias[n]) (k contiguous in both
+// operands, k_len and n_out multiples of 8; bias may be null; act = ReLU when `relu`), fp16 result.
+lf_status contract_gemm(lf_context* ctx, ArenaCursor& cur, const op16* a, const op16* w, op16* out, int m_rows, int n_out,
+                        int k_len, const float* bias, int relu);
+// ... and as the outer product mean's sum over the sequences, stored grouped per pair:
+// out[((i * n + j) * c + a) * c + b] = scale * sum_s left[s][i*c + a] right[s][j*c + b] for i < cnt, j < n
+// (left, right: k_len rows of n*c, left already offset to its first i), so that the c*c -> c_z projection that
+// follows is a plain GEMM over rows (i, j).
+lf_status contract_outer(lf_context* ctx, ArenaCursor& cur, const op16* left, const op16* right, op16* out, int cnt, int n, int c,
+                         int k_len, float scale);
+
 // Channel-sharded form for the GPUs of one box: a, b are this rank's `c` channels over all n rows
 // ([c][n][ld]); row i of channel h of the product goes to rank i / rows_per_rank, into its buffer
 // x_peers[...] laid out [all channels][rows_per_rank][ldx], at channel ch0 + h.

@@ -346,11 +346,12 @@ def test_msa_row_attention_pair_bias_on_the_16_bit_path(dev):
         assert err <= bound
 
 
-@pytest.mark.parametrize("S,n,cm,c", [(128, 256, 256, 32), (37, 50, 64, 32), (300, 24, 64, 8)])
+@pytest.mark.parametrize("S,n,cm,c", [(128, 256, 256, 32), (37, 50, 64, 32), (300, 24, 64, 8), (20, 33, 64, 24)])
 def test_outer_product_mean_on_the_16_bit_path(dev, S, n, cm, c):
-    """In 16-bit mode the sum over the sequences of the outer products - one GEMM of [(i,a)] x [(j,b)] over s - runs
-    on the tensor cores with fp16 operands and fp16 sums (scaled by a power of two near 1 / S); the c*c -> c_z
-    projection and the division by the coverage stay float32.  First case: the Evoformer block's shape."""
+    """In 16-bit mode the three GEMMs of the operator run on the tensor cores: the left | right projection, the sum
+    over the sequences of the outer products (fp16 sums scaled by a power of two near 1 / S) and the c*c -> c_z
+    projection, a plain GEMM over the pairs because the sums are stored grouped per pair; the division by the
+    coverage is float32.  First case: the Evoformer block's shape; last: a width that is not a power of two."""
     import localfold_b200 as lf
     from parity_report import record
     d = syn.draw(1900 + S)
