@@ -1115,11 +1115,13 @@ template <typename F>
 lf_status run_with_arena(lf_context* ctx, lf_result* r, bool timed, F body) {
   cudaSetDevice(ctx->device);
   ArenaCursor dry{ctx, 0, true};
+  dry.sized_by_dry_pass = true;
   LF_TRY(body(dry));
   LF_TRY(lf_arena_ensure(ctx, dry.peak));
   uint64_t before = ctx->launches;
   if (timed) cudaEventRecord(ctx->ev0, ctx->stream);
   ArenaCursor cur{ctx, 0, false};
+  cur.sized_by_dry_pass = true;
   LF_TRY(body(cur));
   if (cur.peak > ctx->arena_peak) ctx->arena_peak = cur.peak;
   float ms = 0.f;

@@ -112,6 +112,8 @@ struct ArenaCursor {
   size_t offset;
   bool dry;       // planning pass: only adds sizes up
   size_t peak = 0;   // high-water mark (callers may rewind `offset` between operators)
+  bool sized_by_dry_pass = false;   // the arena was sized by a planning pass over the same calls: a launcher may take
+                                    // scratch of its own (entry points that laid the arena out themselves leave it false)
   template <typename T>
   T* take(size_t count) {
     size_t bytes = lf_align_up(count * sizeof(T), 256);

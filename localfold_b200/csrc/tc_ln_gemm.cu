@@ -54,6 +54,8 @@ struct LnGemmParams {
   // its [ch_per_rank][peer_plane_rows][ld] buffer, at rows peer_row0 + local row; stores go to the peers' memory
   int peer_ranks, ch_per_rank, peer_plane_rows, peer_row0;
   PeerPtrs peer_a, peer_b;
+  const float* mask_pad;    // tiles along the pair rows (tile_per_row): the mask with rows zero-padded to mask_ld
+  int mask_ld;
   int plane_tma;            // the planes are written by TMA from staging rows (maps in PlaneMaps), plane_box_h planes per copy
   int plane_box_h;
   // attention projection epilogue
@@ -516,14 +518,29 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
               tmem_ld16(acc + c0, pv);
               tmem_ld16(acc + 128 + c0, gv);
               tmem_ld_wait();
-              const int64_t r64 = t * LG_ROWS + pass * 64;     // n is a multiple of 64: a run lies inside one pair row and
-              if (r64 >= p.rows) break;                        // is in range or out of it as a whole, for all four warps alike
-              const float4* m4 = reinterpret_cast<const float4*>(p.mask + r64 + part * 16);
+              // A run of 64 k lies inside one pair row: n is a multiple of 64, or the tiles are laid along the pair rows
+              // (tile_per_row) and the run past a row's end is clipped by the copy.  It is in range or out of it as a
+              // whole, for all four warps alike.
+              const int64_t r64 = row_base + pass * 64;
+              if (pass * 64 >= row_count) break;
+              // (tiles along the pair rows read a copy of the mask whose rows are padded with zeros to whole tiles)
+              const float4* m4 = reinterpret_cast<const float4*>(
+                  p.tile_per_row ? p.mask_pad + (t / p.tile_per_row) * p.mask_ld + (t % p.tile_per_row) * LG_ROWS + pass * 64 + part * 16
+                                 : p.mask + r64 + part * 16);
               uint32_t pk[8];
 #pragma unroll
               for (int g4 = 0; g4 < 4; ++g4) {
-                const float4 m = __ldg(m4 + g4);
-                const float mm[4] = {m.x, m.y, m.z, m.w};
+                float mm[4];
+                if (p.tile_per_row && !p.mask_pad) {   // ragged rows of the flat mask: no alignment, nothing read past the row's end
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int in_tile = pass * 64 + part * 16 + g4 * 4 + e;
+                    mm[e] = in_tile < row_count ? __ldg(p.mask + row_base + in_tile) : 0.f;
+                  }
+                } else {
+                  const float4 m = __ldg(m4 + g4);
+                  mm[0] = m.x; mm[1] = m.y; mm[2] = m.z; mm[3] = m.w;
+                }
                 float val[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
@@ -546,7 +563,9 @@ ln_gemm_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__
                 if (!mbar_wait(grp_full, staged & 1u, abort_flag, p.status, 20)) { ok = false; break; }
                 if (lane == 0) {
                   const uint32_t u64 = (uint32_t)r64;
-                  const int ti = (int)(u64 / un), tk = (int)(u64 % un);
+                  int ti, tk;
+                  if (p.tile_per_row) { ti = (int)(t / p.tile_per_row); tk = (int)(t % p.tile_per_row) * LG_ROWS + pass * 64; }
+                  else { ti = (int)(u64 / un); tk = (int)(u64 % un); }
                   for (int h0 = 0; h0 < 32; h0 += p.plane_box_h) {
                     const int hh = q * 32 + h0, owner = hh / p.ch_per_rank;
                     tma_store_3d(&planes.m[2 * owner + j], stage + h0 * 128, tk, p.peer_row0 + ti, hh - owner * p.ch_per_rank);
@@ -898,12 +917,14 @@ void configure_ln_gemm() {
 lf_status make_map_plane_runs(lf_context* ctx, CUtensorMap* map, const void* base, uint64_t n, uint64_t plane_rows, uint64_t planes,
                               uint64_t ld, uint32_t box_h);
 
-// Destinations of the triangle projection as tensor maps, when the shape allows the staged copies (runs of 64 k,
-// at most LG_MAX_PLANE_OWNERS owners); otherwise the kernel stores with its own threads.
+// Destinations of the triangle projection as tensor maps, when the shape allows the staged copies (at most
+// LG_MAX_PLANE_OWNERS owners); otherwise the kernel stores with its own threads.
 static lf_status plane_maps(lf_context* ctx, LnGemmParams& p, PlaneMaps& pm, const PeerPtrs& a, const PeerPtrs& b, int owners,
                             int plane_rows) {
   p.plane_tma = 0;
-  if ((p.n & 63) != 0 || owners > LG_MAX_PLANE_OWNERS || 128 % owners != 0) return LF_OK;
+  if (owners > LG_MAX_PLANE_OWNERS || 128 % owners != 0 || p.ld % 8 != 0) return LF_OK;
+  // a length that is not a multiple of 64: tiles along the pair rows, so that a run never straddles two of them
+  if ((p.n & 63) != 0) p.tile_per_row = (p.n + LG_ROWS - 1) / LG_ROWS;
   p.ch_per_rank = 128 / owners;
   p.plane_box_h = p.ch_per_rank < 32 ? p.ch_per_rank : 32;
   for (int o = 0; o < owners; ++o) {
@@ -916,10 +937,35 @@ static lf_status plane_maps(lf_context* ctx, LnGemmParams& p, PlaneMaps& pm, con
   return LF_OK;
 }
 
+// mask [rows][n] -> [rows][mld], zeros past n
+__global__ void pad_mask_kernel(const float* __restrict__ mask, int rows, int n, int mld, float* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)rows * mld) return;
+  const int i = (int)(idx / mld), k = (int)(idx % mld);
+  out[idx] = k < n ? mask[(int64_t)i * n + k] : 0.f;
+}
+
+// A length that is not a multiple of 64 runs the projection with tiles along the pair rows; they read the mask from a
+// copy padded to whole tiles when the call's arena has room planned for one (taken in the sizing pass too), and
+// element by element otherwise.
+static const float* padded_mask(lf_context* ctx, ArenaCursor& cur, const float* mask, int rows, int n, int& mld) {
+  mld = (n & 63) && cur.sized_by_dry_pass ? (n + LG_ROWS - 1) / LG_ROWS * LG_ROWS : 0;
+  if (!mld) return nullptr;
+  float* out = cur.take<float>((int64_t)rows * mld);
+  if (!cur.dry) {
+    pad_mask_kernel<<<(unsigned)(((int64_t)rows * mld + 255) / 256), 256, 0, ctx->stream>>>(mask, rows, n, mld, out);
+    ctx->launches++;
+  }
+  return out;
+}
+
 lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
                            int n, int ld, int variance, float eps, const lf_weights* w, op16* a, op16* b) {
+  int mld = 0;
+  const float* mask_pad = padded_mask(ctx, cur, mask, rows, n, mld);
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
+  p.mask_pad = mask_pad; p.mask_ld = mld;
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;
   p.eps = eps; p.variance = variance;
@@ -942,8 +988,11 @@ lf_status triangle_project(lf_context* ctx, ArenaCursor& cur, const void* z, int
 lf_status triangle_project_scatter(lf_context* ctx, ArenaCursor& cur, const void* z, int act_dtype, const float* mask, int rows,
                                    int n, int ld, int variance, float eps, const lf_weights* w, const PeerPtrs& a_peers,
                                    const PeerPtrs& b_peers, int ranks, int row0) {
+  int mld = 0;
+  const float* mask_pad = padded_mask(ctx, cur, mask, rows, n, mld);
   if (cur.dry) return LF_OK;
   LnGemmParams p{};
+  p.mask_pad = mask_pad; p.mask_ld = mld;
   p.act = z; p.act_bf16 = act_dtype == LF_DTYPE_BF16; p.rows = (int64_t)rows * n; p.transpose = 0; p.batch = 1; p.Q = 1;
   p.plane_rows = rows;
   p.eps = eps; p.variance = variance;
@@ -1053,12 +1102,18 @@ lf_status attention_output(lf_context* ctx, ArenaCursor& cur, const op16* o, int
   // rows (b, q) sit at pair row b*Q + q, or q*batch + b for the transposed orientation, where a warp's 32
   // consecutive q must share b.
   CUtensorMap mo{};
-  p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out) && (!transpose || Q % 32 == 0)) ? 1 : 0;
+  p.tma_out = (!p.out_bf16 && (resid == nullptr || resid == out)) ? 1 : 0;
   if (p.tma_out) {
-    if (transpose) LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)batch, (uint64_t)Q, 512, (uint64_t)batch * 512, 1, 32));
-    else LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)p.rows, 1, 512, (uint64_t)p.rows * 512, 32, 1));
+    if (transpose) {
+      LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)batch, (uint64_t)Q, 512, (uint64_t)batch * 512, 1, 32));
+      // a query length that is not a multiple of 32: tiles along the batch rows, so that a warp's 32 queries share
+      // their batch row; the copy clips the last tile of a row at Q
+      if (Q % 32 != 0) { p.tile_per_row = (Q + LG_ROWS - 1) / LG_ROWS; p.n = Q; p.plane_rows = batch; }
+    } else {
+      LF_TRY(make_map_f32_rows(ctx, &mo, out, (uint64_t)p.rows, 1, 512, (uint64_t)p.rows * 512, 32, 1));
+    }
   }
-  const int64_t tiles = (p.rows + LG_ROWS - 1) / LG_ROWS;
+  const int64_t tiles = p.tile_per_row ? (int64_t)batch * p.tile_per_row : (p.rows + LG_ROWS - 1) / LG_ROWS;
   const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   lf_prof_begin(ctx, LF_KERNEL_LN_GEMM);
   // the fp16 rows are in logical order; the transposed scatter happens in the epilogue (or in the tensor map)
