@@ -10,4 +10,5 @@ from .operators import (  # noqa: F401
     TriangleMultiplicationIncomingGpu, TriangleMultiplicationOutgoingGpu,
     af3_triangle_multiplication, create_device, distogram_logits, error_metrics, int5_decode, validate_triangle_input,
 )
+from .pipeline import PairStackPipeline  # noqa: F401
 from .stack import Af3MsaBlockGpu, Af3MsaStackGpu, Af3PairformerStackGpu, EvoformerBlockGpu, EvoformerStackGpu, ExtraMsaBlockGpu, ExtraMsaStackGpu, PairStackGpu, PreparedMsaBlock, PreparedPairBlock  # noqa: F401

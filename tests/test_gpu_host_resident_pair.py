@@ -57,3 +57,32 @@ def test_af3_block_with_the_pair_on_the_host():
     stack.close()
     dev.close()
     assert oracle.relative_l2(got["pair"], want) <= 2e-3
+
+
+def test_pipeline_of_host_pairs_matches_one_at_a_time():
+    """``PairStackPipeline``: several host pairs in flight on one GPU, a context per lane; every pair's result is
+    that of its own one-at-a-time call."""
+    import torch
+    import localfold_b200 as lf
+    n, jobs = 96, 5
+    pair, mask, blocks = syn.af2_pair_block(77, n, blocks=2)
+    opts = {"precision": "bf16", "variance": "two-pass"}
+    dev = lf.Device(0)
+    stack = lf.PairStackGpu(dev).prepare(blocks, 128, 128)
+    want = []
+    for i in range(jobs):
+        z = np.array(pair * (1.0 + 0.1 * i), np.float32)
+        stack.run(z, mask, opts, inplace=True)
+        want.append(z)
+    stack.close()
+    dev.close()
+    pinned = [torch.from_numpy(np.array(pair * (1.0 + 0.1 * i), np.float32)).pin_memory() for i in range(jobs)]
+    arrays = [p.numpy() for p in pinned]
+    pipe = lf.PairStackPipeline(blocks, 128, 128, lanes=3)
+    results = pipe.run_many(arrays, [mask] * jobs, opts)
+    pipe.close()
+    assert len(results) == jobs and all(r["launches"] > 0 for r in results)
+    for got, ref in zip(arrays, want):
+        assert np.array_equal(got, ref)
+    with pytest.raises(ValueError):
+        lf.PairStackPipeline(blocks, 128, 128, lanes=2).run_many([arrays[0], arrays[0]], [mask, mask], opts)
