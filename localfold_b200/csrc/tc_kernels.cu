@@ -351,8 +351,12 @@ constexpr int CT_A_BYTES = CT_BM * CT_BK * 2;   // 16 KiB
 constexpr int CT_B_BYTES = CT_BN * CT_BK * 2;   // 32 KiB
 constexpr int CT_STAGE_BYTES = CT_A_BYTES + CT_B_BYTES;
 constexpr int CT_OUT_STAGE = 32 * 256;          // per epilogue warp: 32 rows x 128 fp16 columns, for stores into a peer's memory
-constexpr int CT_SMEM = CT_STAGES * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * CT_OUT_STAGE;
-constexpr int CT_THREADS = 192;
+// EW epilogue warps: 4 for the triangle contraction (long k loops hide the epilogue), 8 for the plain GEMMs, whose k
+// loop of 4 to 16 blocks is shorter than a 4-warp epilogue of the 128 x 256 tile; the 8-warp form gives a stage
+// of the operand ring to the four extra staging areas.
+constexpr int ct_stages(int ew) { return ew == 8 ? 3 : CT_STAGES; }
+constexpr int ct_smem(int ew) { return ct_stages(ew) * CT_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + ew * CT_OUT_STAGE; }
+constexpr int ct_threads(int ew) { return 64 + 32 * ew; }
 
 // Extras of the plain-GEMM uses of the kernel (local stores): a bias per output column and a ReLU in the epilogue;
 // `group_c` > 0: rows are (i, a) and columns (j, b) with a, b < group_c, and element (i, a, j, b) is stored at
@@ -361,22 +365,23 @@ constexpr int CT_THREADS = 192;
 // rows, as rows bound for a peer do (a GEMM with a short k loop is bound by its stores otherwise).
 struct ContractExtra { const float* bias; int relu; int group_c; int group_n; int staged; };
 
-template <int MAJOR>
-__global__ void __launch_bounds__(CT_THREADS, 1)
+template <int MAJOR, int EW = 4>
+__global__ void __launch_bounds__(ct_threads(EW), 1)
 contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 op16* __restrict__ x, int m_rows, int n_rows, int k_len, int ldx, int64_t x_plane, int col0, int c,
                 float scale, Status* status, const __grid_constant__ PeerPtrs xpeer, int rows_per_rank, int ch0,
                 const ContractExtra ex) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + CT_STAGES * CT_STAGE_BYTES);
+  constexpr int ST = EW == 8 ? 3 : CT_STAGES;      // = ct_stages(EW)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ST * CT_STAGE_BYTES);
   uint64_t* full = bars;                       // [STAGES]
-  uint64_t* empty = bars + CT_STAGES;          // [STAGES]
-  uint64_t* tmem_full = bars + 2 * CT_STAGES;  // [2]
+  uint64_t* empty = bars + ST;                 // [STAGES]
+  uint64_t* tmem_full = bars + 2 * ST;         // [2]
   uint64_t* tmem_empty = tmem_full + 2;        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* out_stage = smem + CT_STAGES * CT_STAGE_BYTES + 256;     // [4 epilogue warps][CT_OUT_STAGE]
+  uint8_t* out_stage = smem + ST * CT_STAGE_BYTES + 256;     // [EW epilogue warps][CT_OUT_STAGE]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // x[h][i][col0 + j] for i < m_rows, j < n_rows; the contraction index runs over k_len
@@ -386,8 +391,8 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   const int kblocks = (k_len + CT_BK - 1) / CT_BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < CT_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], 4); }
+    for (int s = 0; s < ST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tmem_full[b], 1); mbar_init(&tmem_empty[b], EW); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -419,7 +424,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 #pragma unroll
             for (int q = 0; q < CT_BN / 64; ++q) tma_load_3d(sB + q * 8192, &mapB, &full[stage], nj * CT_BN + q * 64, kb * CT_BK, h);
           }
-          if (++stage == CT_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == ST) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
       }
@@ -453,7 +458,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             umma_f16(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
-          if (++stage == CT_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == ST) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(&tmem_full[buf]);
@@ -461,6 +466,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
   } else {
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int chalf = (warp - 2) >> 2;      // EW == 8: the half of the tile's 256 columns this warp takes
     const int row = q * 32 + lane;
     int it = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++it) {
@@ -491,7 +497,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         op16* owner_base = rows_per_rank > 0 ? reinterpret_cast<op16*>(xpeer.p[owner]) + (int64_t)(ch0 + h) * x_plane + col0
                                              : x + (int64_t)h * x_plane + col0;
 #pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
+        for (int half = (EW == 8 ? chalf : 0); half < (EW == 8 ? chalf + 1 : 2); ++half) {
 #pragma unroll 1
           for (int cc = 0; cc < 4; ++cc) {
             uint32_t r[32];
@@ -539,7 +545,7 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
       } else
 #pragma unroll 1
-      for (int cc = 0; cc < CT_BN / 32; ++cc) {
+      for (int cc = (EW == 8 ? chalf * 4 : 0); cc < (EW == 8 ? chalf * 4 + 4 : CT_BN / 32); ++cc) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * CT_BN + cc * 32, r);
         tmem_ld_wait();
@@ -609,8 +615,10 @@ void configure_once() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return; }
   static std::once_flag per_device[64];
   std::call_once(per_device[dev], [] {
-    cudaFuncSetAttribute(contract_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
-    cudaFuncSetAttribute(contract_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, CT_SMEM);
+    cudaFuncSetAttribute(contract_kernel<0, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, ct_smem(4));
+    cudaFuncSetAttribute(contract_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, ct_smem(4));
+    cudaFuncSetAttribute(contract_kernel<0, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, ct_smem(8));
+    cudaFuncSetAttribute(contract_kernel<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, ct_smem(8));
     configure_ln_gemm();
     configure_attention();
     configure_transition();
@@ -673,10 +681,13 @@ static lf_status contract_impl(lf_context* ctx, ArenaCursor& cur, const op16* a,
   const int tiles = c * ((m_rows + CT_BM - 1) / CT_BM) * ((n_rows + CT_BN - 1) / CT_BN);
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   lf_prof_begin(ctx, LF_KERNEL_TRIANGLE_CONTRACT);
-  if (!incoming)
-    contract_kernel<0><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0, ex);
-  else
-    contract_kernel<1><<<grid, CT_THREADS, CT_SMEM, ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0, ex);
+#define CT_LAUNCH(MAJ, EWN) \
+  contract_kernel<MAJ, EWN><<<grid, ct_threads(EWN), ct_smem(EWN), ctx->stream>>>(mapA, mapB, x, m_rows, n_rows, k_len, ldx, x_plane, col0, c, \
+      scale, (Status*)ctx->tc_status, peers ? *peers : PeerPtrs{}, rows_per_rank, ch0, ex)
+  const bool wide_epilogue = (ex.staged || ex.group_c) && !peers;      // the plain-GEMM uses
+  if (!incoming) { if (wide_epilogue) CT_LAUNCH(0, 8); else CT_LAUNCH(0, 4); }
+  else { if (wide_epilogue) CT_LAUNCH(1, 8); else CT_LAUNCH(1, 4); }
+#undef CT_LAUNCH
   lf_prof_end(ctx);
   ctx->launches++;
   return LF_OK;
