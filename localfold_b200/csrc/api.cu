@@ -1075,9 +1075,10 @@ void trn_f32(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
 template <typename T>
 lf_status trn_half(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
   const auto& f = a.w->f;
-  const int c = a.ch, hd = a.hidden, wide = a.swiglu ? 2 * hd : hd;
+  const int c = a.ch, hd = a.hidden, wide = a.swiglu ? 2 * hd : hd, c16 = c + 16;
   const int64_t chunk = a.rows < (1 << 18) ? a.rows : (1 << 18);
-  op16* nrm = cur.take<op16>(chunk * c);
+  // normalised rows with a column of ones after the channels: the first projection's operand carries its bias there
+  op16* nrm = cur.take<op16>(chunk * c16);
   op16* h1 = cur.take<op16>(chunk * wide);
   op16* h2 = a.swiglu ? cur.take<op16>(chunk * hd) : h1;
   const op16* w1 = gemm_operand(a.w, 0);
@@ -1086,13 +1087,13 @@ lf_status trn_half(lf_context* ctx, ArenaCursor& cur, const TrnArgs& a) {
     int64_t rows = a.rows - r0 < chunk ? a.rows - r0 : chunk;
     const T* in = (const T*)a.act + r0 * c;
     T* out = (T*)a.out + r0 * c;
-    LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16>), lf_ceil_div(rows, 8), 256, 0, in, rows, c, f[TRN_LN_G], f[TRN_LN_B],
+    LAUNCH(ctx, cur, (simt::layer_norm_kernel<T, op16, true>), lf_ceil_div(rows, 8), 256, 0, in, rows, c, f[TRN_LN_G], f[TRN_LN_B],
            a.eps, a.variance, 0, 1, 1, nrm);
     if (a.swiglu) {
-      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c));
-      LAUNCH(ctx, cur, simt::hidden_act_half_kernel, lf_ceil_div(rows * hd, 256), 256, 0, h1, f[TRN_B1], rows, hd, wide, 1, h2);
+      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c16));
+      LAUNCH(ctx, cur, simt::hidden_act_half_kernel, lf_ceil_div(rows * hd, 256), 256, 0, h1, (const float*)nullptr, rows, hd, wide, 1, h2);
     } else {
-      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c, f[TRN_B1], 1));     // bias and ReLU in the GEMM's epilogue
+      LF_TRY(hgemm(ctx, cur, nrm, w1, h1, rows, wide, c16, nullptr, 1));     // ReLU in the GEMM's epilogue
     }
     LF_TRY(hgemm(ctx, cur, h2, w2, nrm, rows, c, hd));
     LAUNCH(ctx, cur, (simt::finish_half_kernel<T>), lf_ceil_div(rows * c / 8, 256), 256, 0, nrm, 1.0f, f[TRN_B2],

@@ -52,7 +52,9 @@ __device__ __forceinline__ void add_store8(float (&v)[8], const TAct* r, TAct* o
 // LayerNorm over the last axis, one warp per row.  `rows` logical rows; logical
 // row r = b*Q + i reads memory row i*batch + b when `transpose` (batch, Q > 0).
 // variance: 1 two-pass, 2 fast (E[x^2]-E[x]^2, unclamped).
-template <typename TIn, typename TOut = float>
+// PAD16: the output rows are ch + 16 long, a one and fifteen zeros after the channels (the k column through which a
+// GEMM that follows adds its bias)
+template <typename TIn, typename TOut = float, bool PAD16 = false>
 __global__ void layer_norm_kernel(const TIn* __restrict__ in, int64_t rows, int ch,
                                   const float* __restrict__ gamma, const float* __restrict__ beta,
                                   float eps, int variance, int transpose, int batch, int Q,
@@ -78,8 +80,9 @@ __global__ void layer_norm_kernel(const TIn* __restrict__ in, int64_t rows, int 
   float inv = rsqrtf(var + eps);
   // one Newton step: rsqrtf is 2 ulp, the parity bar is tighter than that squared error allows
   inv = inv * (1.5f - 0.5f * (var + eps) * inv * inv);
-  TOut* y = out + row * ch;
+  TOut* y = out + row * (PAD16 ? ch + 16 : ch);
   for (int c = lane; c < ch; c += 32) y[c] = from_f<TOut>((to_f(x[c]) - mean) * inv * gamma[c] + beta[c]);
+  if (PAD16 && lane < 16) y[ch + lane] = from_f<TOut>(lane == 0 ? 1.f : 0.f);
 }
 
 // ---------------------------------------------------------------------------

@@ -173,6 +173,17 @@ __global__ void gemm_operand_kernel(const float* __restrict__ w, int K, int ldw,
   out[idx] = __float2half_rn(w[(int64_t)k * ldw + col0 + n]);
 }
 
+// ... with 16 more k columns: the bias in the first, zeros after it (the activations carry a column of ones there, so the
+// GEMM adds the bias)
+__global__ void gemm_operand_bias_kernel(const float* __restrict__ w, int K, int ldw, int N, const float* __restrict__ bias,
+                                         op16* __restrict__ out) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int K2 = K + 16;
+  if (idx >= (int64_t)N * K2) return;
+  int n = (int)(idx / K2), k = (int)(idx % K2);
+  out[idx] = __float2half_rn(k < K ? w[(int64_t)k * ldw + n] : k == K ? bias[n] : 0.f);
+}
+
 lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
   const bool tri = w->kind == LF_WEIGHTS_TRIANGLE_AF2 || w->kind == LF_WEIGHTS_TRIANGLE_AF3;
   const bool att = w->kind == LF_WEIGHTS_ATTENTION_AF2 || w->kind == LF_WEIGHTS_GRID_ATTENTION_AF3;
@@ -316,9 +327,10 @@ lf_status prepare_weights(lf_context* ctx, lf_weights* w) {
       w->dims.channels % 8 == 0 && w->dims.hidden % 8 == 0) {
     const int c = w->dims.channels, hd = w->dims.hidden, wide = w->kind == LF_WEIGHTS_TRANSITION_AF3 ? 2 * hd : hd;
     op16 *w1 = nullptr, *w2 = nullptr;
-    LF_TRY(alloc16((int64_t)wide * c, &w1));
+    LF_TRY(alloc16((int64_t)wide * (c + 16), &w1));      // first projection: [wide][c + 16], its bias in column c
     LF_TRY(alloc16((int64_t)c * hd, &w2));
-    operand(w->f[TRN_W1], c, wide, 0, wide, w1);
+    gemm_operand_bias_kernel<<<(unsigned)(((int64_t)wide * (c + 16) + 255) / 256), 256, 0, ctx->stream>>>(w->f[TRN_W1], c, wide, wide,
+                                                                                                       w->f[TRN_B1], w1);
     operand(w->f[TRN_W2], hd, c, 0, c, w2);
     w->g = {w1, w2};
   }
@@ -364,6 +376,11 @@ constexpr int ct_threads(int ew) { return 64 + 32 * ew; }
 // warp writes as whole 2 * group_c^2-byte runs.  `staged`: local rows leave in 256-byte runs through the staging
 // rows, as rows bound for a peer do (a GEMM with a short k loop is bound by its stores otherwise).
 struct ContractExtra { const float* bias; int relu; int group_c; int group_n; int staged; };
+
+__device__ __forceinline__ uint32_t relu_half2(uint32_t v) {      // max(v, 0) on two packed fp16 values
+  const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&v), __float2half2_rn(0.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
 
 template <int MAJOR, int EW = 4>
 __global__ void __launch_bounds__(ct_threads(EW), 1)
@@ -520,15 +537,12 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                   for (int e = 0; e < 8; ++e) o[e] += gj + e < n_rows ? __ldg(ex.bias + gj + e) : 0.f;
                 }
               }
-              if (ex.relu) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = fmaxf(o[e], 0.f);
-              }
               uint4 pk;
               pk.x = pack_half2(o[0], o[1]);
               pk.y = pack_half2(o[2], o[3]);
               pk.z = pack_half2(o[4], o[5]);
               pk.w = pack_half2(o[6], o[7]);
+              if (ex.relu) { pk.x = relu_half2(pk.x); pk.y = relu_half2(pk.y); pk.z = relu_half2(pk.z); pk.w = relu_half2(pk.w); }
               *reinterpret_cast<uint4*>(stage + lane * 256 + (((cc * 4 + v) ^ (lane & 15)) << 4)) = pk;
             }
           }
@@ -569,15 +583,12 @@ contract_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                   for (int e = 0; e < 8; ++e) o[e] += gj + e < n_rows ? __ldg(ex.bias + gj + e) : 0.f;
                 }
               }
-              if (ex.relu) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = fmaxf(o[e], 0.f);
-              }
               uint4 pk;
               pk.x = pack_half2(o[0], o[1]);
               pk.y = pack_half2(o[2], o[3]);
               pk.z = pack_half2(o[4], o[5]);
               pk.w = pack_half2(o[6], o[7]);
+              if (ex.relu) { pk.x = relu_half2(pk.x); pk.y = relu_half2(pk.y); pk.z = relu_half2(pk.z); pk.w = relu_half2(pk.w); }
               if (ex.group_c) {
                 const int gc = ex.group_c;
                 *reinterpret_cast<uint4*>(x + ((((int64_t)(gi / gc) * ex.group_n + gj / gc) * gc + gi % gc) * gc + gj % gc)) = pk;
