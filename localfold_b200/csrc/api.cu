@@ -1319,7 +1319,7 @@ lf_status lf_outer_product_mean_run(lf_context* ctx, const lf_opm_desc* d, lf_re
              d->layer_norm_epsilon, d->variance, 0, 1, 1, nrm16);
       LF_TRY(hgemm(ctx, cur, nrm16, wlr, lr16, rows, 2 * c, cm));
       LAUNCH(ctx, cur, simt::opm_split_half_kernel, lf_ceil_div(rows * c, 256), 256, 0, lr16, f[OPM_BL], f[OPM_BR], mask, rows, c, left16, right16);
-      LAUNCH(ctx, cur, simt::opm_counts_kernel, lf_ceil_div((int64_t)N * N, 256), 256, 0, mask, S, N, counts);
+      LAUNCH(ctx, cur, simt::opm_counts_kernel, lf_ceil_div((int64_t)((N + 3) / 4) * N, 256), 256, 0, mask, S, N, counts);
       for (int i0 = 0; i0 < N; i0 += ni) {
         int cnt = N - i0 < ni ? N - i0 : ni;
         LF_TRY(tc::contract_outer(ctx, cur, left16 + (int64_t)i0 * c, right16, outer16, cnt, N, c, S, outer_scale));

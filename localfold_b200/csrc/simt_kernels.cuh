@@ -416,10 +416,20 @@ __global__ void rows_to_pieces_kernel(const TSrc* __restrict__ src, int HD, int 
   if (q >= Q) return;
   const int64_t r = (int64_t)b * Q + q;
   const TSrc* x = src + r * 4 * HD + col0 + piece * 8;
+  float in[8];
+  if (sizeof(TSrc) == 2) {      // fp16 rows: one 16-byte load
+    const uint4 raw = *reinterpret_cast<const uint4*>(x);
+    const __half* hx = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) in[e] = __half2float(hx[e]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) in[e] = to_f(x[e]);
+  }
   float v[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    float t = to_f(x[e]);
+    float t = in[e];
     if (bias) t += bias[col0 + piece * 8 + e];
     t *= scale;
     v[e] = kind == 3 ? sigmoidf_(t) : t;
@@ -447,8 +457,12 @@ __global__ void pieces_to_rows_kernel(const __half* __restrict__ src, int batch,
   uint4 raw = *reinterpret_cast<const uint4*>(in);
   const __half* h = reinterpret_cast<const __half*>(&raw);
   TDst* out = dst + r * ld + col0 + piece * 8;
+  if (sizeof(TDst) == 2) {      // fp16 rows: the piece's 16 bytes as they are
+    *reinterpret_cast<uint4*>(out) = raw;
+  } else {
 #pragma unroll
-  for (int e = 0; e < 8; ++e) out[e] = from_f<TDst>(__half2float(h[e]));
+    for (int e = 0; e < 8; ++e) out[e] = from_f<TDst>(__half2float(h[e]));
+  }
 }
 
 // Glue of the 16-bit GEMM path (activations x weights on the tensor cores through the contraction kernel).
@@ -637,12 +651,24 @@ __global__ void opm_split_half_kernel(const __half* __restrict__ lr, const float
 
 // counts[i][j] = sum_s mask[s][i] mask[s][j]
 __global__ void opm_counts_kernel(const float* __restrict__ mask, int S, int N, float* __restrict__ counts) {
+  // four rows i per thread: a value of column j is loaded once for four products
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)N * N) return;
-  int i = (int)(idx / N), j = (int)(idx % N);
-  float cnt = 0.f;
-  for (int s = 0; s < S; ++s) cnt += mask[(int64_t)s * N + i] * mask[(int64_t)s * N + j];
-  counts[idx] = cnt;
+  const int n4 = (N + 3) >> 2;
+  if (idx >= (int64_t)n4 * N) return;
+  const int i0 = (int)(idx / N) * 4, j = (int)(idx % N);
+  int ii[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) ii[e] = i0 + e < N ? i0 + e : N - 1;
+  float cnt[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < S; ++s) {
+    const float* row = mask + (int64_t)s * N;
+    const float mj = row[j];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cnt[e] = fmaf(row[ii[e]], mj, cnt[e]);
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    if (i0 + e < N) counts[(int64_t)(i0 + e) * N + j] = cnt[e];
 }
 
 // out[i][j][z] = (proj[(i - i0) N + j][z] * scale + bout[z]) / (eps + counts[i][j]) (+ resid), or with the bias after
