@@ -55,3 +55,33 @@ def test_host_side_validation_matches_the_reference_messages():
     assert m["maxAbsoluteError"] == 2.0 and m["meanAbsoluteError"] == 1.0
     with pytest.raises(RangeError):
         error_metrics(np.zeros(0), np.zeros(0))
+
+
+def test_python_mirror_of_every_descriptor_matches_the_header(tmp_path):
+    """Sizes and field offsets of the ctypes structures against the C header, as a C compiler lays it out: a field
+    added on one side only would shift every pointer after it."""
+    import subprocess
+    pairs = {"lf_result": nat.Result, "lf_weight_dims": nat.WeightDims, "lf_triangle_desc": nat.TriangleDesc,
+             "lf_attention_desc": nat.AttentionDesc, "lf_transition_desc": nat.TransitionDesc, "lf_opm_desc": nat.OpmDesc,
+             "lf_single_attention_desc": nat.SingleAttentionDesc, "lf_msa_attention_desc": nat.MsaAttentionDesc,
+             "lf_global_attention_desc": nat.GlobalAttentionDesc, "lf_distogram_desc": nat.DistogramDesc,
+             "lf_pair_block_weights": nat.PairBlockWeights, "lf_pair_stack_desc": nat.PairStackDesc,
+             "lf_shard_step_desc": nat.ShardStepDesc, "lf_encoded_tensor": nat.EncodedTensorDesc,
+             "lf_shard_peers": nat.ShardPeers}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "localfold_pairstack.h"', "int main(void) {"]
+    for c_name, mirror in pairs.items():
+        lines.append(f'  printf("{c_name} size %zu\\n", sizeof({c_name}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{c_name} {field} %zu\\n", offsetof({c_name}, {field}));')
+    lines += ["  return 0;", "}"]
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(binary), str(source)], check=True)
+    out = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.splitlines()
+    assert len(out) > 150
+    for line in out:
+        c_name, field, value = line.split()
+        mirror = pairs[c_name]
+        want = ctypes.sizeof(mirror) if field == "size" else getattr(mirror, field).offset
+        assert int(value) == want, line
