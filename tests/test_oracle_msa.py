@@ -83,6 +83,41 @@ def test_outer_product_mean_divides_by_the_coverage_of_both_tokens():
     assert abs(out[0, 1] - 6 / (1e-3 + 1)) < 1e-4
 
 
+def test_outer_product_mean_bias_after_the_division():
+    """The dialect key ``opmBiasAfterNorm`` (``cpu/af3/trunk/msa.js:141-150``): sum / max(count, 1) + bias instead of
+    (sum + bias) / (1e-3 + count); a pair no sequence covers divides by one and keeps the bare bias.  Hand values,
+    then a float64 formulation on random inputs."""
+    w = dict(_pinned_opm(2, 3), outputB=np.array([5.0], np.float32))
+    msa = np.zeros((2, 2, 1), np.float32)
+    mask = np.array([[1, 1], [1, 0]], np.float32)
+    after = oracle.outer_product_mean_af3(msa, mask, w, 1, bias_after_norm=True).reshape(2, 2)
+    before = oracle.outer_product_mean_af3(msa, mask, w, 1, bias_after_norm=False).reshape(2, 2)
+    assert abs(after[0, 0] - (12 / 2 + 5)) < 1e-5 and abs(before[0, 0] - (12 + 5) / (1e-3 + 2)) < 1e-4
+    assert abs(after[0, 1] - (6 / 1 + 5)) < 1e-5 and abs(after[1, 1] - (6 / 1 + 5)) < 1e-5
+    none = oracle.outer_product_mean_af3(msa, np.zeros((2, 2), np.float32), w, 1, bias_after_norm=True)
+    assert np.allclose(none, 5.0)
+    rng = np.random.default_rng(12)
+    S, n, cm, co, cz = 7, 9, 16, 4, 6
+    msa = rng.standard_normal((S, n, cm)).astype(np.float32)
+    mask = (rng.random((S, n)) > 0.3).astype(np.float32)
+    w = {"outerChannels": co, "layerNormInputScale": (1 + 0.1 * rng.standard_normal(cm)).astype(np.float32),
+         "layerNormInputOffset": (0.1 * rng.standard_normal(cm)).astype(np.float32),
+         "leftProjection": (rng.standard_normal((cm, co)) / 4).astype(np.float32),
+         "rightProjection": (rng.standard_normal((cm, co)) / 4).astype(np.float32),
+         "outputW": (rng.standard_normal((co * co, cz)) / 4).astype(np.float32),
+         "outputB": rng.standard_normal(cz).astype(np.float32)}
+    x = msa.astype(np.float64)
+    mean = x.mean(-1, keepdims=True)
+    xn = (x - mean) / np.sqrt(((x - mean) ** 2).mean(-1, keepdims=True) + 1e-5) * w["layerNormInputScale"] + w["layerNormInputOffset"]
+    left = xn @ w["leftProjection"].astype(np.float64) * mask[..., None]
+    right = xn @ w["rightProjection"].astype(np.float64) * mask[..., None]
+    outer = np.einsum("sia,sjb->ijab", left, right).reshape(n, n, co * co)
+    count = np.einsum("si,sj->ij", mask.astype(np.float64), mask.astype(np.float64))
+    want = outer @ w["outputW"].astype(np.float64) / np.maximum(count, 1.0)[..., None] + w["outputB"]
+    got = oracle.outer_product_mean_af3(msa, mask, w, cz, bias_after_norm=True)
+    assert oracle.relative_l2(got, want) < 1e-6
+
+
 def test_msa_block_order_matters_and_has_no_default():
     msa, pair, mm, pm, w = syn.af3_msa_block(13, S=3, n=8, cm=16, cz=16, co=4, msa_heads=2, msa_dim=8, pair_heads=2)
     m_a, p_a = oracle.msa_block_af3(msa, pair, mm, pm, w, False, False)
